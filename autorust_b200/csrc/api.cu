@@ -1,0 +1,255 @@
+// C ABI of libar_attn.so (include/ar_attn.h): argument checks, workspace layout, TMA tensor
+// maps and kernel dispatch.  Plays the part of `cuda_flash_*::run_ex` + `CudaProgram::call`
+// in autorust (src/runtime/cuda_flash_bf16.rs:495-580, src/runtime/ops_cuda.rs:930-1018):
+// marshal the arguments, launch on the caller's stream, never synchronise.
+#include "../../include/ar_attn.h"
+#include "ar_kernels.h"
+
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+namespace {
+
+std::atomic<uint64_t> g_selected[4];
+std::atomic<uint64_t> g_launches;
+
+// Device status word used when the caller passes no workspace.
+__device__ uint32_t g_status_word;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// 1 when the current device is compute capability 10.x.
+bool device_ok() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  static std::mutex mu;
+  static int cache[64];  // 0 unknown, 1 ok, 2 not ok
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && cache[dev]) return cache[dev] == 1;
+  int major = 0;
+  bool ok = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess && major == 10;
+  if (dev < 64) cache[dev] = ok ? 1 : 2;
+  return ok;
+}
+
+// [BH, S, D] row-major tensor; boxes of 128 rows x 128 bytes, 128-byte swizzle.
+bool make_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t BH, int64_t S, int64_t D) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)D * esize, (cuuint64_t)D * esize * (cuuint64_t)S};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / esize), 128u, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+constexpr size_t STATUS_BYTES = 256;
+
+struct SageLayout {
+  size_t q8, k8, q_scale, k_scale, k_mean, v16, total;
+};
+SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  const int64_t nblk = (S + 127) / 128;
+  SageLayout L;
+  size_t off = STATUS_BYTES;
+  L.q8 = off; off = align_up(off + (size_t)(B * Hq * S * D), 256);
+  L.k8 = off; off = align_up(off + (size_t)(B * Hkv * S * D), 256);
+  L.q_scale = off; off = align_up(off + sizeof(float) * (size_t)(B * Hq * nblk), 256);
+  L.k_scale = off; off = align_up(off + sizeof(float) * (size_t)(B * Hkv * nblk), 256);
+  L.k_mean = off; off = align_up(off + sizeof(float) * (size_t)(B * Hkv * D), 256);
+  L.v16 = off;
+  if (dtype == AR_DTYPE_F32) off = align_up(off + 2 * (size_t)(B * Hkv * S * D), 256);
+  L.total = off;
+  return L;
+}
+
+int check_shape(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0) return AR_ERR_SHAPE;
+  if (Hq % Hkv != 0) return AR_ERR_SHAPE;
+  return AR_OK;
+}
+
+bool mode_has_kernel(int mode, int dtype, int64_t B, int64_t Hq, int64_t S, int64_t D) {
+  if (B * Hq > 65535 || S > (1 << 24)) return false;  // grid.y / 32-bit index limits of the kernels
+  switch (mode) {
+    case AR_MODE_EXACT_F32: return dtype == AR_DTYPE_F32 && (D == 64 || D == 128);
+    case AR_MODE_TF32: return false;
+    case AR_MODE_BF16: return dtype == AR_DTYPE_BF16 && ar::attn_tc_has(ar::TC_BF16, (int)D);
+    case AR_MODE_SAGE_INT8: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE, (int)D);
+    default: return false;
+  }
+}
+
+uint32_t* status_word(void* workspace) {
+  if (workspace) return (uint32_t*)workspace;
+  uint32_t* p = nullptr;
+  if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) return nullptr;
+  return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ar_attn_version(void) { return 1; }
+
+int ar_attn_supported(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal,
+                      int has_mask) {
+  (void)causal;
+  (void)has_mask;
+  if (check_shape(B, Hq, Hkv, S, D) != AR_OK) return 0;
+  if (!mode_has_kernel(mode, dtype, B, Hq, S, D)) return 0;
+  return device_ok() ? 1 : 0;
+}
+
+size_t ar_attn_workspace_bytes(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  if (check_shape(B, Hq, Hkv, S, D) != AR_OK) return 0;
+  if (mode == AR_MODE_SAGE_INT8) return sage_layout(dtype, B, Hq, Hkv, S, D).total;
+  return 0;
+}
+
+int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale, float* k_scale,
+                     float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
+                     void* cu_stream) {
+  if (!q || !k || !q8 || !k8 || !q_scale || !k_scale || !k_mean) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if (block != 128 || (D != 64 && D != 128) || (dtype != AR_DTYPE_F32 && dtype != AR_DTYPE_BF16)) return AR_ERR_UNSUPPORTED;
+  if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8)) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  ar::PrologueArgs a{q, k, dtype, q8, k8, q_scale, k_scale, k_mean, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, smooth};
+  int launches = 0;
+  cudaError_t e = ar::launch_sage_prologue(a, (cudaStream_t)cu_stream, &launches);
+  g_launches += (uint64_t)launches;
+  return e == cudaSuccess ? AR_OK : AR_ERR_CUDA;
+}
+
+int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
+                    int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                    size_t workspace_bytes, void* cu_stream) {
+  if (!q || !k || !v || !o) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if (!mode_has_kernel(mode, dtype, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(workspace)) return AR_ERR_ALIGNMENT;
+  if (mask && ((uintptr_t)mask & 3u)) return AR_ERR_ALIGNMENT;
+  const size_t need = ar_attn_workspace_bytes(mode, dtype, B, Hq, Hkv, S, D);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return AR_ERR_WORKSPACE;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+
+  if (mode == AR_MODE_EXACT_F32) {
+    ar::ExactArgs a{(const float*)q, (const float*)k, (const float*)v, (float*)o, mask,
+                    (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, causal};
+    cudaError_t e = ar::launch_attn_exact(a, stream);
+    if (e != cudaSuccess) return AR_ERR_CUDA;
+    g_launches++;
+    g_selected[mode]++;
+    return AR_OK;
+  }
+
+  uint32_t* status = status_word(workspace);
+  if (!status) return AR_ERR_CUDA;
+  ar::TcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.D = (int)D;
+  a.out = o;
+  a.mask = mask;
+  a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
+  a.causal = causal ? 1 : 0;
+  a.status = status;
+  if (mode == AR_MODE_BF16) {
+    a.mode = ar::TC_BF16;
+    a.out_f32 = 0;
+    if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hq, S, D) ||
+        !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D) ||
+        !make_map(&a.tm_v, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+      return AR_ERR_CUDA;
+  } else {  // AR_MODE_SAGE_INT8
+    const SageLayout L = sage_layout(dtype, B, Hq, Hkv, S, D);
+    uint8_t* ws = (uint8_t*)workspace;
+    int8_t* q8 = (int8_t*)(ws + L.q8);
+    int8_t* k8 = (int8_t*)(ws + L.k8);
+    float* qs = (float*)(ws + L.q_scale);
+    float* ks = (float*)(ws + L.k_scale);
+    float* km = (float*)(ws + L.k_mean);
+    ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
+    int launches = 0;
+    if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
+    cudaError_t e = ar::launch_sage_prologue(p, stream, &launches);
+    g_launches += (uint64_t)launches;
+    if (e != cudaSuccess) return AR_ERR_CUDA;
+    const void* v16 = v;
+    if (dtype == AR_DTYPE_F32) {
+      e = ar::launch_f32_to_bf16((const float*)v, ws + L.v16, B * Hkv * S * D, stream);
+      g_launches++;
+      if (e != cudaSuccess) return AR_ERR_CUDA;
+      v16 = ws + L.v16;
+    }
+    a.mode = ar::TC_SAGE;
+    a.out_f32 = dtype == AR_DTYPE_F32;
+    a.q_scale = qs;
+    a.k_scale = ks;
+    if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hq, S, D) ||
+        !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hkv, S, D) ||
+        !make_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+      return AR_ERR_CUDA;
+  }
+  if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  cudaError_t e = ar::launch_attn_tc(a, stream);
+  if (e != cudaSuccess) return AR_ERR_CUDA;
+  g_launches++;
+  g_selected[mode]++;
+  return AR_OK;
+}
+
+int ar_attn_last_status(void* workspace, void* cu_stream) {
+  uint32_t* status = status_word(workspace);
+  if (!status) return AR_ERR_CUDA;
+  uint32_t host = 0;
+  if (cudaStreamSynchronize((cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (cudaMemcpy(&host, status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return AR_ERR_CUDA;
+  return host == 0 ? AR_OK : AR_ERR_DEVICE_WAIT;
+}
+
+uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 4) ? g_selected[mode].load() : 0; }
+uint64_t ar_attn_launch_count(void) { return g_launches.load(); }
+
+const char* ar_attn_strerror(int status) {
+  switch (status) {
+    case AR_OK: return "ok";
+    case AR_ERR_UNSUPPORTED: return "unsupported mode / dtype / shape";
+    case AR_ERR_NULL: return "null pointer";
+    case AR_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
+    case AR_ERR_WORKSPACE: return "workspace missing or too small";
+    case AR_ERR_SHAPE: return "invalid shape";
+    case AR_ERR_CUDA: return "CUDA call failed";
+    case AR_ERR_DEVICE_WAIT: return "a bounded device-side wait expired";
+    case AR_ERR_NO_DEVICE: return "no sm_100 device is current";
+    default: return "unknown status";
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,54 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel translation units.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace ar {
+
+// Tensor-core forward (attn_fwd_tc.cu): bf16 or Sage INT8 QK^T, bf16 PV.
+enum TcMode { TC_BF16 = 0, TC_SAGE = 1 };
+
+struct TcArgs {
+  int mode;             // TcMode
+  int D;                // 64 or 128
+  CUtensorMap tm_q;     // [B*Hq, S, D]   bf16 (TC_BF16) or int8 (TC_SAGE), 128-byte swizzle, box 128 rows
+  CUtensorMap tm_k;     // [B*Hkv, S, D]  same element type as tm_q
+  CUtensorMap tm_v;     // [B*Hkv, S, D]  bf16
+  void* out;            // [B*Hq, S, D]   bf16 or f32
+  int out_f32;
+  const float* mask;    // [S, S] additive or null
+  const float* q_scale; // TC_SAGE: [B*Hq, nblk]
+  const float* k_scale; // TC_SAGE: [B*Hkv, nblk]
+  int B, Hq, Hkv, S;
+  int causal;
+  uint32_t* status;     // device status word
+};
+cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream);
+bool attn_tc_has(int mode, int D);
+
+// Exact f32 forward on FFMA (attn_fwd_exact.cu).
+struct ExactArgs {
+  const float *q, *k, *v;
+  float* out;
+  const float* mask;
+  int B, Hq, Hkv, S, D;
+  int causal;
+};
+cudaError_t launch_attn_exact(const ExactArgs& a, cudaStream_t stream);
+
+// Sage prologue (sage_prologue.cu).
+struct PrologueArgs {
+  const void *q, *k;
+  int dtype;  // 0 f32, 1 bf16
+  int8_t *q8, *k8;
+  float *q_scale, *k_scale, *k_mean;
+  int B, Hq, Hkv, S, D;
+  int smooth;
+};
+// Returns the number of kernels launched through *launches.
+cudaError_t launch_sage_prologue(const PrologueArgs& a, cudaStream_t stream, int* launches);
+// f32 -> bf16 copy of V for Sage with f32 tensors.
+cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream);
+
+}  // namespace ar

@@ -1,0 +1,401 @@
+// Fused attention forward on the sm_100a tensor cores.
+//
+// Replaces autorust's `ar_flash_bf16` (src/runtime/cuda_flash_bf16.rs:98-428) and
+// `ar_flash_sage` (src/runtime/cuda_flash_sage.rs:86-415) -- mma.sync kernels with a 64x32
+// tile -- by one warp-specialised kernel:
+//
+//   CTA = 2 query tiles of 128 rows of one (batch, head) pair, 320 threads:
+//     warps 0-3   softmax for query tile 0   (thread r owns row r = TMEM lane r)
+//     warps 4-7   softmax for query tile 1
+//     warp  8     TMA producer: Q tiles once, then K and V tiles through two rings
+//     warp  9     MMA issuer: S_t = Q_t K_j^T (kind::f16 or kind::i8) and O_t += P_t V_j (kind::f16)
+//   TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [384,384+D);
+//   P_t (bf16, two per column) overwrites the first 64 columns of S_t and is the A operand
+//   of the PV MMA straight from TMEM.
+//
+// The issue order  PV_0(j), S_0(j+1), PV_1(j), S_1(j+1)  lets the tensor pipe work on one
+// query tile while the softmax warps work on the other.  tcgen05.mma instructions of one
+// thread execute in issue order, which is what makes overwriting S_t by S_t(j+1) safe
+// once PV_t(j) has been issued, and what lets the softmax warps touch O_t after S_t(j)
+// has arrived (PV_t(j-1) is then complete).
+//
+// Semantics follow the reference kernels: logits scaled by 1/sqrt(D) in f32, additive
+// [S,S] f32 mask first, then key >= S or (causal and key > row) overrides the logit with the
+// finite -1e30, online softmax in f32 with a running max that starts at -1e30, P rounded to
+// bf16 (rn) for the PV MMA while the row sum keeps the unrounded values, O = acc * (l > 0 ? 1/l : 0)
+// (src/runtime/cuda_flash_bf16.rs:327-424).  Differences that stay inside the tolerance of
+// the reference's own tests: exp is evaluated as ex2 with log2(e) folded into the scale, and
+// the accumulator is rescaled only when the running max grows by more than 2^8.
+//
+// Sage: S_t is the exact s32 product of the INT8 tiles the prologue wrote; it is dequantised
+// by q_scale[q block] * k_scale[k block] / sqrt(D), one scalar per 128x128 tile
+// (src/runtime/cuda_flash_sage.rs:315-322 does the same per row pair).
+#include "ar_kernels.h"
+#include "ar_ptx.cuh"
+
+namespace ar {
+namespace {
+using namespace arptx;
+
+constexpr int BM = 128;  // query rows per tile
+constexpr int BN = 128;  // keys per step
+constexpr float NEG = -1e30f;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+constexpr int NUM_THREADS = 320;
+
+template <int MODE, int D>
+struct Cfg {
+  static constexpr int QK_ESIZE = MODE == TC_SAGE ? 1 : 2;
+  static constexpr int QK_ROW_BYTES = D * QK_ESIZE;
+  static_assert(QK_ROW_BYTES % 128 == 0, "Q/K rows must fill whole 128-byte swizzle atoms");
+  static constexpr int QK_BOXES = QK_ROW_BYTES / 128;
+  static constexpr int QK_BOX_ELEMS = 128 / QK_ESIZE;
+  static constexpr int QK_TILE_BYTES = BM * QK_ROW_BYTES;
+  static constexpr int QK_KSTEPS = QK_ROW_BYTES / 32;  // one MMA consumes 32 bytes of K extent
+  static constexpr int V_BOXES = D * 2 / 128;
+  static constexpr int V_TILE_BYTES = BN * D * 2;
+  static constexpr int PV_KSTEPS = BN / 16;
+  static constexpr int STAGES = (2 * QK_TILE_BYTES + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2;
+  static constexpr int SMEM_TILES = 2 * QK_TILE_BYTES + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
+  static constexpr int NUM_BARS = 2 + 4 * STAGES + 6;
+  static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
+  static constexpr uint32_t IDESC_QK = MODE == TC_SAGE ? make_idesc(2, 1, 1, 0, 0, BM, BN) : make_idesc(1, 1, 1, 0, 0, BM, BN);
+  static constexpr uint32_t IDESC_PV = make_idesc(1, 1, 1, 0, 1, BM, D);
+};
+
+template <int MODE, int D>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
+                   const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
+                   int causal, int out_f32, uint32_t* status) {
+  using C = Cfg<MODE, D>;
+  constexpr int ST = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + 2 * C::QK_TILE_BYTES;
+  uint8_t* sV = sK + ST * C::QK_TILE_BYTES;
+  uint64_t* bars = (uint64_t*)(sV + ST * C::V_TILE_BYTES);
+  uint64_t* q_full = bars;             // [2]
+  uint64_t* k_full = q_full + 2;       // [ST]
+  uint64_t* k_empty = k_full + ST;     // [ST]
+  uint64_t* v_full = k_empty + ST;     // [ST]
+  uint64_t* v_empty = v_full + ST;     // [ST]
+  uint64_t* s_full = v_empty + ST;     // [2]
+  uint64_t* p_full = s_full + 2;       // [2]
+  uint64_t* o_full = p_full + 2;       // [2]
+  uint32_t* tmem_slot = (uint32_t*)(o_full + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / Hq;
+  const int h = bh - b * Hq;
+  const int kvbh = b * Hkv + h / (Hq / Hkv);
+  const int q0 = blockIdx.x * (2 * BM);
+  const int nkv_all = (N + BN - 1) / BN;
+  int nkv[2];
+#pragma unroll
+  for (int t = 0; t < 2; t++) {
+    const int row0 = q0 + t * BM;
+    nkv[t] = row0 >= N ? 0 : (causal ? min(nkv_all, (row0 + BM - 1) / BN + 1) : nkv_all);
+  }
+  const int nkv_max = max(nkv[0], nkv[1]);
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_full[i], 1);
+    }
+    for (int i = 0; i < ST; i++) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int t = 0; t < 2; t++) {
+        if (nkv[t] == 0) continue;
+        mbar_arrive_expect_tx(&q_full[t], C::QK_TILE_BYTES);
+        for (int bx = 0; bx < C::QK_BOXES; bx++)
+          tma_load_3d(sQ + t * C::QK_TILE_BYTES + bx * (BM * 128), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS,
+                      q0 + t * BM, bh);
+      }
+      int issued = 0;
+      for (int j = 0; j < nkv_max; j++) {
+        const int s = j % ST;
+        const int n = j / ST;
+        if (n > 0 && !mbar_wait(&k_empty[s], (n - 1) & 1, abort_flag, status, 0x10)) break;
+        mbar_arrive_expect_tx(&k_full[s], C::QK_TILE_BYTES);
+        for (int bx = 0; bx < C::QK_BOXES; bx++)
+          tma_load_3d(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN,
+                      kvbh);
+        if (n > 0 && !mbar_wait(&v_empty[s], (n - 1) & 1, abort_flag, status, 0x11)) break;
+        mbar_arrive_expect_tx(&v_full[s], C::V_TILE_BYTES);
+        for (int bx = 0; bx < C::V_BOXES; bx++)
+          tma_load_3d(sV + s * C::V_TILE_BYTES + bx * (BN * 128), &tm_v, &v_full[s], bx * 64, j * BN, kvbh);
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        // A wait ran out somewhere in this CTA.  Let the loads this thread started land (bounded)
+        // before the CTA's shared memory is handed back.
+        for (int t = 0; t < 2; t++)
+          if (nkv[t] > 0) mbar_wait_quiet(&q_full[t], 0);
+        for (int j = max(0, issued - ST); j < issued; j++) {
+          mbar_wait_quiet(&k_full[j % ST], (j / ST) & 1);
+          mbar_wait_quiet(&v_full[j % ST], (j / ST) & 1);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t tS[2] = {tb, tb + 128};
+      const uint32_t tO[2] = {tb + 256, tb + 384};
+      auto issue_qk = [&](int t, int ks) {
+        const uint32_t qa = smem_u32(sQ + t * C::QK_TILE_BYTES);
+        const uint32_t ka = smem_u32(sK + ks * C::QK_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::QK_KSTEPS; s++) {
+          const uint32_t off = (s >> 2) * (BM * 128) + (s & 3) * 32;
+          mma_ss<MODE == TC_SAGE ? KIND_I8 : KIND_F16>(tS[t], make_sdesc_sw128(qa + off, 16, 1024),
+                                                      make_sdesc_sw128(ka + off, 16, 1024), C::IDESC_QK, s > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int vs, bool acc) {
+        const uint32_t va = smem_u32(sV + vs * C::V_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::PV_KSTEPS; s++)
+          mma_ts<KIND_F16>(tO[t], tS[t] + s * 8, make_sdesc_sw128(va + s * 2048, BN * 128, 1024), C::IDESC_PV,
+                           (acc || s > 0) ? 1u : 0u);
+      };
+      bool ok = true;
+      if (nkv_max > 0) ok = mbar_wait(&k_full[0], 0, abort_flag, status, 0x20);
+      for (int t = 0; t < 2 && ok; t++) {
+        if (nkv[t] == 0) continue;
+        ok = mbar_wait(&q_full[t], 0, abort_flag, status, 0x21);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(t, 0);
+        tc_commit(&s_full[t]);
+      }
+      if (ok && nkv_max > 0) tc_commit(&k_empty[0]);
+      for (int j = 0; j < nkv_max && ok; j++) {
+        const int s = j % ST;
+        const int s1 = (j + 1) % ST;
+        ok = mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22);
+        if (!ok) break;
+        bool k_next_ready = false;
+        for (int t = 0; t < 2 && ok; t++) {
+          if (j >= nkv[t]) continue;
+          ok = mbar_wait(&p_full[t], j & 1, abort_flag, status, 0x23);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(t, s, j > 0);
+          if (j + 1 < nkv[t]) {
+            if (!k_next_ready) {
+              ok = mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24);
+              if (!ok) break;
+              tc_fence_after();
+              k_next_ready = true;
+            }
+            issue_qk(t, s1);
+            tc_commit(&s_full[t]);
+          } else {
+            tc_commit(&o_full[t]);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[s]);
+        if (j + 1 < nkv_max) tc_commit(&k_empty[s1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps
+    const int t = warp >> 2;
+    const int r = tid & 127;
+    const int row = q0 + t * BM + r;
+    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+    const uint32_t tS = tmem_addr(tb, lane_base, t * 128);
+    const uint32_t tO = tmem_addr(tb, lane_base, 256 + t * 128);
+    const float scale_log2 = rsqrtf((float)D) * LOG2E;
+    const int nblk = nkv_all;
+    float qs = 1.f;
+    if (MODE == TC_SAGE && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
+    float m = NEG, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv[t]; j++) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, status, 0x30));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[BN];
+      tmem_ld32(tS + 0, sv + 0);
+      tmem_ld32(tS + 32, sv + 32);
+      tmem_ld32(tS + 64, sv + 64);
+      tmem_ld32(tS + 96, sv + 96);
+      tmem_wait_ld();
+      float c = scale_log2;
+      if (MODE == TC_SAGE) {
+        c *= qs * k_scale[(size_t)kvbh * nblk + j];
+        // exact s32 -> f32 for |x| < 2^22: add the integer to the bits of 1.5 * 2^23, subtract it again
+#pragma unroll
+        for (int i = 0; i < BN; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i] + 0x4B400000u) - 12582912.0f);
+      }
+      const int col0 = j * BN;
+      const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
+      if (edge) {
+        const float* mrow = (mask != nullptr && row < N) ? mask + (size_t)row * N : nullptr;
+#pragma unroll
+        for (int i = 0; i < BN; i++) {
+          const int col = col0 + i;
+          float x = __uint_as_float(sv[i]) * c;
+          if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
+          if (col >= N || (causal && col > row)) x = NEG;
+          sv[i] = __float_as_uint(x);
+        }
+        c = 1.0f;
+      }
+      float mx = __uint_as_float(sv[0]);
+#pragma unroll
+      for (int i = 1; i < BN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      const float mc = mx * c;
+      if (j == 0) {
+        m = fmaxf(m, mc);
+      } else {
+        const bool need = mc > m + RESCALE_THRESHOLD;
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_new = need ? mc : m;
+          const float alpha = ex2f(m - m_new);
+          m = m_new;
+          l *= alpha;
+#pragma unroll
+          for (int cch = 0; cch < D / 32; cch++) {
+            uint32_t ov[32];
+            tmem_ld32(tO + cch * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st32(tO + cch * 32, ov);
+          }
+        }
+      }
+      const float negm = -m;
+      float lsum = 0.f;
+#pragma unroll
+      for (int qd = 0; qd < 4; qd++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+          const float p0 = ex2f(fmaf(__uint_as_float(sv[qd * 32 + 2 * i]), c, negm));
+          const float p1 = ex2f(fmaf(__uint_as_float(sv[qd * 32 + 2 * i + 1]), c, negm));
+          lsum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(tS + qd * 16, pk);
+      }
+      l += lsum;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[t]);
+    }
+    if (ok && nkv[t] > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], 0, abort_flag, status, 0x31));
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const size_t obase = ((size_t)bh * N + row) * D;
+#pragma unroll
+        for (int cch = 0; cch < D / 32; cch++) {
+          uint32_t ov[32];
+          tmem_ld32(tO + cch * 32, ov);
+          tmem_wait_ld();
+          if (row < N) {
+            if (out_f32) {
+              float4* dst = (float4*)((float*)out + obase + cch * 32);
+#pragma unroll
+              for (int i = 0; i < 8; i++)
+                dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv, __uint_as_float(ov[4 * i + 1]) * inv,
+                                     __uint_as_float(ov[4 * i + 2]) * inv, __uint_as_float(ov[4 * i + 3]) * inv);
+            } else {
+              uint4* dst = (uint4*)((uint16_t*)out + obase + cch * 32);
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                uint4 w;
+                w.x = pack_bf16x2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+                w.y = pack_bf16x2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+                w.z = pack_bf16x2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+                w.w = pack_bf16x2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+                dst[i] = w;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tb, 512);
+}
+
+template <int MODE, int D>
+cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
+  using C = Cfg<MODE, D>;
+  auto kern = attn_fwd_tc_kernel<MODE, D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  dim3 grid((a.S + 2 * BM - 1) / (2 * BM), a.B * a.Hq, 1);
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale, a.k_scale, a.S,
+                                                     a.Hq, a.Hkv, a.causal, a.out_f32, a.status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attn_tc_has(int mode, int D) {
+  if (mode == TC_BF16) return D == 64 || D == 128;
+  if (mode == TC_SAGE) return D == 128;
+  return false;
+}
+
+cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
+  if (a.mode == TC_BF16 && a.D == 128) return launch_one<TC_BF16, 128>(a, stream);
+  if (a.mode == TC_BF16 && a.D == 64) return launch_one<TC_BF16, 64>(a, stream);
+  if (a.mode == TC_SAGE && a.D == 128) return launch_one<TC_SAGE, 128>(a, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace ar

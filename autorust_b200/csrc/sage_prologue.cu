@@ -1,0 +1,215 @@
+// Sage prologue: K mean-smoothing and per-128-token-block symmetric INT8 quantisation of Q and K.
+//
+// The scalar arithmetic is autorust's in-kernel quantiser
+// (src/runtime/cuda_flash_sage.rs:130-135,209-222): scale = amax > 0 ? amax / 127 : 1,
+// inv = 1 / scale, q8 = clamp(rn(x * inv), -127, 127).  The reference applies it per query row /
+// per key row in shared memory, once per query block, and never smooths K; here it runs once per
+// tensor, over blocks of 128 tokens (the MMA tile), after subtracting the token mean of K, and
+// writes INT8 tensors and f32 scales to global memory for the attention kernel.
+//
+// Both kernels are bandwidth-bound and move 16 bytes per thread per access.  Arithmetic that
+// decides bits is kept free of fused multiply-adds and fast-math: every tensor is widened to f32
+// exactly, the K mean is summed in a fixed order (runs of 16 tokens, then the 8 runs of a
+// 128-token span, then the spans, each left to right, times 1.0f / S), K - mean is one f32
+// subtraction, and the division and reciprocal are IEEE.
+#include "ar_kernels.h"
+#include <cuda_bf16.h>
+
+namespace ar {
+namespace {
+
+// 8 consecutive elements starting at element index `idx` (a multiple of 8), widened to f32.
+template <int DTYPE>
+__device__ __forceinline__ void load8(const void* base, size_t idx, float* x) {
+  if constexpr (DTYPE == 1) {
+    const uint4 w = *(const uint4*)((const uint16_t*)base + idx);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      x[2 * i] = __uint_as_float(u[i] << 16);
+      x[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  } else {
+    const float4 a = *(const float4*)((const float*)base + idx);
+    const float4 b = *(const float4*)((const float*)base + idx + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+  }
+}
+
+// k_mean[bh, d]: one CTA per (batch, kv head); MEAN_SLOTS spans of 128 tokens in flight per round.
+// Thread (slot, g, c): slot = tid / D, g = run of 16 tokens inside the span, c = 8-wide d chunk.
+constexpr int MEAN_SLOTS = 4;
+template <int DTYPE, int D>
+__global__ void __launch_bounds__(MEAN_SLOTS * D) k_mean_kernel(const void* __restrict__ K, float* __restrict__ k_mean,
+                                                                int S) {
+  constexpr int CH = D / 8;  // d chunks per token
+  __shared__ float run_sums[MEAN_SLOTS][8][D];  // [span slot][run][d]
+  __shared__ float span_sums[MEAN_SLOTS][D];
+  const int tid = threadIdx.x;
+  const int slot = tid / D;
+  const int g = (tid % D) / CH;
+  const int c = tid % CH;
+  const size_t base = (size_t)blockIdx.x * S * D;
+  float total = 0.f;  // meaningful for tid < D
+  const int nspan = (S + 127) / 128;
+  for (int span0 = 0; span0 < nspan; span0 += MEAN_SLOTS) {
+    const int span = span0 + slot;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    if (span < nspan) {
+      const int t0 = span * 128 + g * 16;
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        float x[8][8];
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+          if (t0 + half * 8 + t < S) load8<DTYPE>(K, base + (size_t)(t0 + half * 8 + t) * D + c * 8, x[t]);
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+          if (t0 + half * 8 + t < S) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] += x[t][i];
+          }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) run_sums[slot][g][c * 8 + i] = acc[i];
+    __syncthreads();
+    {
+      // thread (slot, d): the 8 run sums of its span, left to right
+      const int d = tid % D;
+      float s = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < 8; gg++) s += run_sums[slot][gg][d];
+      span_sums[slot][d] = s;
+    }
+    __syncthreads();
+    if (tid < D) {
+      for (int sl = 0; sl < MEAN_SLOTS && span0 + sl < nspan; sl++) total += span_sums[sl][tid];
+    }
+    // the next round rewrites run_sums before its first barrier and span_sums after it; both are
+    // ordered behind this round's reads by the two barriers above
+  }
+  if (tid < D) k_mean[(size_t)blockIdx.x * D + tid] = total * (1.0f / (float)S);
+}
+
+// One CTA per (tensor row block of 128 tokens, bh).  blockIdx.y < BHq: Q, else K.
+template <int DTYPE, int D>
+__global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ Q, const void* __restrict__ K,
+                                                       const float* __restrict__ k_mean, int8_t* __restrict__ q8,
+                                                       int8_t* __restrict__ k8, float* __restrict__ q_scale,
+                                                       float* __restrict__ k_scale, int S, int BHq, int smooth) {
+  constexpr int CH = D / 8;
+  constexpr int NCHUNK = 128 * CH / 256;  // chunks per thread: 8 (D=128) or 4 (D=64)
+  __shared__ float warp_max[8];
+  const int tid = threadIdx.x;
+  const bool is_k = (int)blockIdx.y >= BHq;
+  const int bh = is_k ? blockIdx.y - BHq : blockIdx.y;
+  const void* src = is_k ? K : Q;
+  int8_t* dst = is_k ? k8 : q8;
+  const int nblk = gridDim.x;
+  const int t0 = blockIdx.x * 128;
+  const size_t base = (size_t)bh * S * D;
+  const int c = tid % CH;  // 256 % CH == 0: every chunk of this thread has the same d range
+  float mu[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) mu[i] = 0.f;
+  if (is_k && smooth) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) mu[i] = k_mean[(size_t)bh * D + c * 8 + i];
+  }
+  float x[NCHUNK][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int n = 0; n < NCHUNK; n++) {
+    const int tok = t0 + (tid + 256 * n) / CH;
+    if (tok < S) {
+      load8<DTYPE>(src, base + (size_t)tok * D + c * 8, x[n]);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        x[n][i] = x[n][i] - mu[i];
+        amax = fmaxf(amax, fabsf(x[n][i]));
+      }
+    }
+  }
+#pragma unroll
+  for (int sh = 16; sh > 0; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+  if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) amax = fmaxf(amax, warp_max[w]);
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  const float inv = __fdiv_rn(1.0f, scale);
+  if (tid == 0) (is_k ? k_scale : q_scale)[(size_t)bh * nblk + blockIdx.x] = scale;
+#pragma unroll
+  for (int n = 0; n < NCHUNK; n++) {
+    const int tok = t0 + (tid + 256 * n) / CH;
+    if (tok < S) {
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        int v = __float2int_rn(__fmul_rn(x[n][i], inv));
+        v = max(-127, min(127, v));
+        w[i >> 2] |= ((uint32_t)v & 0xffu) << (8 * (i & 3));
+      }
+      *(uint2*)(dst + base + (size_t)tok * D + c * 8) = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst,
+                                                          int64_t n8) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 a = *(const float4*)(src + i * 8);
+    const float4 b = *(const float4*)(src + i * 8 + 4);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 w;
+    w.x = *(uint32_t*)&p0; w.y = *(uint32_t*)&p1; w.z = *(uint32_t*)&p2; w.w = *(uint32_t*)&p3;
+    *(uint4*)(dst + i * 8) = w;
+  }
+}
+
+template <int DTYPE, int D>
+cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* launches) {
+  const int nblk = (a.S + 127) / 128;
+  const int bhq = a.B * a.Hq, bhk = a.B * a.Hkv;
+  *launches = 0;
+  if (a.smooth) {
+    k_mean_kernel<DTYPE, D><<<bhk, MEAN_SLOTS * D, 0, stream>>>(a.k, a.k_mean, a.S);
+    (*launches)++;
+  } else {
+    cudaError_t e = cudaMemsetAsync(a.k_mean, 0, sizeof(float) * (size_t)bhk * D, stream);
+    if (e != cudaSuccess) return e;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  quantize_kernel<DTYPE, D><<<dim3(nblk, bhq + bhk, 1), 256, 0, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale,
+                                                                         a.k_scale, a.S, bhq, a.smooth);
+  (*launches)++;
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_sage_prologue(const PrologueArgs& a, cudaStream_t stream, int* launches) {
+  if (a.dtype == 1 && a.D == 128) return launch_prologue_t<1, 128>(a, stream, launches);
+  if (a.dtype == 1 && a.D == 64) return launch_prologue_t<1, 64>(a, stream, launches);
+  if (a.dtype == 0 && a.D == 128) return launch_prologue_t<0, 128>(a, stream, launches);
+  if (a.dtype == 0 && a.D == 64) return launch_prologue_t<0, 64>(a, stream, launches);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream) {
+  const int64_t n8 = n / 8;
+  int blocks = (int)((n8 + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(src, (uint16_t*)dst, n8);
+  return cudaGetLastError();
+}
+
+}  // namespace ar

@@ -1,0 +1,109 @@
+"""Thin torch-facing wrappers over the C ABI: torch owns device memory and streams, the library
+does the work.  These are the calls bench.py and the GPU tests time; every one goes through
+libar_attn.so and raises when the library or a B200 is missing.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _abi
+
+_MODE_NAMES = {"exact": _abi.MODE_EXACT_F32, "tf32": _abi.MODE_TF32, "bf16": _abi.MODE_BF16,
+               "sage": _abi.MODE_SAGE_INT8}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _abi.DTYPE_F32
+    if t.dtype == torch.bfloat16:
+        return _abi.DTYPE_BF16
+    raise TypeError(f"attention tensors must be float32 or bfloat16, got {t.dtype}")
+
+
+def _check_qkv(q, k, v):
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be [B, H, S, D]")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("q, k, v must be CUDA tensors: there is no CPU path")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise ValueError("q, k, v must be contiguous [B, H, S, D]")
+    if k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
+        raise ValueError("shape mismatch between q, k, v")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share one dtype")
+
+
+def mode_code(mode) -> int:
+    return _MODE_NAMES[mode] if isinstance(mode, str) else int(mode)
+
+
+def workspace_bytes(mode, q: torch.Tensor, k: torch.Tensor) -> int:
+    B, Hq, S, D = q.shape
+    return int(_abi.load().ar_attn_workspace_bytes(mode_code(mode), _dtype_code(q), B, Hq, k.shape[1], S, D))
+
+
+def supported(mode, q: torch.Tensor, k: torch.Tensor, causal=False, has_mask=False) -> bool:
+    B, Hq, S, D = q.shape
+    with torch.cuda.device(q.device):
+        return bool(_abi.load().ar_attn_supported(mode_code(mode), _dtype_code(q), B, Hq, k.shape[1], S, D,
+                                                  int(causal), int(has_mask)))
+
+
+def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None = None,
+                 causal: bool = False, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                 stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+    """o = softmax(q k^T / sqrt(D) + mask) v through ar_attn_forward, asynchronously on `stream`
+    (default: torch's current stream).  `workspace` is a uint8 CUDA tensor of at least
+    workspace_bytes(); one is allocated when the mode needs it and none is given."""
+    L = _abi.load()
+    _check_qkv(q, k, v)
+    m = mode_code(mode)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    if mask is not None:
+        if mask.dtype != torch.float32 or tuple(mask.shape) != (S, S) or not mask.is_cuda or not mask.is_contiguous():
+            raise ValueError("mask must be a contiguous float32 CUDA tensor of shape [S, S]")
+    if out is None:
+        out = torch.empty_like(q)
+    need = int(L.ar_attn_workspace_bytes(m, _dtype_code(q), B, Hq, Hkv, S, D))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_attn_forward(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                               mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal),
+                               workspace.data_ptr() if workspace is not None else None,
+                               workspace.numel() * workspace.element_size() if workspace is not None else 0,
+                               s.cuda_stream)
+    _abi.check(rc, "ar_attn_forward")
+    # keep the scratch alive until the stream has consumed it
+    if workspace is not None:
+        workspace.record_stream(s)
+    return out
+
+
+def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=None):
+    """The Sage prologue on its own: returns (q8, k8, q_scale, k_scale, k_mean)."""
+    L = _abi.load()
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    nblk = (S + 127) // 128
+    dev = q.device
+    q8 = torch.empty(q.shape, dtype=torch.int8, device=dev)
+    k8 = torch.empty(k.shape, dtype=torch.int8, device=dev)
+    qs = torch.empty((B, Hq, nblk), dtype=torch.float32, device=dev)
+    ks = torch.empty((B, Hkv, nblk), dtype=torch.float32, device=dev)
+    km = torch.empty((B, Hkv, D), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_sage_quantize(q.data_ptr(), k.data_ptr(), _dtype_code(q), q8.data_ptr(), k8.data_ptr(),
+                                qs.data_ptr(), ks.data_ptr(), km.data_ptr(), B, Hq, Hkv, S, D, 128, int(smooth),
+                                s.cuda_stream)
+    _abi.check(rc, "ar_sage_quantize")
+    return q8, k8, qs, ks, km
+
+
+def last_status(workspace: torch.Tensor | None = None) -> int:
+    L = _abi.load()
+    return int(L.ar_attn_last_status(workspace.data_ptr() if workspace is not None else None,
+                                     torch.cuda.current_stream().cuda_stream))

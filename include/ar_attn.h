@@ -1,0 +1,123 @@
+/*
+ * ar_attn.h -- C ABI of libar_attn.so: autorust's fused attention forward and its
+ * Sage (INT8 QK^T) variant as hand-written sm_100a kernels.
+ *
+ * The library is what autorust's CUDA runtime would bind in place of the NVRTC
+ * kernel strings it launches today.  One call here replaces one
+ * `HostCall::exec` -> `Compiled::run_host_kernel` launch
+ * (src/engine/session.rs:208-255, src/runtime/device.rs:383-402), and
+ * `ar_attn_supported` keeps the role of the per-kernel `supported()` gates
+ * (src/runtime/cuda_flash_bf16.rs:436-445, cuda_flash_tc.rs:386-396,
+ * cuda_flash_sage.rs:69-79, cuda_flash.rs:145-147).
+ *
+ * Conventions
+ *   - every pointer is a raw device pointer (a CUdeviceptr passed as void*) owned by
+ *     the caller; nothing is allocated, freed or kept by the library;
+ *   - tensors are dense row-major: q, o [B, Hq, S, D]; k, v [B, Hkv, S, D];
+ *     mask [S, S] f32, additive, nullable -- the argument order of the reference
+ *     kernels, `Q,K,V,O,M,N,head_dim,causal,has_mask,hq,hkv`
+ *     (src/runtime/cuda_flash_bf16.rs:226-230);
+ *   - q, k, v, o (and the workspace) must be 16-byte aligned: the kernels stage tiles
+ *     with TMA.  A misaligned pointer is reported as AR_ERR_ALIGNMENT, never a fault;
+ *   - calls are asynchronous on `cu_stream` (a CUstream / cudaStream_t as void*, NULL =
+ *     the default stream) and never synchronise: the caller decides when to wait, as
+ *     `run_host_kernel(.., wait)` does;
+ *   - no hidden per-call host state: a call may be replayed with the same pointers
+ *     (src/engine/jit.rs:186-195);
+ *   - every failure is a negative return code; nothing aborts.
+ */
+#ifndef AR_ATTN_H
+#define AR_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Kernel families, in the reference's dispatch vocabulary
+ * (src/models/flash_attention.rs:548-693). */
+enum ar_attn_mode {
+  AR_MODE_EXACT_F32 = 0, /* scalar-FFMA f32 kernel        src/runtime/cuda_flash.rs:48-142     */
+  AR_MODE_TF32 = 1,      /* f32 tensors, TF32 tensor core src/runtime/cuda_flash_tc.rs:92-376  */
+  AR_MODE_BF16 = 2,      /* bf16 in/out, f32 softmax      src/runtime/cuda_flash_bf16.rs:98-428 */
+  AR_MODE_SAGE_INT8 = 3  /* INT8 QK^T, bf16 PV            src/runtime/cuda_flash_sage.rs:86-415 */
+};
+
+/* Element types of q/k/v/o. */
+enum ar_attn_dtype { AR_DTYPE_F32 = 0, AR_DTYPE_BF16 = 1 };
+
+enum ar_attn_status {
+  AR_OK = 0,
+  AR_ERR_UNSUPPORTED = -1, /* shape / dtype / mode combination has no kernel: caller falls back */
+  AR_ERR_NULL = -2,        /* a required pointer is NULL */
+  AR_ERR_ALIGNMENT = -3,   /* q/k/v/o/workspace not 16-byte aligned */
+  AR_ERR_WORKSPACE = -4,   /* workspace missing or smaller than ar_attn_workspace_bytes() */
+  AR_ERR_SHAPE = -5,       /* non-positive extent, Hq % Hkv != 0, ... */
+  AR_ERR_CUDA = -6,        /* a CUDA runtime / driver call failed (launch, tensor map) */
+  AR_ERR_DEVICE_WAIT = -7, /* a bounded wait inside a kernel ran out (see ar_attn_last_status) */
+  AR_ERR_NO_DEVICE = -8    /* no sm_100 device is current */
+};
+
+/* ABI version; bumped on any signature change.  (No counterpart in the reference.) */
+int ar_attn_version(void);
+
+/* 1 when ar_attn_forward has a kernel for this problem on the current device, else 0.
+ * Replaces `cuda_flash_*::supported(n, d, settings)`; unlike the reference (HEAD_DIM == 64
+ * only, src/runtime/cuda_flash_bf16.rs:58) D may be 64 or 128. */
+int ar_attn_supported(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal,
+                      int has_mask);
+
+/* Bytes of device scratch ar_attn_forward needs for this problem (0 for most modes).
+ * Sage: the INT8 copies of Q and K, their per-block scales, the K mean, and -- for f32
+ * inputs -- the bf16 copy of V.  TF32: the transposed copy of V.  Always includes the
+ * 256-byte status block at the start of the workspace.  The reference keeps the same data
+ * in shared memory per CTA (src/runtime/cuda_flash_sage.rs:175-180). */
+size_t ar_attn_workspace_bytes(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D);
+
+/* The fused forward: o = softmax(q k^T / sqrt(D) + mask) v with the reference kernels'
+ * semantics (finite -1e30 sentinel, mask added before the causal override, GQA by
+ * kh = h / (Hq / Hkv); src/runtime/cuda_flash_bf16.rs:244-251,335-348).
+ * Replaces `cuda_flash{,_tc,_bf16,_sage}::run_ex` (src/runtime/cuda_flash_bf16.rs:495-580,
+ * cuda_flash_tc.rs:446-527, cuda_flash_sage.rs:452-516, cuda_flash.rs:203-285).
+ * dtype: element type of q, k, v and o.  EXACT_F32 and TF32 want AR_DTYPE_F32, BF16 wants
+ * AR_DTYPE_BF16, SAGE_INT8 takes either.  Sage runs the quantise prologue
+ * (ar_sage_quantize, 128-token blocks, K smoothing) into the workspace first.
+ * workspace may be NULL when ar_attn_workspace_bytes() is 0. */
+int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
+                    int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                    size_t workspace_bytes, void* cu_stream);
+
+/* The Sage prologue on its own: optional K mean-smoothing, then symmetric INT8 quantisation of
+ * Q and K with one f32 scale per `block` consecutive tokens
+ * (scale = amax > 0 ? amax / 127 : 1; q8 = clamp(rn(x * (1 / scale)), -127, 127): the scalar
+ * arithmetic of `ar_q4`, src/runtime/cuda_flash_sage.rs:130-135,209-222, which the reference
+ * applies per row inside its attention kernel).
+ * q8 [B,Hq,S,D], k8 [B,Hkv,S,D] int8; q_scale [B,Hq,ceil(S/block)], k_scale [B,Hkv,ceil(S/block)],
+ * k_mean [B,Hkv,D] f32.  block must be 128.  smooth = 0 skips the mean (k_mean is zeroed). */
+int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale, float* k_scale,
+                     float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
+                     void* cu_stream);
+
+/* Reads the device status word of a workspace after synchronising `cu_stream`: AR_OK, or
+ * AR_ERR_DEVICE_WAIT when a bounded wait expired inside a kernel (the launch then returned
+ * without finishing its tile).  Stands where the reference has only `cuStreamSynchronize`'s
+ * error (src/runtime/ops_cuda.rs:1013-1016). */
+int ar_attn_last_status(void* workspace, void* cu_stream);
+
+/* Number of launches per kernel family since the library was loaded: the
+ * `selections()` counters the reference's tests assert on
+ * (src/runtime/cuda_flash_tc.rs:398-412, src/runtime/cuda_flash_bf16.rs:447-461,
+ * src/runtime/cuda_flash_sage.rs:421-436). */
+uint64_t ar_attn_selections(int mode);
+
+/* Total kernel launches issued by this library since load (all kernels, prologue included). */
+uint64_t ar_attn_launch_count(void);
+
+const char* ar_attn_strerror(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AR_ATTN_H */

@@ -1,0 +1,166 @@
+"""ctypes front-end of the CPU oracle (oracle/ar_oracle.c, oracle/ar_cpu_baseline.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's CPU
+baseline leg.  The shipped package (autorust_b200/) never imports this module.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_DIR = Path(__file__).resolve().parent
+_LIB_PATH = _DIR / "libar_oracle.so"
+_lib = None
+
+F32, BF16 = 0, 1
+
+
+def build(force: bool = False) -> Path:
+    """Compile libar_oracle.so with gcc (make)."""
+    srcs = [_DIR / "ar_oracle.c", _DIR / "ar_cpu_baseline.c", _DIR / "Makefile"]
+    stale = (not _LIB_PATH.exists()) or any(s.stat().st_mtime > _LIB_PATH.stat().st_mtime for s in srcs)
+    if force or stale:
+        subprocess.run(["make", "-C", str(_DIR), "-B", "libar_oracle.so"], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            build()
+        L = ctypes.CDLL(str(_LIB_PATH))
+        i64, p, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+        L.ar_oracle_sdpa_f32.argtypes = [p, p, p, p, i64, i64, p, i64, i64, i64, i64, i64, ci]
+        L.ar_oracle_sdpa_f32.restype = ci
+        L.ar_oracle_flash.argtypes = [ci, ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, i64, ci]
+        L.ar_oracle_flash.restype = ci
+        L.ar_oracle_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, i64, ci]
+        L.ar_oracle_sage_quantize.restype = ci
+        L.ar_oracle_rows_f32.argtypes = [ci, p, p, i64, p, p, p, i64, i64, ci]
+        L.ar_oracle_rows_f32.restype = ci
+        L.ar_cpu_sdpa_f32.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, ci, i64, i64]
+        L.ar_cpu_sdpa_f32.restype = ci
+        L.ar_oracle_f32_to_bf16.argtypes = [p, p, i64]
+        L.ar_oracle_bf16_to_f32.argtypes = [p, p, i64]
+        _lib = L
+    return _lib
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16 bit patterns (uint16)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().ar_oracle_f32_to_bf16(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def bf16_to_f32(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().ar_oracle_bf16_to_f32(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def sdpa_f32(q, k, v, mask=None, causal=False):
+    """Graph SDPA semantics.  q [B,Hq,N,D], k/v [B,Hkv,N,D] f32; mask additive f32 broadcastable to
+    [B,Hq,N,N] (bool masks: pass 0 / -inf)."""
+    q = np.ascontiguousarray(q, np.float32)
+    k = np.ascontiguousarray(k, np.float32)
+    v = np.ascontiguousarray(v, np.float32)
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    msb = msh = 0
+    if mask is not None:
+        mask = np.ascontiguousarray(np.broadcast_to(np.asarray(mask, np.float32), (B, Hq, N, N)))
+        msb, msh = Hq * N * N, N * N
+    out = np.empty_like(q)
+    rc = lib().ar_oracle_sdpa_f32(_ptr(q), _ptr(k), _ptr(v), _ptr(mask), msb, msh, _ptr(out), B, Hq, Hkv, N, D,
+                                  int(causal))
+    if rc != 0:
+        raise ValueError("ar_oracle_sdpa_f32 rejected the shapes")
+    return out
+
+
+def flash(mode: int, q, k, v, mask=None, causal=False, block=128, smooth=True, out_bf16=None):
+    """The fused kernels' semantics with mode rounding: 0 exact f32, 1 tf32, 2 bf16, 3 sage.
+    q/k/v: float32 arrays, or uint16 arrays holding bf16 bit patterns.  Returns f32, or uint16 bf16
+    bits when the output dtype is bf16 (default: same as the input dtype)."""
+    in_bf16 = q.dtype == np.uint16
+    dt = np.uint16 if in_bf16 else np.float32
+    q = np.ascontiguousarray(q, dt)
+    k = np.ascontiguousarray(k, dt)
+    v = np.ascontiguousarray(v, dt)
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    if out_bf16 is None:
+        out_bf16 = in_bf16
+    out = np.empty(q.shape, dtype=np.uint16 if out_bf16 else np.float32)
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, np.float32)
+        assert mask.shape == (N, N)
+    rc = lib().ar_oracle_flash(mode, BF16 if in_bf16 else F32, BF16 if out_bf16 else F32, _ptr(q), _ptr(k), _ptr(v),
+                               _ptr(mask), _ptr(out), B, Hq, Hkv, N, D, int(causal), block, int(smooth))
+    if rc != 0:
+        raise ValueError("ar_oracle_flash rejected the arguments")
+    return out
+
+
+def sage_quantize(q, k, block=128, smooth=True):
+    """Returns (q8, k8, q_scale, k_scale, k_mean) as the prologue specifies them."""
+    in_bf16 = q.dtype == np.uint16
+    dt = np.uint16 if in_bf16 else np.float32
+    q = np.ascontiguousarray(q, dt)
+    k = np.ascontiguousarray(k, dt)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    nblk = (S + block - 1) // block
+    q8 = np.zeros(q.shape, np.int8)
+    k8 = np.zeros(k.shape, np.int8)
+    qs = np.zeros((B, Hq, nblk), np.float32)
+    ks = np.zeros((B, Hkv, nblk), np.float32)
+    km = np.zeros((B, Hkv, D), np.float32)
+    rc = lib().ar_oracle_sage_quantize(_ptr(q), _ptr(k), BF16 if in_bf16 else F32, _ptr(q8), _ptr(k8), _ptr(qs),
+                                       _ptr(ks), _ptr(km), B, Hq, Hkv, S, D, block, int(smooth))
+    if rc != 0:
+        raise ValueError("ar_oracle_sage_quantize rejected the arguments")
+    return q8, k8, qs, ks, km
+
+
+def rows_f32(q_rows, row_idx, k, v, causal=False):
+    """Exact f32 attention for selected query rows of one head (sampled check at full sizes)."""
+    in_bf16 = q_rows.dtype == np.uint16
+    dt = np.uint16 if in_bf16 else np.float32
+    q_rows = np.ascontiguousarray(q_rows, dt)
+    k = np.ascontiguousarray(k, dt)
+    v = np.ascontiguousarray(v, dt)
+    row_idx = np.ascontiguousarray(row_idx, np.int64)
+    N, D = k.shape
+    out = np.empty((len(row_idx), D), np.float32)
+    lib().ar_oracle_rows_f32(BF16 if in_bf16 else F32, _ptr(q_rows), _ptr(row_idx), len(row_idx), _ptr(k), _ptr(v),
+                             _ptr(out), N, D, int(causal))
+    return out
+
+
+def cpu_sdpa_f32(q, k, v, causal=False, bh_begin=0, bh_end=None):
+    """The timed CPU baseline (blocked AVX2 GEMMs + softmax over all host cores).
+    Returns (out, threads_used); only heads [bh_begin, bh_end) of `out` are written."""
+    q = np.ascontiguousarray(q, np.float32)
+    k = np.ascontiguousarray(k, np.float32)
+    v = np.ascontiguousarray(v, np.float32)
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    if bh_end is None:
+        bh_end = B * Hq
+    out = np.zeros_like(q)
+    n = lib().ar_cpu_sdpa_f32(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, Hq, Hkv, N, D, int(causal), bh_begin, bh_end)
+    if n < 0:
+        raise ValueError("ar_cpu_sdpa_f32 rejected the shapes")
+    return out, n
