@@ -29,6 +29,7 @@ SYMBOLS = (
     "ar_attn_workspace_bytes",
     "ar_attn_forward",
     "ar_sage_quantize",
+    "ar_sage_attention_prequantized",
     "ar_attn_last_status",
     "ar_attn_selections",
     "ar_attn_launch_count",
@@ -64,6 +65,8 @@ def load() -> ctypes.CDLL:
     L.ar_attn_forward.restype = ci
     L.ar_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, ci, p]
     L.ar_sage_quantize.restype = ci
+    L.ar_sage_attention_prequantized.argtypes = [p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]
+    L.ar_sage_attention_prequantized.restype = ci
     L.ar_attn_last_status.argtypes = [p, p]
     L.ar_attn_last_status.restype = ci
     L.ar_attn_selections.argtypes = [ci]

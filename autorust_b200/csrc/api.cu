@@ -101,7 +101,7 @@ bool mode_has_kernel(int mode, int dtype, int64_t B, int64_t Hq, int64_t S, int6
   }
 }
 
-uint32_t* status_word(void* workspace) {
+uint32_t* status_ptr(void* workspace) {
   if (workspace) return (uint32_t*)workspace;
   uint32_t* p = nullptr;
   if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) return nullptr;
@@ -170,7 +170,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     return AR_OK;
   }
 
-  uint32_t* status = status_word(workspace);
+  uint32_t* status = status_ptr(workspace);
   if (!status) return AR_ERR_CUDA;
   ar::TcArgs a;
   memset(&a, 0, sizeof(a));
@@ -225,8 +225,45 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   return AR_OK;
 }
 
+int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const float* q_scale, const float* k_scale,
+                                   const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
+                                   int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
+                                   void* cu_stream) {
+  if (!q8 || !k8 || !q_scale || !k_scale || !v_bf16 || !o) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if (!mode_has_kernel(AR_MODE_SAGE_INT8, AR_DTYPE_BF16, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
+  if (out_dtype != AR_DTYPE_F32 && out_dtype != AR_DTYPE_BF16) return AR_ERR_UNSUPPORTED;
+  if (!aligned16(q8) || !aligned16(k8) || !aligned16(v_bf16) || !aligned16(o)) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  uint32_t* status = status_ptr(status_word);
+  if (!status) return AR_ERR_CUDA;
+  ar::TcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.mode = ar::TC_SAGE;
+  a.D = (int)D;
+  a.out = o;
+  a.out_f32 = out_dtype == AR_DTYPE_F32;
+  a.mask = mask;
+  a.q_scale = q_scale;
+  a.k_scale = k_scale;
+  a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
+  a.causal = causal ? 1 : 0;
+  a.status = status;
+  if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hq, S, D) ||
+      !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hkv, S, D) ||
+      !make_map(&a.tm_v, v_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+    return AR_ERR_CUDA;
+  if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;
+  g_launches++;
+  g_selected[AR_MODE_SAGE_INT8]++;
+  return AR_OK;
+}
+
 int ar_attn_last_status(void* workspace, void* cu_stream) {
-  uint32_t* status = status_word(workspace);
+  uint32_t* status = status_ptr(workspace);
   if (!status) return AR_ERR_CUDA;
   uint32_t host = 0;
   if (cudaStreamSynchronize((cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;

@@ -39,8 +39,11 @@ using namespace arptx;
 
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per step
-constexpr float NEG = -1e30f;
 constexpr float LOG2E = 1.4426950408889634f;
+// The reference's finite sentinel (-1e30), expressed in the log2 domain the softmax works in, so that
+// a logit masked by an additive -1e30 still ties with the initial running max (p = 1 for a fully
+// masked row, as in the reference).
+constexpr float NEG = -1e30f * LOG2E;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr int NUM_THREADS = 320;
 

@@ -103,6 +103,26 @@ def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=
     return q8, k8, qs, ks, km
 
 
+def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None, causal=False, stream=None,
+                                out_dtype=torch.bfloat16):
+    """The Sage attention kernel alone, on the tensors sage_quantize returned (v must be bf16)."""
+    L = _abi.load()
+    B, Hq, S, D = q8.shape
+    Hkv = k8.shape[1]
+    if v.dtype != torch.bfloat16:
+        raise TypeError("v must be bfloat16")
+    if out is None:
+        out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=q8.device)
+    with torch.cuda.device(q8.device):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_sage_attention_prequantized(q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(),
+                                              v.data_ptr(), out.data_ptr(), _dtype_code(out),
+                                              mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D,
+                                              int(causal), None, s.cuda_stream)
+    _abi.check(rc, "ar_sage_attention_prequantized")
+    return out
+
+
 def last_status(workspace: torch.Tensor | None = None) -> int:
     L = _abi.load()
     return int(L.ar_attn_last_status(workspace.data_ptr() if workspace is not None else None,

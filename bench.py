@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (per GPU): the Sage INT8 forward BASELINE.json's metric is quoted on -- B=4, H=32,
+S=8192, D=128, non-causal, bf16 q/k/v ~ N(0,1) with a per-(head, channel) offset ~ N(0,4) on K,
+seed 2 -- as seeded synthetic tensors.  One step = the quantise prologue + the attention kernel
+over that batch.  With N > 1 every rank owns one such batch (weak scaling; global batch element
+g = c*N + r lives on rank r) and the bf16 outputs are all-gathered over NCCL, chunk by chunk on a
+side stream while the next chunk computes.
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput (inputs already in HBM);
+`e2e` goes through the host-facing call with pinned host buffers, H2D and D2H copies inside the
+timed region; `roofline` is the attention kernel timed with CUDA events inside the timed region;
+`cpu_baseline` is the CPU port of the reference's SDPA path timed on this box's host cores on a
+bounded sample.  `--impl reference` times only that CPU path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = {"B": 4, "H": 32, "S": 8192, "D": 128, "causal": False, "seed": 2, "k_offset_sigma": 2.0}
+METRIC = "sage_int8_attention_fwd_throughput"
+UNIT = "TOPS"  # INT8 ops of QK^T + bf16 flops of PV, 4*B*H*S^2*D per batch
+
+
+def work_ops(B, H, S, D, causal=False):
+    return 4.0 * B * H * S * S * D / (2.0 if causal else 1.0)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d.get("hbm_gbs"), "bf16_tflops": d.get("bf16_tflops"),
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------- clocks sampler
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------- CPU baseline
+def cpu_inputs(nheads: int):
+    import numpy as np
+    w = WORKLOAD
+    rng = np.random.default_rng(w["seed"])
+    q = rng.standard_normal((1, nheads, w["S"], w["D"]), dtype=np.float32)
+    k = rng.standard_normal((1, nheads, w["S"], w["D"]), dtype=np.float32)
+    k += np.float32(w["k_offset_sigma"]) * rng.standard_normal((1, nheads, 1, w["D"]), dtype=np.float32)
+    v = rng.standard_normal((1, nheads, w["S"], w["D"]), dtype=np.float32)
+    return q, k, v
+
+
+def cpu_step(q, k, v):
+    """One bounded sample of the workload on the host cores; returns (seconds, threads)."""
+    import oracle
+    t0 = time.perf_counter()
+    _, threads = oracle.cpu_sdpa_f32(q, k, v, WORKLOAD["causal"])
+    return time.perf_counter() - t0, threads
+
+
+def cpu_baseline_leg(budget_s: float = 12.0) -> dict:
+    import oracle
+    oracle.build()
+    w = WORKLOAD
+    q, k, v = cpu_inputs(1)
+    cpu_step(q, k, v)  # warm-up (page faults, thread pool)
+    dt, threads = cpu_step(q, k, v)
+    nheads = max(1, min(16, int(budget_s / max(dt, 1e-3))))
+    q, k, v = cpu_inputs(nheads)
+    dt, threads = cpu_step(q, k, v)
+    ops = work_ops(1, nheads, w["S"], w["D"], w["causal"])
+    return {"value": ops / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{nheads} of {w['B'] * w['H']} (batch, head) pairs of the workload, f32 SDPA "
+                      f"(blocked AVX2 GEMMs + softmax, OpenMP), {dt:.2f} s"}
+
+
+def run_reference_arm(args, rank: int) -> None:
+    """The reference's own path for this workload is its CPU SDPA (no Rust toolchain here: the C port
+    in oracle/ar_cpu_baseline.c).  Each step is a bounded sample: `heads` (batch, head) pairs."""
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    w = WORKLOAD
+    heads = 4
+    q, k, v = cpu_inputs(heads)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_step(q, k, v)
+    times, threads = [], 1
+    for _ in range(args.steps):
+        dt, threads = cpu_step(q, k, v)
+        times.append(dt)
+    total = sum(times)
+    ops = work_ops(1, heads, w["S"], w["D"], w["causal"]) * args.steps
+    value = ops / total / 1e12
+    sample = f"{heads} of {w['B'] * w['H']} (batch, head) pairs per step, f32 SDPA port, all host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal (BASELINE config 3)", **WORKLOAD,
+                   "timing": "wall clock around each bounded CPU sample"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------- GPU arm
+def make_inputs(torch, device, seed):
+    w = WORKLOAD
+    g = torch.Generator(device=device).manual_seed(seed)
+    shp = (w["B"], w["H"], w["S"], w["D"])
+    q = torch.randn(shp, device=device, generator=g).to(torch.bfloat16)
+    k = (torch.randn(shp, device=device, generator=g) +
+         w["k_offset_sigma"] * torch.randn((1, w["H"], 1, w["D"]), device=device, generator=g)).to(torch.bfloat16)
+    v = torch.randn(shp, device=device, generator=g).to(torch.bfloat16)
+    return q, k, v
+
+
+def int8_peak_tops(torch, device) -> float | None:
+    """Dense INT8 tensor throughput of this GPU, measured live with a library GEMM (not in
+    MEASURED_PEAKS.json): torch._int_mm 8192^3, best of 10."""
+    try:
+        n = 8192
+        a = torch.randint(-8, 8, (n, n), dtype=torch.int8, device=device)
+        b = torch.randint(-8, 8, (n, n), dtype=torch.int8, device=device)
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None or ms < best else best
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+    import torch.distributed as dist
+    from autorust_b200 import _abi, ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the attention path has no CPU fallback (use --impl reference "
+                         "for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    L = _abi.load()
+    w = WORKLOAD
+    B, H, S, D = w["B"], w["H"], w["S"], w["D"]
+    q, k, v = make_inputs(torch, device, w["seed"] + 1000 * rank)
+    out = torch.empty_like(q)
+    nblk = (S + 127) // 128
+    q8 = torch.empty((B, H, S, D), dtype=torch.int8, device=device)
+    k8 = torch.empty_like(q8)
+    qs = torch.empty((B, H, nblk), dtype=torch.float32, device=device)
+    ks = torch.empty_like(qs)
+    km = torch.empty((B, H, D), dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream()
+    comm_stream = torch.cuda.Stream() if world > 1 else None
+    gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device) if world > 1 else None
+    kernel_events: list = []
+
+    def quantise(b0, b1):
+        rc = L.ar_sage_quantize(q[b0:b1].data_ptr(), k[b0:b1].data_ptr(), _abi.DTYPE_BF16, q8[b0:b1].data_ptr(),
+                                k8[b0:b1].data_ptr(), qs[b0:b1].data_ptr(), ks[b0:b1].data_ptr(), km[b0:b1].data_ptr(),
+                                b1 - b0, H, H, S, D, 128, 1, stream.cuda_stream)
+        _abi.check(rc, "ar_sage_quantize")
+
+    def attend(b0, b1, record):
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        rc = L.ar_sage_attention_prequantized(q8[b0:b1].data_ptr(), k8[b0:b1].data_ptr(), qs[b0:b1].data_ptr(),
+                                              ks[b0:b1].data_ptr(), v[b0:b1].data_ptr(), out[b0:b1].data_ptr(),
+                                              _abi.DTYPE_BF16, None, b1 - b0, H, H, S, D, int(w["causal"]), None,
+                                              stream.cuda_stream)
+        _abi.check(rc, "ar_sage_attention_prequantized")
+        if record:
+            e1.record(stream)
+            kernel_events.append((e0, e1, b1 - b0))
+
+    def step(record=False):
+        """Prologue + attention over this rank's batch (the two C-ABI calls ar_attn_forward makes for
+        the Sage mode, issued apart so the attention kernel can be bracketed by events)."""
+        if world == 1:
+            quantise(0, B)
+            attend(0, B, record)
+            return
+        for c in range(B):  # one batch element per chunk; gather chunk c while chunk c+1 computes
+            quantise(c, c + 1)
+            attend(c, c + 1, record)
+            done = torch.cuda.Event()
+            done.record(stream)
+            comm_stream.wait_event(done)
+            with torch.cuda.stream(comm_stream):
+                dist.all_gather_into_tensor(gathered[c], out[c])
+        stream.wait_stream(comm_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    launches0 = int(L.ar_attn_launch_count())
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(args.steps):
+        step(record=True)
+    t1.record(stream)
+    barrier()
+    launches = int(L.ar_attn_launch_count()) - launches0
+    ms_total = t0.elapsed_time(t1)
+    status = int(L.ar_attn_last_status(None, stream.cuda_stream))
+    if status != 0:
+        raise SystemExit(f"device status after the timed region: {_abi.strerror(status)}")
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    ops_per_step_rank = work_ops(B, H, S, D, w["causal"])
+    value = ops_per_step_rank * world / (ms_per_step * 1e-3) / 1e12
+
+    # roofline of the dominant kernel: its launches inside the timed region, bracketed by events
+    kern_ms = [e0.elapsed_time(e1) * (B / nb) for (e0, e1, nb) in kernel_events]  # scaled to a full-batch launch
+    kern_ms_avg = sum(kern_ms) / len(kern_ms)
+    peaks = measured_peaks()
+    i8_peak = int8_peak_tops(torch, device) if rank == 0 else None
+    achieved = ops_per_step_rank / (kern_ms_avg * 1e-3) / 1e12
+    bf16_peak = peaks["bf16_tflops"]
+    roofline = {
+        "bound": "tensor", "kernel": "attn_fwd_tc_kernel<SAGE,128>", "achieved": achieved, "peak": bf16_peak,
+        "unit": "TFLOP/s", "frac": achieved / bf16_peak, "traffic": None,
+        "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst), {peaks['source']}",
+        "kernel_ms": kern_ms_avg,
+        "note": "achieved = (INT8 QK^T ops + bf16 PV flops) / kernel time; half of the work runs at the INT8 rate",
+    }
+    if i8_peak:
+        mixed = 2.0 / (1.0 / i8_peak + 1.0 / bf16_peak)
+        roofline.update({"int8_peak_tops_live": i8_peak, "frac_of_int8_peak": achieved / i8_peak,
+                         "mixed_peak": mixed, "frac_of_mixed_peak": achieved / mixed})
+
+    # end to end through the host-facing call: pinned host buffers, H2D + D2H inside the timed region
+    e2e = None
+    if True:
+        from autorust_b200 import host
+        e2e = host.bench_e2e(q, k, v, causal=w["causal"], steps=max(3, min(args.steps, 10)), warmup=2, world=world)
+        e2e_value = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
+        e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d_bytes"] * world,
+               "d2h_bytes_per_step": e2e["d2h_bytes"] * world, "ms_per_step": e2e["ms_per_step"],
+               "api": e2e["api"]}
+        if world > 1:
+            t = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e["ms_per_step"] = float(t.item())
+            e2e["value"] = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline_leg()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
+            "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (BASELINE config 3)",
+                       **w, "global_batch": B * world, "partition": "batch-interleaved over ranks, bf16 output "
+                       "all-gather over NCCL overlapped per batch element" if world > 1 else "single GPU",
+                       "l2": "inputs (805 MB) exceed L2 (126 MB); no flush needed",
+                       "timing": "CUDA events on the launching stream, max over ranks"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "per_gpu_tops": value / world,
+        }
+        print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_gpu_arm(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -100,6 +100,17 @@ int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t
                      float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
                      void* cu_stream);
 
+/* The Sage attention kernel alone, on tensors ar_sage_quantize already produced (for callers that
+ * keep quantised K across calls, and for timing the kernel apart from its prologue): INT8 QK^T,
+ * dequantised per 128x128 tile by q_scale * k_scale / sqrt(D), online softmax, bf16 P.V.
+ * This is the body of `ar_flash_sage` after its in-kernel quantisation
+ * (src/runtime/cuda_flash_sage.rs:283-414).  v is bf16 [B,Hkv,S,D]; o is bf16 or f32 (out_dtype).
+ * status_word: 4 bytes of device memory for the bounded-wait status, or NULL for the library's own. */
+int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const float* q_scale, const float* k_scale,
+                                   const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
+                                   int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
+                                   void* cu_stream);
+
 /* Reads the device status word of a workspace after synchronising `cu_stream`: AR_OK, or
  * AR_ERR_DEVICE_WAIT when a bounded wait expired inside a kernel (the launch then returned
  * without finishing its tile).  Stands where the reference has only `cuStreamSynchronize`'s
