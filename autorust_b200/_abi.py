@@ -21,6 +21,8 @@ AR_ERR_SHAPE = -5
 AR_ERR_CUDA = -6
 AR_ERR_DEVICE_WAIT = -7
 AR_ERR_NO_DEVICE = -8
+AR_ERR_TOO_LARGE = -9
+SAGE_STATIC_SCRATCH_BYTES = 32 << 20
 
 # Every symbol include/ar_attn.h declares; tests check that the library exports each one.
 SYMBOLS = (
@@ -30,6 +32,7 @@ SYMBOLS = (
     "ar_attn_forward",
     "ar_sage_quantize",
     "ar_sage_attention_prequantized",
+    "ar_sage_forward_static",
     "ar_attn_last_status",
     "ar_attn_selections",
     "ar_attn_launch_count",
@@ -67,6 +70,8 @@ def load() -> ctypes.CDLL:
     L.ar_sage_quantize.restype = ci
     L.ar_sage_attention_prequantized.argtypes = [p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]
     L.ar_sage_attention_prequantized.restype = ci
+    L.ar_sage_forward_static.argtypes = [ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p]
+    L.ar_sage_forward_static.restype = ci
     L.ar_attn_last_status.argtypes = [p, p]
     L.ar_attn_last_status.restype = ci
     L.ar_attn_selections.argtypes = [ci]

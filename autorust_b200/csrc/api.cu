@@ -110,6 +110,14 @@ uint32_t* status_ptr(void* workspace) {
 
 }  // namespace
 
+namespace ar {
+// Lets other translation units of the library feed the launch counters.
+void count_launches(int mode, int kernels) {
+  g_launches += (uint64_t)kernels;
+  if (mode >= 0 && mode < 4) g_selected[mode]++;
+}
+}  // namespace ar
+
 extern "C" {
 
 int ar_attn_version(void) { return 1; }
@@ -285,6 +293,7 @@ const char* ar_attn_strerror(int status) {
     case AR_ERR_CUDA: return "CUDA call failed";
     case AR_ERR_DEVICE_WAIT: return "a bounded device-side wait expired";
     case AR_ERR_NO_DEVICE: return "no sm_100 device is current";
+    case AR_ERR_TOO_LARGE: return "problem exceeds the library's built-in scratch (ar_sage_forward_static)";
     default: return "unknown status";
   }
 }

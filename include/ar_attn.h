@@ -57,7 +57,8 @@ enum ar_attn_status {
   AR_ERR_SHAPE = -5,       /* non-positive extent, Hq % Hkv != 0, ... */
   AR_ERR_CUDA = -6,        /* a CUDA runtime / driver call failed (launch, tensor map) */
   AR_ERR_DEVICE_WAIT = -7, /* a bounded wait inside a kernel ran out (see ar_attn_last_status) */
-  AR_ERR_NO_DEVICE = -8    /* no sm_100 device is current */
+  AR_ERR_NO_DEVICE = -8,   /* no sm_100 device is current */
+  AR_ERR_TOO_LARGE = -9    /* problem exceeds the built-in scratch of ar_sage_forward_static */
 };
 
 /* ABI version; bumped on any signature change.  (No counterpart in the reference.) */
@@ -110,6 +111,25 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
                                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
                                    void* cu_stream);
+
+/* Size of the scratch ar_sage_forward_static keeps inside the library, per GPU. */
+#define AR_SAGE_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* The Sage forward (what ar_attn_forward does in AR_MODE_SAGE_INT8: prologue, then attention) for
+ * callers that cannot allocate device memory where attention runs -- a replay loop whose buffers were
+ * planned ahead of time, a process that handed the whole GPU to another allocator, a latency-critical
+ * path that cannot afford cudaMalloc's device-wide synchronisation.  It has no counterpart in the
+ * reference.  The scratch lives in a fixed AR_SAGE_STATIC_SCRATCH_BYTES array in device memory, present
+ * on every GPU that loads the library until the process exits; the call itself allocates and frees
+ * nothing.  A problem whose Sage workspace (ar_attn_workspace_bytes) exceeds that size returns
+ * AR_ERR_TOO_LARGE.  The first call on a device resolves the array's address; issue it before any stream
+ * capture.  All calls on a device share the array and it keeps the previous call's contents (the status
+ * word is cleared per call, the rest is rewritten before it is read): calls that overlap on one GPU
+ * race -- order them on a stream, or use ar_attn_forward with separate workspaces.
+ * After the stream is synchronised, ar_attn_last_status cannot see this call's status word; a launch that
+ * did not finish shows up as wrong output.  dtype, pointers, shapes, mask and causal as ar_attn_forward. */
+int ar_sage_forward_static(int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
+                           int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* cu_stream);
 
 /* Reads the device status word of a workspace after synchronising `cu_stream`: AR_OK, or
  * AR_ERR_DEVICE_WAIT when a bounded wait expired inside a kernel (the launch then returned
