@@ -4,11 +4,13 @@
 // `ar_flash_sage` (src/runtime/cuda_flash_sage.rs:86-415) -- mma.sync kernels with a 64x32
 // tile -- by one warp-specialised kernel:
 //
-//   CTA = 2 query tiles of 128 rows of one (batch, head) pair, 320 threads:
+//   CTA = 2 query tiles of 128 rows of one (batch, head) pair, 384 threads:
 //     warps 0-3   softmax for query tile 0   (thread r owns row r = TMEM lane r)
 //     warps 4-7   softmax for query tile 1
 //     warp  8     TMA producer: Q tiles once, then K and V tiles through two rings
 //     warp  9     MMA issuer: S_t = Q_t K_j^T (kind::f16 or kind::i8) and O_t += P_t V_j (kind::f16)
+//     warps 10-11 idle; they complete the third warpgroup so that it can hand its registers
+//                 (setmaxnreg) to the softmax warps, which keep a whole 128-column row in registers
 //   TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [384,384+D);
 //   P_t (bf16, two per column) overwrites the first 64 columns of S_t and is the A operand
 //   of the PV MMA straight from TMEM.
@@ -45,7 +47,9 @@ constexpr float LOG2E = 1.4426950408889634f;
 // masked row, as in the reference).
 constexpr float NEG = -1e30f * LOG2E;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 384;    // 3 warpgroups: softmax 0, softmax 1, {TMA producer, MMA issuer, 2 idle warps}
+constexpr int SOFTMAX_REGS = 232;   // register budget of the softmax warps after setmaxnreg
+constexpr int SERVICE_REGS = 40;    // ... and of the third warpgroup
 
 template <int MODE, int D>
 struct Cfg {
@@ -139,6 +143,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after();
   const uint32_t tb = *tmem_slot;
 
+  if (warp >= 8) setmaxnreg_dec<SERVICE_REGS>();
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -238,15 +243,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (j + 1 < nkv_max) tc_commit(&k_empty[s1]);
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------------ softmax warps
+    setmaxnreg_inc<SOFTMAX_REGS>();
     const int t = warp >> 2;
     const int r = tid & 127;
     const int row = q0 + t * BM + r;
     const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
     const uint32_t tS = tmem_addr(tb, lane_base, t * 128);
     const uint32_t tO = tmem_addr(tb, lane_base, 256 + t * 128);
-    const float scale_log2 = rsqrtf((float)D) * LOG2E;
+    const float scale_log2 = (1.0f / sqrtf((float)D)) * LOG2E;
     const int nblk = nkv_all;
     float qs = 1.f;
     if (MODE == TC_SAGE && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
@@ -263,30 +269,53 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
       float c = scale_log2;
-      if (MODE == TC_SAGE) {
-        c *= qs * k_scale[(size_t)kvbh * nblk + j];
-        // exact s32 -> f32 for |x| < 2^22: add the integer to the bits of 1.5 * 2^23, subtract it again
-#pragma unroll
-        for (int i = 0; i < BN; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i] + 0x4B400000u) - 12582912.0f);
-      }
+      if (MODE == TC_SAGE) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
+      float mc;  // row maximum of this tile in the scaled (log2) domain
       if (edge) {
+        // boundary / diagonal / masked tiles: element-wise path; leaves scaled logits in sv and c = 1
         const float* mrow = (mask != nullptr && row < N) ? mask + (size_t)row * N : nullptr;
+        float mx = NEG;
 #pragma unroll
         for (int i = 0; i < BN; i++) {
           const int col = col0 + i;
-          float x = __uint_as_float(sv[i]) * c;
+          float x = MODE == TC_SAGE ? (float)(int)sv[i] * c : __uint_as_float(sv[i]) * c;
           if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
           if (col >= N || (causal && col > row)) x = NEG;
           sv[i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
         }
         c = 1.0f;
-      }
-      float mx = __uint_as_float(sv[0]);
+        mc = mx;
+      } else if (MODE == TC_SAGE) {
+        // exact s32 scores: integer maximum first, one conversion for the row; then every element goes
+        // s32 -> f32 through the bits of 1.5 * 2^23 (exact for |x| < 2^22)
+        int m0 = (int)sv[0], m1 = (int)sv[1], m2 = (int)sv[2], m3 = (int)sv[3];
 #pragma unroll
-      for (int i = 1; i < BN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      const float mc = mx * c;
+        for (int i = 4; i < BN; i += 8) {
+          m0 = __vimax3_s32(m0, (int)sv[i], (int)sv[i + 1]);
+          m1 = __vimax3_s32(m1, (int)sv[i + 2], (int)sv[i + 3]);
+          if (i + 4 < BN) {
+            m2 = __vimax3_s32(m2, (int)sv[i + 4], (int)sv[i + 5]);
+            m3 = __vimax3_s32(m3, (int)sv[i + 6], (int)sv[i + 7]);
+          }
+        }
+        mc = (float)max(max(m0, m1), max(m2, m3)) * c;
+      } else {
+        float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]),
+              m3 = __uint_as_float(sv[3]);
+#pragma unroll
+        for (int i = 4; i < BN; i += 8) {
+          m0 = fmax3(m0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+          if (i + 4 < BN) {
+            m2 = fmax3(m2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+            m3 = fmax3(m3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+          }
+        }
+        mc = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c;
+      }
       if (j == 0) {
         m = fmaxf(m, mc);
       } else {
@@ -296,31 +325,51 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const float alpha = ex2f(m - m_new);
           m = m_new;
           l *= alpha;
+          const uint64_t alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll
           for (int cch = 0; cch < D / 32; cch++) {
             uint32_t ov[32];
             tmem_ld32(tO + cch * 32, ov);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            for (int i = 0; i < 32; i += 2) {
+              float a, b;
+              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), alpha2), a, b);
+              ov[i] = __float_as_uint(a);
+              ov[i + 1] = __float_as_uint(b);
+            }
             tmem_st32(tO + cch * 32, ov);
           }
         }
       }
-      const float negm = -m;
-      float lsum = 0.f;
+      // p = 2^(x * c - m), two lanes per instruction; the row sum keeps the unrounded values
+      const uint64_t c2 = pack_f32x2(c, c);
+      const uint64_t negm2 = pack_f32x2(-m, -m);
+      const uint64_t magic2 = pack_f32x2(-12582912.0f, -12582912.0f);
+      uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
       for (int qd = 0; qd < 4; qd++) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-          const float p0 = ex2f(fmaf(__uint_as_float(sv[qd * 32 + 2 * i]), c, negm));
-          const float p1 = ex2f(fmaf(__uint_as_float(sv[qd * 32 + 2 * i + 1]), c, negm));
-          lsum += p0 + p1;
+          uint64_t x2;
+          if (MODE == TC_SAGE && !edge)
+            x2 = add_f32x2(pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
+                                      __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u)), magic2);
+          else
+            x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i]), __uint_as_float(sv[qd * 32 + 2 * i + 1]));
+          float a, b;
+          unpack_f32x2(fma_f32x2(x2, c2, negm2), a, b);
+          const float p0 = ex2f(a), p1 = ex2f(b);
+          const uint64_t p2 = pack_f32x2(p0, p1);
+          if (i & 1) sum_b = add_f32x2(sum_b, p2); else sum_a = add_f32x2(sum_a, p2);
           pk[i] = pack_bf16x2(p0, p1);
         }
         tmem_st16(tS + qd * 16, pk);
       }
+      float lsum, lsum_hi;
+      unpack_f32x2(add_f32x2(sum_a, sum_b), lsum, lsum_hi);
+      lsum += lsum_hi;
       l += lsum;
       tmem_wait_st();
       tc_fence_before();

@@ -1,0 +1,53 @@
+"""Runs one attention configuration a few times and prints its device time: the small, self-ending
+case to put under a profiler (or to time a shape that is not the benchmark's).
+
+    python -m autorust_b200.profile_case --mode sage --B 1 --H 32 --S 8192 --D 128 --iters 3
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import ops
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="sage", choices=["exact", "bf16", "sage"])
+    ap.add_argument("--B", type=int, default=1)
+    ap.add_argument("--H", type=int, default=32)
+    ap.add_argument("--Hkv", type=int, default=0)
+    ap.add_argument("--S", type=int, default=8192)
+    ap.add_argument("--D", type=int, default=128)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=1)
+    a = ap.parse_args()
+    hkv = a.Hkv or a.H
+    dtype = torch.float32 if a.mode == "exact" else torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(a.B, a.H, a.S, a.D, device="cuda", generator=g).to(dtype)
+    k = (torch.randn(a.B, hkv, a.S, a.D, device="cuda", generator=g) +
+         2.0 * torch.randn(1, hkv, 1, a.D, device="cuda", generator=g)).to(dtype)
+    v = torch.randn(a.B, hkv, a.S, a.D, device="cuda", generator=g).to(dtype)
+    out = torch.empty_like(q)
+    nbytes = ops.workspace_bytes(a.mode, q, k)
+    ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device="cuda")
+    for _ in range(a.warmup):
+        ops.attn_forward(a.mode, q, k, v, None, a.causal, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        ops.attn_forward(a.mode, q, k, v, None, a.causal, out=out, workspace=ws)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.iters
+    work = 4.0 * a.B * a.H * a.S * a.S * a.D / (2.0 if a.causal else 1.0)
+    print(f"{a.mode} B={a.B} H={a.H}/{hkv} S={a.S} D={a.D} causal={a.causal}: {ms:.3f} ms/forward, "
+          f"{work / ms / 1e9:.1f} T(FL)OP/s, status={ops.last_status(ws if nbytes else None)}")
+
+
+if __name__ == "__main__":
+    main()
