@@ -14,8 +14,8 @@ namespace {
 std::atomic<uint64_t> g_selected[4];
 std::atomic<uint64_t> g_launches;
 
-// Device status word used when the caller passes no workspace.
-__device__ uint32_t g_status_word;
+// Device status block used when the caller passes no workspace (word 0 is the status word).
+__device__ __align__(256) uint32_t g_status_word[64];
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -278,6 +278,18 @@ int ar_attn_last_status(void* workspace, void* cu_stream) {
   if (cudaMemcpy(&host, status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return AR_ERR_CUDA;
   return host == 0 ? AR_OK : AR_ERR_DEVICE_WAIT;
 }
+
+#ifdef AR_TRACE
+// Debug builds only: copies the 31 cycle accumulators the traced kernel adds behind the status word.
+int ar_debug_read_trace(void* workspace, unsigned long long* out31, int clear) {
+  uint32_t* st = status_ptr(workspace);
+  if (!st) return AR_ERR_CUDA;
+  cudaDeviceSynchronize();
+  if (cudaMemcpy(out31, st + 2, 31 * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return AR_ERR_CUDA;
+  if (clear) cudaMemset(st + 2, 0, 31 * 8);
+  return AR_OK;
+}
+#endif
 
 uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 4) ? g_selected[mode].load() : 0; }
 uint64_t ar_attn_launch_count(void) { return g_launches.load(); }

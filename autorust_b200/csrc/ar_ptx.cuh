@@ -51,27 +51,54 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware suspend the thread for up to `hint_ns` while the phase is pending.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
-// Wait budget: far longer than any launch of these kernels, short enough that a
-// broken pipeline ends by itself.
-#ifndef AR_WAIT_BUDGET_NS
-#define AR_WAIT_BUDGET_NS 400000000ull /* 0.4 s */
+// Wait budget in SM clock cycles (clock64): about 0.4 s at 2 GHz -- far longer than any launch of these
+// kernels, short enough that a broken pipeline ends by itself.  The SM-local cycle counter is used
+// because reading it costs a few cycles, whereas %globaltimer is a slow system register.
+#ifndef AR_WAIT_MODE
+#define AR_WAIT_MODE 0
+#endif
+#ifndef AR_WAIT_BUDGET_CYCLES
+#define AR_WAIT_BUDGET_CYCLES 800000000ll
 #endif
 
 // Bounded wait on `bar` for phase `parity`. `abort_flag` is a CTA-shared word: once
 // any wait in the CTA has run out, every later wait returns false at once.
 // On expiry the site id is OR-ed into *status (global memory; may be null).
+// mbarrier.try_wait suspends the thread in hardware for a bounded time, so the loop is not a hot spin.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
-  const uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
+#if AR_WAIT_MODE == 1
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+#elif AR_WAIT_MODE == 2
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xff) == 0) {
+    __nanosleep(40);
+#elif AR_WAIT_MODE == 3
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(200);
+#else
+    if (mbar_try_wait(bar, parity)) return true;
+#endif
+    if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > AR_WAIT_BUDGET_NS) {
+      if (clock64() - t0 > AR_WAIT_BUDGET_CYCLES) {
         *abort_flag = 1u;
         if (status) atomicOr(status, 0x80000000u | site);
         return false;
@@ -83,9 +110,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Bounded wait that records nothing: used on the way out of an aborted CTA to let copies that
 // are still in flight land.  Gives up after about a millisecond.
 __device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
-  const uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (globaltimer_ns() - t0 > 1000000ull) return false;
+    if (clock64() - t0 > 2000000ll) return false;
   }
   return true;
 }
@@ -179,6 +206,54 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
         "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+// The same two instructions with the 64-bit shared-memory descriptors passed as (low, high) words.
+// The issuing thread keeps the high words (layout, strides) and per-tile low words (address >> 4)
+// in registers and only adds a small constant to a low word per instruction, which keeps the
+// single-threaded issue loop short.
+template <int KIND>
+__device__ __forceinline__ void mma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                            uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (KIND == KIND_F16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if constexpr (KIND == KIND_TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+template <int KIND>
+__device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t accumulate) {
+  if constexpr (KIND == KIND_F16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }

@@ -39,6 +39,20 @@ namespace ar {
 namespace {
 using namespace arptx;
 
+// Optional cycle accounting (-DAR_TRACE, debug builds only): per-role clock64 deltas accumulated
+// behind the status word.
+#ifdef AR_TRACE
+#define TR_DECL(n) long long tr_##n = 0
+#define TR_T(var) const long long var = clock64()
+#define TR_ADD(n, a, b) tr_##n += (b) - (a)
+#define TR_FLUSH(slot, n) atomicAdd(((unsigned long long*)status) + 1 + (slot), (unsigned long long)tr_##n)
+#else
+#define TR_DECL(n)
+#define TR_T(var)
+#define TR_ADD(n, a, b)
+#define TR_FLUSH(slot, n)
+#endif
+
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per step
 constexpr float LOG2E = 1.4426950408889634f;
@@ -48,8 +62,118 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG = -1e30f * LOG2E;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr int NUM_THREADS = 384;    // 3 warpgroups: softmax 0, softmax 1, {TMA producer, MMA issuer, 2 idle warps}
-constexpr int SOFTMAX_REGS = 232;   // register budget of the softmax warps after setmaxnreg
-constexpr int SERVICE_REGS = 40;    // ... and of the third warpgroup
+constexpr int SOFTMAX_REGS = 224;   // register budget of the softmax warps after setmaxnreg
+constexpr int SERVICE_REGS = 56;    // ... and of the third warpgroup
+
+// One softmax step of one row: scores of 128 keys (sv, raw accumulator bits) -> P in TMEM, running
+// max m and running sum l updated, O rescaled in place when the max grows by more than the threshold.
+// EDGE selects the element-wise path for steps that touch the sequence end, the causal diagonal or
+// an additive mask.
+template <int MODE, int D, bool EDGE>
+__device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float& l, float c, int j, int col0, int row,
+                                             int N, int causal, const float* __restrict__ mask, uint32_t tS,
+                                             uint32_t tO) {
+  float mc;  // row maximum of this step in the scaled (log2) domain
+  if constexpr (EDGE) {
+    // leaves scaled logits in sv and c = 1
+    const float* mrow = (mask != nullptr && row < N) ? mask + (size_t)row * N : nullptr;
+    float mx = NEG;
+#pragma unroll
+    for (int i = 0; i < BN; i++) {
+      const int col = col0 + i;
+      float x = MODE == TC_SAGE ? (float)(int)sv[i] * c : __uint_as_float(sv[i]) * c;
+      if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
+      if (col >= N || (causal && col > row)) x = NEG;
+      sv[i] = __float_as_uint(x);
+      mx = fmaxf(mx, x);
+    }
+    c = 1.0f;
+    mc = mx;
+  } else if constexpr (MODE == TC_SAGE) {
+    // exact s32 scores: integer maximum first, one conversion for the row
+    int m0 = (int)sv[0], m1 = (int)sv[1], m2 = (int)sv[2], m3 = (int)sv[3];
+#pragma unroll
+    for (int i = 4; i < BN; i += 8) {
+      m0 = __vimax3_s32(m0, (int)sv[i], (int)sv[i + 1]);
+      m1 = __vimax3_s32(m1, (int)sv[i + 2], (int)sv[i + 3]);
+      if (i + 4 < BN) {
+        m2 = __vimax3_s32(m2, (int)sv[i + 4], (int)sv[i + 5]);
+        m3 = __vimax3_s32(m3, (int)sv[i + 6], (int)sv[i + 7]);
+      }
+    }
+    mc = (float)max(max(m0, m1), max(m2, m3)) * c;
+  } else {
+    float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]),
+          m3 = __uint_as_float(sv[3]);
+#pragma unroll
+    for (int i = 4; i < BN; i += 8) {
+      m0 = fmax3(m0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+      m1 = fmax3(m1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+      if (i + 4 < BN) {
+        m2 = fmax3(m2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+        m3 = fmax3(m3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+      }
+    }
+    mc = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c;
+  }
+  if (j == 0) {
+    m = fmaxf(m, mc);
+  } else {
+    const bool need = mc > m + RESCALE_THRESHOLD;
+    if (__any_sync(0xffffffffu, need)) {
+      // S(j) has arrived, so PV(j-1) of this tile is complete and O may be scaled in place
+      const float m_new = need ? mc : m;
+      const float alpha = ex2f(m - m_new);
+      m = m_new;
+      l *= alpha;
+      const uint64_t alpha2 = pack_f32x2(alpha, alpha);
+#pragma unroll 1
+      for (int cch = 0; cch < D / 32; cch++) {
+        uint32_t ov[32];
+        tmem_ld32(tO + cch * 32, ov);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a, b;
+          unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), alpha2), a, b);
+          ov[i] = __float_as_uint(a);
+          ov[i + 1] = __float_as_uint(b);
+        }
+        tmem_st32(tO + cch * 32, ov);
+      }
+    }
+  }
+  // p = 2^(x * c - m), two lanes per instruction; the row sum keeps the unrounded values
+  const uint64_t c2 = pack_f32x2(c, c);
+  const uint64_t negm2 = pack_f32x2(-m, -m);
+  const uint64_t magic2 = pack_f32x2(-12582912.0f, -12582912.0f);
+  uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+  for (int qd = 0; qd < 4; qd++) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      uint64_t x2;
+      if constexpr (MODE == TC_SAGE && !EDGE) {
+        // s32 -> f32 through the bits of 1.5 * 2^23 (exact for |x| < 2^22)
+        x2 = add_f32x2(pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
+                                  __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u)), magic2);
+      } else {
+        x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i]), __uint_as_float(sv[qd * 32 + 2 * i + 1]));
+      }
+      float a, b;
+      unpack_f32x2(fma_f32x2(x2, c2, negm2), a, b);
+      const float p0 = ex2f(a), p1 = ex2f(b);
+      const uint64_t p2 = pack_f32x2(p0, p1);
+      if (i & 1) sum_b = add_f32x2(sum_b, p2); else sum_a = add_f32x2(sum_a, p2);
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+    tmem_st16(tS + qd * 16, pk);
+  }
+  float lsum, lsum_hi;
+  unpack_f32x2(add_f32x2(sum_a, sum_b), lsum, lsum_hi);
+  l += lsum + lsum_hi;
+}
 
 template <int MODE, int D>
 struct Cfg {
@@ -103,7 +227,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int b = bh / Hq;
   const int h = bh - b * Hq;
   const int kvbh = b * Hkv + h / (Hq / Hkv);
-  const int q0 = blockIdx.x * (2 * BM);
+  // causal: heavy (late) query tiles first, so that the last CTAs of the grid are the light ones
+  const int qblock = causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int q0 = qblock * (2 * BM);
   const int nkv_all = (N + BN - 1) / BN;
   int nkv[2];
 #pragma unroll
@@ -183,25 +309,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t tS[2] = {tb, tb + 128};
-      const uint32_t tO[2] = {tb + 256, tb + 384};
+      // Descriptor words that never change: the high halves, and the low halves (address >> 4) of the
+      // first Q tile, K stage and V stage.  Per instruction only a constant is added to a low word.
+      const uint64_t qk_proto = make_sdesc_sw128(0, 16, 1024);
+      const uint64_t v_proto = make_sdesc_sw128(0, BN * 128, 1024);
+      const uint32_t qk_hi = (uint32_t)(qk_proto >> 32), v_hi = (uint32_t)(v_proto >> 32);
+      const uint32_t qk_lo = (uint32_t)qk_proto, v_lo = (uint32_t)v_proto;
+      const uint32_t q_lo0 = qk_lo | (smem_u32(sQ) >> 4);
+      const uint32_t k_lo0 = qk_lo | (smem_u32(sK) >> 4);
+      const uint32_t v_lo0 = v_lo | (smem_u32(sV) >> 4);
       auto issue_qk = [&](int t, int ks) {
-        const uint32_t qa = smem_u32(sQ + t * C::QK_TILE_BYTES);
-        const uint32_t ka = smem_u32(sK + ks * C::QK_TILE_BYTES);
+        const uint32_t d = tb + t * 128;
+        const uint32_t qa = q_lo0 + t * (C::QK_TILE_BYTES >> 4);
+        const uint32_t ka = k_lo0 + ks * (C::QK_TILE_BYTES >> 4);
 #pragma unroll
         for (int s = 0; s < C::QK_KSTEPS; s++) {
-          const uint32_t off = (s >> 2) * (BM * 128) + (s & 3) * 32;
-          mma_ss<MODE == TC_SAGE ? KIND_I8 : KIND_F16>(tS[t], make_sdesc_sw128(qa + off, 16, 1024),
-                                                      make_sdesc_sw128(ka + off, 16, 1024), C::IDESC_QK, s > 0);
+          const uint32_t off = ((s >> 2) * (BM * 128) + (s & 3) * 32) >> 4;
+          mma_ss_lohi<MODE == TC_SAGE ? KIND_I8 : KIND_F16>(d, qa + off, qk_hi, ka + off, qk_hi, C::IDESC_QK, s > 0);
         }
       };
       auto issue_pv = [&](int t, int vs, bool acc) {
-        const uint32_t va = smem_u32(sV + vs * C::V_TILE_BYTES);
+        const uint32_t d = tb + 256 + t * 128;
+        const uint32_t a = tb + t * 128;
+        const uint32_t va = v_lo0 + vs * (C::V_TILE_BYTES >> 4);
 #pragma unroll
         for (int s = 0; s < C::PV_KSTEPS; s++)
-          mma_ts<KIND_F16>(tO[t], tS[t] + s * 8, make_sdesc_sw128(va + s * 2048, BN * 128, 1024), C::IDESC_PV,
-                           (acc || s > 0) ? 1u : 0u);
+          mma_ts_lohi<KIND_F16>(d, a + s * 8, va + s * (2048 >> 4), v_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
       };
+      TR_DECL(mma_wait_kv); TR_DECL(mma_wait_p); TR_DECL(mma_issue); TR_T(tm_begin);
       bool ok = true;
       if (nkv_max > 0) ok = mbar_wait(&k_full[0], 0, abort_flag, status, 0x20);
       for (int t = 0; t < 2 && ok; t++) {
@@ -216,23 +351,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int j = 0; j < nkv_max && ok; j++) {
         const int s = j % ST;
         const int s1 = (j + 1) % ST;
+        TR_T(tv0);
         ok = mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22);
+        TR_T(tv1); TR_ADD(mma_wait_kv, tv0, tv1);
         if (!ok) break;
         bool k_next_ready = false;
         for (int t = 0; t < 2 && ok; t++) {
           if (j >= nkv[t]) continue;
+          TR_T(tp0);
           ok = mbar_wait(&p_full[t], j & 1, abort_flag, status, 0x23);
+          TR_T(tp1); TR_ADD(mma_wait_p, tp0, tp1);
           if (!ok) break;
           tc_fence_after();
+          TR_T(ti0);
           issue_pv(t, s, j > 0);
+          TR_T(ti1); TR_ADD(mma_issue, ti0, ti1);
           if (j + 1 < nkv[t]) {
             if (!k_next_ready) {
+              TR_T(tk0);
               ok = mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24);
+              TR_T(tk1); TR_ADD(mma_wait_kv, tk0, tk1);
               if (!ok) break;
               tc_fence_after();
               k_next_ready = true;
             }
+            TR_T(tq0);
             issue_qk(t, s1);
+            TR_T(tq1); TR_ADD(mma_issue, tq0, tq1);
             tc_commit(&s_full[t]);
           } else {
             tc_commit(&o_full[t]);
@@ -242,6 +387,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_commit(&v_empty[s]);
         if (j + 1 < nkv_max) tc_commit(&k_empty[s1]);
       }
+#ifdef AR_TRACE
+      { TR_T(tm_end); TR_DECL(mma_total); TR_ADD(mma_total, tm_begin, tm_end); TR_FLUSH(5, mma_wait_p); TR_FLUSH(6, mma_wait_kv); TR_FLUSH(7, mma_issue); TR_FLUSH(8, mma_total); }
+#endif
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------ softmax warps
@@ -257,9 +405,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     float qs = 1.f;
     if (MODE == TC_SAGE && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
     float m = NEG, l = 0.f;
+    TR_DECL(sm_wait_s); TR_DECL(sm_ld); TR_DECL(sm_compute); TR_DECL(sm_st); TR_DECL(sm_steps); TR_T(tsm_begin);
     bool ok = true;
     for (int j = 0; j < nkv[t]; j++) {
+      TR_T(ts0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, status, 0x30));
+      TR_T(ts1); TR_ADD(sm_wait_s, ts0, ts1);
       if (!ok) break;
       tc_fence_after();
       uint32_t sv[BN];
@@ -268,113 +419,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 64, sv + 64);
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
+      TR_T(ts2); TR_ADD(sm_ld, ts1, ts2);
       float c = scale_log2;
       if (MODE == TC_SAGE) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
-      float mc;  // row maximum of this tile in the scaled (log2) domain
-      if (edge) {
-        // boundary / diagonal / masked tiles: element-wise path; leaves scaled logits in sv and c = 1
-        const float* mrow = (mask != nullptr && row < N) ? mask + (size_t)row * N : nullptr;
-        float mx = NEG;
-#pragma unroll
-        for (int i = 0; i < BN; i++) {
-          const int col = col0 + i;
-          float x = MODE == TC_SAGE ? (float)(int)sv[i] * c : __uint_as_float(sv[i]) * c;
-          if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
-          if (col >= N || (causal && col > row)) x = NEG;
-          sv[i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
-        c = 1.0f;
-        mc = mx;
-      } else if (MODE == TC_SAGE) {
-        // exact s32 scores: integer maximum first, one conversion for the row; then every element goes
-        // s32 -> f32 through the bits of 1.5 * 2^23 (exact for |x| < 2^22)
-        int m0 = (int)sv[0], m1 = (int)sv[1], m2 = (int)sv[2], m3 = (int)sv[3];
-#pragma unroll
-        for (int i = 4; i < BN; i += 8) {
-          m0 = __vimax3_s32(m0, (int)sv[i], (int)sv[i + 1]);
-          m1 = __vimax3_s32(m1, (int)sv[i + 2], (int)sv[i + 3]);
-          if (i + 4 < BN) {
-            m2 = __vimax3_s32(m2, (int)sv[i + 4], (int)sv[i + 5]);
-            m3 = __vimax3_s32(m3, (int)sv[i + 6], (int)sv[i + 7]);
-          }
-        }
-        mc = (float)max(max(m0, m1), max(m2, m3)) * c;
-      } else {
-        float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]),
-              m3 = __uint_as_float(sv[3]);
-#pragma unroll
-        for (int i = 4; i < BN; i += 8) {
-          m0 = fmax3(m0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-          m1 = fmax3(m1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
-          if (i + 4 < BN) {
-            m2 = fmax3(m2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
-            m3 = fmax3(m3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
-          }
-        }
-        mc = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c;
-      }
-      if (j == 0) {
-        m = fmaxf(m, mc);
-      } else {
-        const bool need = mc > m + RESCALE_THRESHOLD;
-        if (__any_sync(0xffffffffu, need)) {
-          const float m_new = need ? mc : m;
-          const float alpha = ex2f(m - m_new);
-          m = m_new;
-          l *= alpha;
-          const uint64_t alpha2 = pack_f32x2(alpha, alpha);
-#pragma unroll
-          for (int cch = 0; cch < D / 32; cch++) {
-            uint32_t ov[32];
-            tmem_ld32(tO + cch * 32, ov);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float a, b;
-              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), alpha2), a, b);
-              ov[i] = __float_as_uint(a);
-              ov[i + 1] = __float_as_uint(b);
-            }
-            tmem_st32(tO + cch * 32, ov);
-          }
-        }
-      }
-      // p = 2^(x * c - m), two lanes per instruction; the row sum keeps the unrounded values
-      const uint64_t c2 = pack_f32x2(c, c);
-      const uint64_t negm2 = pack_f32x2(-m, -m);
-      const uint64_t magic2 = pack_f32x2(-12582912.0f, -12582912.0f);
-      uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-#pragma unroll
-      for (int qd = 0; qd < 4; qd++) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-          uint64_t x2;
-          if (MODE == TC_SAGE && !edge)
-            x2 = add_f32x2(pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
-                                      __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u)), magic2);
-          else
-            x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i]), __uint_as_float(sv[qd * 32 + 2 * i + 1]));
-          float a, b;
-          unpack_f32x2(fma_f32x2(x2, c2, negm2), a, b);
-          const float p0 = ex2f(a), p1 = ex2f(b);
-          const uint64_t p2 = pack_f32x2(p0, p1);
-          if (i & 1) sum_b = add_f32x2(sum_b, p2); else sum_a = add_f32x2(sum_a, p2);
-          pk[i] = pack_bf16x2(p0, p1);
-        }
-        tmem_st16(tS + qd * 16, pk);
-      }
-      float lsum, lsum_hi;
-      unpack_f32x2(add_f32x2(sum_a, sum_b), lsum, lsum_hi);
-      lsum += lsum_hi;
-      l += lsum;
+      // Two separate instantiations: the interior step must not carry the merge points of the
+      // boundary path (that alone costs it ~300 cycles of scheduling freedom).
+      if (edge)
+        softmax_step<MODE, D, true>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO);
+      else
+        softmax_step<MODE, D, false>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO);
+      TR_T(ts3); TR_ADD(sm_compute, ts2, ts3);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
+      TR_T(ts4); TR_ADD(sm_st, ts3, ts4); TR_ADD(sm_steps, 0, 1);
     }
+#ifdef AR_TRACE
+    if (tid == 0) { TR_T(tsm_end); TR_DECL(sm_total); TR_ADD(sm_total, tsm_begin, tsm_end); TR_FLUSH(0, sm_wait_s); TR_FLUSH(1, sm_ld); TR_FLUSH(2, sm_compute); TR_FLUSH(3, sm_st); TR_FLUSH(4, sm_total); TR_FLUSH(9, sm_steps); }
+#endif
     if (ok && nkv[t] > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], 0, abort_flag, status, 0x31));
       if (ok) {
