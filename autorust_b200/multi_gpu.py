@@ -1,0 +1,170 @@
+"""Head-parallel sharding of the attention path over the GPUs of one box.
+
+Attention over disjoint (batch, head) pairs is independent, so the flattened batch x kv-head axis is
+cut into `world` contiguous ranges (GQA groups stay whole, K/V are never replicated), each rank runs
+the forward on its slab, and the output slabs are all-gathered with NCCL through libar_gather.so
+(include/ar_attn_gather.h).  The reference has no multi-device code (CURRENT_STATE.md:64,469).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+from . import _abi
+
+
+@dataclass(frozen=True)
+class Shard:
+    """Rank `rank`'s contiguous range [kv_begin, kv_end) of the flattened (batch, kv head) axis."""
+    rank: int
+    kv_begin: int
+    kv_end: int
+    group: int  # query heads per kv head
+
+    @property
+    def kv_units(self) -> int:
+        return self.kv_end - self.kv_begin
+
+    @property
+    def q_begin(self) -> int:
+        return self.kv_begin * self.group
+
+    @property
+    def q_end(self) -> int:
+        return self.kv_end * self.group
+
+
+def partition(B: int, Hq: int, Hkv: int, world: int) -> list[Shard]:
+    """Cuts the B*Hkv (batch, kv head) units into `world` contiguous, near-equal ranges (the first
+    `remainder` ranks get one unit more).  With the [B, H, S, D] layout each range is one contiguous slab
+    of Q, K, V and O."""
+    if world <= 0 or B <= 0 or Hkv <= 0 or Hq % Hkv != 0:
+        raise ValueError("partition: bad arguments")
+    units = B * Hkv
+    base, rem = divmod(units, world)
+    shards, start = [], 0
+    for r in range(world):
+        n = base + (1 if r < rem else 0)
+        shards.append(Shard(r, start, start + n, Hq // Hkv))
+        start += n
+    return shards
+
+
+def equal_partition(B: int, Hq: int, Hkv: int, world: int) -> list[Shard]:
+    """Like partition(), but insists on equal slabs, which is what an in-place all-gather needs."""
+    if (B * Hkv) % world != 0:
+        raise ValueError(f"{B * Hkv} (batch, kv head) units do not divide over {world} ranks")
+    return partition(B, Hq, Hkv, world)
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _abi.LIB_DIR / "libar_gather.so"
+    if not path.exists():
+        raise _abi.AttnLibraryError(f"{path} is missing: build it with `python -m autorust_b200.build` (needs NCCL)")
+    L = ctypes.CDLL(str(path))
+    p, ci, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    L.ar_gather_unique_id.argtypes = [p]
+    L.ar_gather_init.argtypes = [p, ci, ci]
+    L.ar_gather_init.restype = p
+    L.ar_gather_allgather.argtypes = [p, p, i64, ci, p]
+    L.ar_gather_allgather_into.argtypes = [p, p, p, i64, ci, p]
+    L.ar_gather_destroy.argtypes = [p]
+    L.ar_gather_destroy.restype = None
+    L.ar_gather_last_error.restype = ctypes.c_char_p
+    _lib = L
+    return L
+
+
+class Gather:
+    """One NCCL communicator over the ranks of a torch.distributed process group (any backend is fine
+    for shipping the 128-byte id; the gather itself goes straight to NCCL)."""
+
+    def __init__(self, rank: int, world: int, device_index: int):
+        import torch
+        import torch.distributed as dist
+        L = load()
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            if L.ar_gather_unique_id(ident) != 0:
+                raise RuntimeError("ar_gather_unique_id: " + L.ar_gather_last_error().decode())
+        box = [bytes(ident.raw)]
+        dist.broadcast_object_list(box, src=0)
+        torch.cuda.set_device(device_index)
+        self._h = L.ar_gather_init(box[0], rank, world)
+        if not self._h:
+            raise RuntimeError("ar_gather_init: " + L.ar_gather_last_error().decode())
+        self.rank, self.world = rank, world
+
+    def allgather_into(self, send, recv, stream=None) -> None:
+        """recv[r] <- rank r's `send` (contiguous CUDA tensors, bf16 or f32), asynchronously on `stream`."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        dt = {torch.float32: _abi.DTYPE_F32, torch.bfloat16: _abi.DTYPE_BF16}[send.dtype]
+        if recv.numel() != send.numel() * self.world or not (send.is_contiguous() and recv.is_contiguous()):
+            raise ValueError("allgather_into: recv must hold world contiguous copies of send")
+        rc = load().ar_gather_allgather_into(self._h, send.data_ptr(), recv.data_ptr(), send.numel(), dt, s.cuda_stream)
+        if rc != 0:
+            raise RuntimeError("ar_gather_allgather_into: " + load().ar_gather_last_error().decode())
+
+    def allgather_in_place(self, full, stream=None) -> None:
+        """`full` holds world equal slabs along dim 0 and this rank's slab is already in place."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        dt = {torch.float32: _abi.DTYPE_F32, torch.bfloat16: _abi.DTYPE_BF16}[full.dtype]
+        if full.numel() % self.world != 0 or not full.is_contiguous():
+            raise ValueError("allgather_in_place: tensor must be contiguous and divide by the world size")
+        rc = load().ar_gather_allgather(self._h, full.data_ptr(), full.numel() // self.world, dt, s.cuda_stream)
+        if rc != 0:
+            raise RuntimeError("ar_gather_allgather: " + load().ar_gather_last_error().decode())
+
+    def close(self) -> None:
+        if self._h:
+            load().ar_gather_destroy(self._h)
+            self._h = None
+
+
+def sharded_forward(mode, q, k, v, shard: Shard, gather: Gather, causal=False, mask=None, chunks: int = 1):
+    """Runs the forward on this rank's slab and all-gathers the outputs.
+
+    q, k, v are this rank's slabs flattened over (batch, head): [units * group, S, D] / [units, S, D]
+    viewed as [1, H_local, S, D].  Returns the gathered output [world, H_local_q, S, D].  With
+    chunks > 1 the slab is cut along the head axis and chunk i is gathered on a side stream while
+    chunk i + 1 computes."""
+    import torch
+    from . import ops
+    hq = q.shape[0]
+    S, D = q.shape[-2:]
+    out = torch.empty_like(q)
+    gathered = torch.empty((gather.world,) + tuple(q.shape), dtype=q.dtype, device=q.device)
+    main = torch.cuda.current_stream()
+    side = torch.cuda.Stream()
+    group = shard.group
+    kv_total = k.shape[0]
+    if chunks < 1 or kv_total % chunks != 0:
+        chunks = 1
+    per = kv_total // chunks
+    if chunks == 1:
+        ops.attn_forward(mode, q.view(1, hq, S, D), k.view(1, kv_total, S, D), v.view(1, kv_total, S, D), mask, causal,
+                         out=out.view(1, hq, S, D))
+        gather.allgather_into(out, gathered, main)
+        return gathered
+    # chunked: gathered is laid out [chunk][world][heads of the chunk] and re-viewed at the end
+    staged = torch.empty((chunks, gather.world, per * group, S, D), dtype=q.dtype, device=q.device)
+    for c in range(chunks):
+        qs = q[c * per * group:(c + 1) * per * group]
+        ks, vs = k[c * per:(c + 1) * per], v[c * per:(c + 1) * per]
+        oc = out[c * per * group:(c + 1) * per * group]
+        ops.attn_forward(mode, qs.view(1, per * group, S, D), ks.view(1, per, S, D), vs.view(1, per, S, D), mask, causal,
+                         out=oc.view(1, per * group, S, D))
+        done = torch.cuda.Event()
+        done.record(main)
+        side.wait_event(done)
+        gather.allgather_into(oc, staged[c], side)
+    main.wait_stream(side)
+    return staged.permute(1, 0, 2, 3, 4).reshape(gather.world, hq, S, D)

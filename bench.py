@@ -9,7 +9,7 @@ S=8192, D=128, non-causal, bf16 q/k/v ~ N(0,1) with a per-(head, channel) offset
 seed 2 -- as seeded synthetic tensors.  One step = the quantise prologue + the attention kernel
 over that batch.  With N > 1 every rank owns one such batch (weak scaling; global batch element
 g = c*N + r lives on rank r) and the bf16 outputs are all-gathered over NCCL, chunk by chunk on a
-side stream while the next chunk computes.
+side stream while the next chunk computes (libar_gather.so, include/ar_attn_gather.h).
 
 Prints ONE JSON line (rank 0).  `value` is device-resident throughput (inputs already in HBM);
 `e2e` goes through the host-facing call with pinned host buffers, H2D and D2H copies inside the
@@ -127,7 +127,7 @@ def cpu_baseline_leg(budget_s: float = 12.0) -> dict:
     q, k, v = cpu_inputs(1)
     cpu_step(q, k, v)  # warm-up (page faults, thread pool)
     dt, threads = cpu_step(q, k, v)
-    nheads = max(1, min(16, int(budget_s / max(dt, 1e-3))))
+    nheads = max(1, min(w["B"] * w["H"], int(budget_s / max(dt, 1e-3))))
     q, k, v = cpu_inputs(nheads)
     dt, threads = cpu_step(q, k, v)
     ops = work_ops(1, nheads, w["S"], w["D"], w["causal"])
@@ -228,6 +228,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     stream = torch.cuda.current_stream()
     comm_stream = torch.cuda.Stream() if world > 1 else None
     gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device) if world > 1 else None
+    gather = None
+    if world > 1:
+        from autorust_b200 import multi_gpu
+        gather = multi_gpu.Gather(rank, world, local_rank)  # NCCL communicator of libar_gather.so
     kernel_events: list = []
 
     def quantise(b0, b1):
@@ -263,8 +267,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             done = torch.cuda.Event()
             done.record(stream)
             comm_stream.wait_event(done)
-            with torch.cuda.stream(comm_stream):
-                dist.all_gather_into_tensor(gathered[c], out[c])
+            gather.allgather_into(out[c], gathered[c], comm_stream)
         stream.wait_stream(comm_stream)
 
     def barrier():

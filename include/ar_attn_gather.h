@@ -1,0 +1,51 @@
+/*
+ * ar_attn_gather.h -- C ABI of libar_gather.so: the one cross-GPU step of the attention path.
+ *
+ * Attention over disjoint (batch, head) pairs needs no reduction, so a multi-GPU run shards the
+ * flattened batch x head axis, every rank runs ar_attn_forward on its slab, and the output slabs are
+ * all-gathered over NVLink with NCCL.  autorust itself is single-device (its port skips multi-device
+ * ops, CURRENT_STATE.md:64,469; `CUDA:N` only selects an ordinal, src/runtime/ops_cuda.rs:1162-1169),
+ * so these entry points have no counterpart in the reference; they live in a library of their own so
+ * that single-GPU users never load NCCL.
+ *
+ * One process per GPU.  Rank 0 calls ar_gather_unique_id and ships the 128 bytes to the other ranks by
+ * any host channel; every rank then calls ar_gather_init with its device current.
+ */
+#ifndef AR_ATTN_GATHER_H
+#define AR_ATTN_GATHER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AR_GATHER_ID_BYTES 128
+
+/* Fills id[AR_GATHER_ID_BYTES] with a fresh NCCL unique id.  0 on success. */
+int ar_gather_unique_id(void* id);
+
+/* Creates this rank's communicator (blocking until all `world` ranks have called it).
+ * Returns an opaque handle, or NULL on failure. */
+void* ar_gather_init(const void* id, int rank, int world);
+
+/* In-place all-gather of the output slabs: `o_full` holds world * elems_per_rank elements of `dtype`
+ * (AR_DTYPE_F32 = 0, AR_DTYPE_BF16 = 1) and this rank's slab is already at offset rank * elems_per_rank.
+ * Asynchronous on `cu_stream`.  0 on success, negative on failure. */
+int ar_gather_allgather(void* comm, void* o_full, int64_t elems_per_rank, int dtype, void* cu_stream);
+
+/* Out-of-place variant: gathers `send` (elems_per_rank elements) of every rank into `recv`. */
+int ar_gather_allgather_into(void* comm, const void* send, void* recv, int64_t elems_per_rank, int dtype,
+                             void* cu_stream);
+
+/* Destroys the communicator. */
+void ar_gather_destroy(void* comm);
+
+/* Last NCCL error text of this thread ("" when none). */
+const char* ar_gather_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AR_ATTN_GATHER_H */

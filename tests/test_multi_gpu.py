@@ -1,0 +1,141 @@
+"""Head-parallel sharding: partition arithmetic, the N > 1 path on CPU ranks (gloo, world_size 2), a rank
+that never joins (host-side failure, no GPU involved), and -- on a box with two GPUs -- the NCCL gather
+against the single-GPU result."""
+from __future__ import annotations
+
+import datetime
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from autorust_b200 import multi_gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_partition_is_contiguous_and_respects_gqa_groups():
+    shards = multi_gpu.partition(B=16, Hq=64, Hkv=64, world=8)
+    assert [s.kv_units for s in shards] == [128] * 8
+    assert shards[0].kv_begin == 0 and shards[-1].kv_end == 16 * 64
+    for a, b in zip(shards, shards[1:]):
+        assert a.kv_end == b.kv_begin
+    gqa = multi_gpu.partition(B=2, Hq=8, Hkv=2, world=4)
+    assert [s.kv_units for s in gqa] == [1, 1, 1, 1] and [s.q_begin for s in gqa] == [0, 4, 8, 12]
+    ragged = multi_gpu.partition(B=1, Hq=6, Hkv=6, world=4)
+    assert [s.kv_units for s in ragged] == [2, 2, 1, 1]
+    with pytest.raises(ValueError):
+        multi_gpu.equal_partition(B=1, Hq=6, Hkv=6, world=4)
+    with pytest.raises(ValueError):
+        multi_gpu.partition(B=1, Hq=6, Hkv=4, world=2)
+
+
+def _cpu_rank(rank, world, port, q, k, v, causal, result):
+    """One CPU rank: its slab through the oracle (standing in for the GPU kernel), outputs gathered with gloo."""
+    import torch
+    import torch.distributed as dist
+    import oracle
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=60))
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    sh = multi_gpu.equal_partition(B, Hq, Hkv, world)[rank]
+    qf, kf, vf = q.reshape(B * Hq, S, D), k.reshape(B * Hkv, S, D), v.reshape(B * Hkv, S, D)
+    out = oracle.flash(0, qf[sh.q_begin:sh.q_end][None], kf[sh.kv_begin:sh.kv_end][None], vf[sh.kv_begin:sh.kv_end][None],
+                       None, causal)[0]
+    mine = torch.from_numpy(np.ascontiguousarray(out))
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    if rank == 0:
+        result.put(torch.cat(parts, dim=0).numpy().reshape(B, Hq, S, D))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("Hq,Hkv,causal", [(4, 4, False), (8, 2, True)])
+def test_sharded_run_on_two_cpu_ranks_equals_unsharded(oracle_lib, Hq, Hkv, causal):
+    import torch.multiprocessing as mp
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((2, Hq, 40, 64), dtype=np.float32)
+    k = rng.standard_normal((2, Hkv, 40, 64), dtype=np.float32)
+    v = rng.standard_normal((2, Hkv, 40, 64), dtype=np.float32)
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_rank, args=(r, 2, port, q, k, v, causal, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = result.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    want = oracle_lib.flash(0, q, k, v, None, causal)
+    assert np.array_equal(got, want), "sharding must not change any arithmetic"
+
+
+def test_rank_that_never_joins_times_out_on_the_host():
+    import torch.distributed as dist
+    port = _free_port()
+    with pytest.raises(Exception) as err:
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=2,
+                                timeout=datetime.timedelta(seconds=3))
+    assert "imeout" in str(err.value) or "timed out" in str(err.value).lower() or err.type.__name__.endswith("Error")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def _gpu_rank(rank, world, port, seed, result):
+    import torch
+    import torch.distributed as dist
+    from autorust_b200 import ops
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=120))
+    B, H, S, D = 2, 8, 700, 128
+    g = torch.Generator(device="cuda").manual_seed(seed)  # same seed on every rank: same global tensors
+    q, k, v = (torch.randn(B * H, S, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    sh = multi_gpu.equal_partition(B, H, H, world)[rank]
+    gather = multi_gpu.Gather(rank, world, rank)
+    got = {}
+    for mode in ("bf16", "sage"):
+        for chunks in (1, 2):
+            full = multi_gpu.sharded_forward(mode, q[sh.q_begin:sh.q_end].contiguous(), k[sh.kv_begin:sh.kv_end].contiguous(),
+                                             v[sh.kv_begin:sh.kv_end].contiguous(), sh, gather, causal=True, chunks=chunks)
+            torch.cuda.synchronize()
+            got[(mode, chunks)] = full.reshape(B * H, S, D)
+    if rank == 0:
+        ok = True
+        for mode in ("bf16", "sage"):
+            ref = ops.attn_forward(mode, q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
+            torch.cuda.synchronize()
+            for chunks in (1, 2):
+                ok = ok and torch.equal(got[(mode, chunks)].view(torch.int16), ref.reshape(B * H, S, D).view(torch.int16))
+        result.put(bool(ok))
+    dist.barrier()
+    gather.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_gather_is_bit_identical_to_single_gpu(attn_lib):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_rank, args=(r, 2, port, 7, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ok = result.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert ok
