@@ -61,6 +61,20 @@ bool make_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// General form: a [dim2, dim1, dim0] tensor with dim0 contiguous; boxes of box1 x box0 elements.
+bool make_map_ex(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t dim0, int64_t dim1, int64_t dim2,
+                 int box0, int box1) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)dim0, (cuuint64_t)dim1, (cuuint64_t)dim2};
+  cuuint64_t strides[2] = {(cuuint64_t)dim0 * esize, (cuuint64_t)dim0 * esize * (cuuint64_t)dim1};
+  cuuint32_t box[3] = {(cuuint32_t)box0, (cuuint32_t)box1, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
@@ -94,7 +108,7 @@ bool mode_has_kernel(int mode, int dtype, int64_t B, int64_t Hq, int64_t S, int6
   if (B * Hq > 65535 || S > (1 << 24)) return false;  // grid.y / 32-bit index limits of the kernels
   switch (mode) {
     case AR_MODE_EXACT_F32: return dtype == AR_DTYPE_F32 && (D == 64 || D == 128);
-    case AR_MODE_TF32: return false;
+    case AR_MODE_TF32: return dtype == AR_DTYPE_F32 && ar::attn_tc_has(ar::TC_TF32, (int)D);
     case AR_MODE_BF16: return dtype == AR_DTYPE_BF16 && ar::attn_tc_has(ar::TC_BF16, (int)D);
     case AR_MODE_SAGE_INT8: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE, (int)D);
     default: return false;
@@ -134,6 +148,8 @@ int ar_attn_supported(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, i
 size_t ar_attn_workspace_bytes(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
   if (check_shape(B, Hq, Hkv, S, D) != AR_OK) return 0;
   if (mode == AR_MODE_SAGE_INT8) return sage_layout(dtype, B, Hq, Hkv, S, D).total;
+  if (mode == AR_MODE_TF32)  // status block + the transposed copy of V, rows padded to a multiple of 4 keys
+    return STATUS_BYTES + align_up(sizeof(float) * (size_t)(B * Hkv * D) * (size_t)((S + 3) / 4 * 4), 256);
   return 0;
 }
 
@@ -194,6 +210,18 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hq, S, D) ||
         !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D) ||
         !make_map(&a.tm_v, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+      return AR_ERR_CUDA;
+  } else if (mode == AR_MODE_TF32) {
+    const int64_t S_pad = (S + 3) / 4 * 4;
+    float* vt = (float*)((uint8_t*)workspace + STATUS_BYTES);
+    if (ar::launch_transpose_v((const float*)v, vt, (int)(B * Hkv), (int)S, (int)S_pad, (int)D, stream) != cudaSuccess)
+      return AR_ERR_CUDA;
+    g_launches++;
+    a.mode = ar::TC_TF32;
+    a.out_f32 = 1;
+    if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B * Hq, S, D) ||
+        !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B * Hkv, S, D) ||
+        !make_map_ex(&a.tm_v, vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, S_pad, D, B * Hkv, 32, (int)D))
       return AR_ERR_CUDA;
   } else {  // AR_MODE_SAGE_INT8
     const SageLayout L = sage_layout(dtype, B, Hq, Hkv, S, D);

@@ -7,14 +7,14 @@
 namespace ar {
 
 // Tensor-core forward (attn_fwd_tc.cu): bf16 or Sage INT8 QK^T, bf16 PV.
-enum TcMode { TC_BF16 = 0, TC_SAGE = 1 };
+enum TcMode { TC_BF16 = 0, TC_SAGE = 1, TC_TF32 = 2 };
 
 struct TcArgs {
   int mode;             // TcMode
   int D;                // 64 or 128
   CUtensorMap tm_q;     // [B*Hq, S, D]   bf16 (TC_BF16) or int8 (TC_SAGE), 128-byte swizzle, box 128 rows
   CUtensorMap tm_k;     // [B*Hkv, S, D]  same element type as tm_q
-  CUtensorMap tm_v;     // [B*Hkv, S, D]  bf16
+  CUtensorMap tm_v;     // [B*Hkv, S, D]  bf16; TC_TF32: the transposed copy [B*Hkv, D, S_pad] f32, box 32 keys x D rows
   void* out;            // [B*Hq, S, D]   bf16 or f32
   int out_f32;
   const float* mask;    // [S, S] additive or null
@@ -48,6 +48,9 @@ struct PrologueArgs {
 };
 // Returns the number of kernels launched through *launches.
 cudaError_t launch_sage_prologue(const PrologueArgs& a, cudaStream_t stream, int* launches);
+// [BH, S, D] f32 -> [BH, D, S_pad] f32 (S_pad = S rounded up to 4; the padding is zeroed): the K-major V
+// operand of the TF32 kernel.
+cudaError_t launch_transpose_v(const float* v, float* vt, int BH, int S, int S_pad, int D, cudaStream_t stream);
 // f32 -> bf16 copy of V for Sage with f32 tensors.
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream);
 

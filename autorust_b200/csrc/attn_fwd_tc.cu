@@ -1,8 +1,8 @@
 // Fused attention forward on the sm_100a tensor cores.
 //
-// Replaces autorust's `ar_flash_bf16` (src/runtime/cuda_flash_bf16.rs:98-428) and
-// `ar_flash_sage` (src/runtime/cuda_flash_sage.rs:86-415) -- mma.sync kernels with a 64x32
-// tile -- by one warp-specialised kernel:
+// Replaces autorust's `ar_flash_bf16` (src/runtime/cuda_flash_bf16.rs:98-428), `ar_flash_tc_f32`
+// (src/runtime/cuda_flash_tc.rs:92-376) and `ar_flash_sage` (src/runtime/cuda_flash_sage.rs:86-415)
+// -- mma.sync kernels with a 64x32 tile -- by one warp-specialised kernel:
 //
 //   CTA = 2 query tiles of 128 rows of one (batch, head) pair, 384 threads:
 //     warps 0-3   softmax for query tile 0   (thread r owns row r = TMEM lane r)
@@ -150,7 +150,7 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
   uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
   for (int qd = 0; qd < 4; qd++) {
-    uint32_t pk[16];
+    uint32_t pk[MODE == TC_TF32 ? 32 : 16];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
       uint64_t x2;
@@ -166,9 +166,17 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
       const float p0 = ex2f(a), p1 = ex2f(b);
       const uint64_t p2 = pack_f32x2(p0, p1);
       if (i & 1) sum_b = add_f32x2(sum_b, p2); else sum_a = add_f32x2(sum_a, p2);
-      pk[i] = pack_bf16x2(p0, p1);
+      if constexpr (MODE == TC_TF32) {  // P stays f32 in TMEM; the MMA reads its tf32 part
+        pk[2 * i] = __float_as_uint(p0);
+        pk[2 * i + 1] = __float_as_uint(p1);
+      } else {
+        pk[i] = pack_bf16x2(p0, p1);
+      }
     }
-    tmem_st16(tS + qd * 16, pk);
+    if constexpr (MODE == TC_TF32)
+      tmem_st32(tS + qd * 32, pk);
+    else
+      tmem_st16(tS + qd * 16, pk);
   }
   float lsum, lsum_hi;
   unpack_f32x2(add_f32x2(sum_a, sum_b), lsum, lsum_hi);
@@ -177,22 +185,33 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
 
 template <int MODE, int D>
 struct Cfg {
-  static constexpr int QK_ESIZE = MODE == TC_SAGE ? 1 : 2;
+  static constexpr int QK_ESIZE = MODE == TC_SAGE ? 1 : MODE == TC_TF32 ? 4 : 2;
   static constexpr int QK_ROW_BYTES = D * QK_ESIZE;
   static_assert(QK_ROW_BYTES % 128 == 0, "Q/K rows must fill whole 128-byte swizzle atoms");
   static constexpr int QK_BOXES = QK_ROW_BYTES / 128;
   static constexpr int QK_BOX_ELEMS = 128 / QK_ESIZE;
   static constexpr int QK_TILE_BYTES = BM * QK_ROW_BYTES;
   static constexpr int QK_KSTEPS = QK_ROW_BYTES / 32;  // one MMA consumes 32 bytes of K extent
-  static constexpr int V_BOXES = D * 2 / 128;
-  static constexpr int V_TILE_BYTES = BN * D * 2;
-  static constexpr int PV_KSTEPS = BN / 16;
+  // V operand of the PV MMA.  bf16: the row-major [keys, D] tile itself, consumed MN-major (boxes of 64
+  // d-columns).  TF32: tcgen05 has no MN-major tf32 operand, so the tile comes from a transposed copy
+  // [D, keys] and is consumed K-major (boxes of 32 keys).
+  static constexpr int V_ESIZE = MODE == TC_TF32 ? 4 : 2;
+  static constexpr int V_BOXES = MODE == TC_TF32 ? BN * 4 / 128 : D * 2 / 128;
+  static constexpr int V_BOX_BYTES = MODE == TC_TF32 ? D * 128 : BN * 128;
+  static constexpr int V_TILE_BYTES = BN * D * V_ESIZE;
+  static constexpr int PV_KSTEPS = MODE == TC_TF32 ? BN / 8 : BN / 16;
+  static constexpr int P_COLS = MODE == TC_TF32 ? BN : BN / 2;  // TMEM columns of P
   static constexpr int STAGES = (2 * QK_TILE_BYTES + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2;
   static constexpr int SMEM_TILES = 2 * QK_TILE_BYTES + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
   static constexpr int NUM_BARS = 2 + 4 * STAGES + 6;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
-  static constexpr uint32_t IDESC_QK = MODE == TC_SAGE ? make_idesc(2, 1, 1, 0, 0, BM, BN) : make_idesc(1, 1, 1, 0, 0, BM, BN);
-  static constexpr uint32_t IDESC_PV = make_idesc(1, 1, 1, 0, 1, BM, D);
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
+  static constexpr int PV_KIND = MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
+  static constexpr uint32_t IDESC_QK = MODE == TC_SAGE   ? make_idesc(2, 1, 1, 0, 0, BM, BN)
+                                       : MODE == TC_TF32 ? make_idesc(1, 2, 2, 0, 0, BM, BN)
+                                                         : make_idesc(1, 1, 1, 0, 0, BM, BN);
+  static constexpr uint32_t IDESC_PV = MODE == TC_TF32 ? make_idesc(1, 2, 2, 0, 0, BM, D) : make_idesc(1, 1, 1, 0, 1, BM, D);
 };
 
 template <int MODE, int D>
@@ -291,8 +310,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                       kvbh);
         if (n > 0 && !mbar_wait(&v_empty[s], (n - 1) & 1, abort_flag, status, 0x11)) break;
         mbar_arrive_expect_tx(&v_full[s], C::V_TILE_BYTES);
-        for (int bx = 0; bx < C::V_BOXES; bx++)
-          tma_load_3d(sV + s * C::V_TILE_BYTES + bx * (BN * 128), &tm_v, &v_full[s], bx * 64, j * BN, kvbh);
+        for (int bx = 0; bx < C::V_BOXES; bx++) {
+          if constexpr (MODE == TC_TF32)  // transposed V: x = key, y = d
+            tma_load_3d(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], j * BN + bx * 32, 0, kvbh);
+          else
+            tma_load_3d(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], bx * 64, j * BN, kvbh);
+        }
         issued = j + 1;
       }
       if (*abort_flag) {
@@ -325,7 +348,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int s = 0; s < C::QK_KSTEPS; s++) {
           const uint32_t off = ((s >> 2) * (BM * 128) + (s & 3) * 32) >> 4;
-          mma_ss_lohi<MODE == TC_SAGE ? KIND_I8 : KIND_F16>(d, qa + off, qk_hi, ka + off, qk_hi, C::IDESC_QK, s > 0);
+          mma_ss_lohi<C::QK_KIND>(d, qa + off, qk_hi, ka + off, qk_hi, C::IDESC_QK, s > 0);
         }
       };
       auto issue_pv = [&](int t, int vs, bool acc) {
@@ -333,8 +356,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint32_t a = tb + t * 128;
         const uint32_t va = v_lo0 + vs * (C::V_TILE_BYTES >> 4);
 #pragma unroll
-        for (int s = 0; s < C::PV_KSTEPS; s++)
-          mma_ts_lohi<KIND_F16>(d, a + s * 8, va + s * (2048 >> 4), v_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
+        for (int s = 0; s < C::PV_KSTEPS; s++) {
+          if constexpr (MODE == TC_TF32)  // K-major V^T: 8 keys = 32 bytes per step, 4 steps per 128-byte box
+            mma_ts_lohi<KIND_TF32>(d, a + s * 8, (qk_lo | (va & 0x3fffu)) + (((s >> 2) * C::V_BOX_BYTES + (s & 3) * 32) >> 4),
+                                   qk_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
+          else
+            mma_ts_lohi<KIND_F16>(d, a + s * 8, va + s * (2048 >> 4), v_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
+        }
       };
       TR_DECL(mma_wait_kv); TR_DECL(mma_wait_p); TR_DECL(mma_issue); TR_T(tm_begin);
       bool ok = true;
@@ -504,6 +532,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
 bool attn_tc_has(int mode, int D) {
   if (mode == TC_BF16) return D == 64 || D == 128;
   if (mode == TC_SAGE) return D == 128;
+  if (mode == TC_TF32) return D == 64;  // the reference's only head size; two f32 query tiles of D=128 do not fit
   return false;
 }
 
@@ -511,6 +540,7 @@ cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
   if (a.mode == TC_BF16 && a.D == 128) return launch_one<TC_BF16, 128>(a, stream);
   if (a.mode == TC_BF16 && a.D == 64) return launch_one<TC_BF16, 64>(a, stream);
   if (a.mode == TC_SAGE && a.D == 128) return launch_one<TC_SAGE, 128>(a, stream);
+  if (a.mode == TC_TF32 && a.D == 64) return launch_one<TC_TF32, 64>(a, stream);
   return cudaErrorInvalidValue;
 }
 

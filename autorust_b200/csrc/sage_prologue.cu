@@ -173,6 +173,24 @@ __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restric
   }
 }
 
+// vt[bh][d][s] = v[bh][s][d] through a 32x33 shared tile; columns S..S_pad-1 are written as zero so that
+// a masked key (p = 0) can never meet a NaN left in the scratch.
+__global__ void __launch_bounds__(256) transpose_v_kernel(const float* __restrict__ v, float* __restrict__ vt, int S,
+                                                          int S_pad, int D) {
+  __shared__ float tile[32][33];
+  const int bh = blockIdx.z;
+  const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const float* src = v + (size_t)bh * S * D;
+  float* dst = vt + (size_t)bh * D * S_pad;
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) tile[r][tx] = (s0 + r < S) ? src[(size_t)(s0 + r) * D + d0 + tx] : 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 32; r += 8)
+    if (s0 + tx < S_pad) dst[(size_t)(d0 + r) * S_pad + s0 + tx] = tile[tx][r];
+}
+
 template <int DTYPE, int D>
 cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* launches) {
   const int nblk = (a.S + 127) / 128;
@@ -201,6 +219,12 @@ cudaError_t launch_sage_prologue(const PrologueArgs& a, cudaStream_t stream, int
   if (a.dtype == 0 && a.D == 128) return launch_prologue_t<0, 128>(a, stream, launches);
   if (a.dtype == 0 && a.D == 64) return launch_prologue_t<0, 64>(a, stream, launches);
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_transpose_v(const float* v, float* vt, int BH, int S, int S_pad, int D, cudaStream_t stream) {
+  dim3 grid((S_pad + 31) / 32, D / 32, BH);
+  transpose_v_kernel<<<grid, 256, 0, stream>>>(v, vt, S, S_pad, D);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream) {

@@ -14,7 +14,7 @@ from . import ops
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="sage", choices=["exact", "bf16", "sage"])
+    ap.add_argument("--mode", default="sage", choices=["exact", "tf32", "bf16", "sage"])
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--Hkv", type=int, default=0)
@@ -25,7 +25,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=1)
     a = ap.parse_args()
     hkv = a.Hkv or a.H
-    dtype = torch.float32 if a.mode == "exact" else torch.bfloat16
+    dtype = torch.float32 if a.mode in ("exact", "tf32") else torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(2)
     q = torch.randn(a.B, a.H, a.S, a.D, device="cuda", generator=g).to(dtype)
     k = (torch.randn(a.B, hkv, a.S, a.D, device="cuda", generator=g) +

@@ -44,6 +44,7 @@ def test_workspace_bytes_arithmetic(attn_lib):
     wb = attn_lib.ar_attn_workspace_bytes
     assert wb(_abi.MODE_BF16, _abi.DTYPE_BF16, 8, 32, 32, 4096, 128) == 0
     assert wb(_abi.MODE_EXACT_F32, _abi.DTYPE_F32, 1, 12, 12, 197, 64) == 0
+    assert wb(_abi.MODE_TF32, _abi.DTYPE_F32, 1, 12, 12, 197, 64) == 256 + 12 * 64 * 200 * 4  # V^T, 197 -> 200 keys
     B, H, S, D = 4, 32, 8192, 128
     n = wb(_abi.MODE_SAGE_INT8, _abi.DTYPE_BF16, B, H, H, S, D)
     payload = 2 * B * H * S * D + 2 * 4 * B * H * (S // 128) + 4 * B * H * D

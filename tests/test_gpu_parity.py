@@ -83,6 +83,37 @@ def test_exact_f32_config1_vit_shape(ops, oracle_lib):
     assert rel_close(got, oracle_lib.sdpa_f32(q, k, v), 1e-5)
 
 
+# ----------------------------------------------------------------------------------- TF32 mode
+@pytest.mark.parametrize("n", N_LIST)
+def test_tf32_ragged_lengths(ops, oracle_lib, n):
+    q, k, v = sawtooth_qkv(1, 2, 2, n, 64)
+    got = run_f32(ops, "tf32", q, k, v)
+    assert max_abs(got, oracle_lib.flash(0, q, k, v)) < 5e-3  # tests/flash_cuda_tc.rs:159
+    assert max_abs(got, oracle_lib.flash(1, q, k, v)) < 5e-3  # and against the TF32 rounding model
+    qn, kn, vn = normal_qkv(n, 1, 2, 2, n, 64)
+    got = run_f32(ops, "tf32", qn, kn, vn)
+    exact = oracle_lib.flash(0, qn, kn, vn)
+    assert max_abs(got, exact) <= 2e-2 and cosine(got, exact) >= 0.999
+
+
+@pytest.mark.parametrize("label,b,hq,hkv,n,causal,has_mask", MASK_CASES, ids=[c[0] for c in MASK_CASES])
+def test_tf32_masks_causal_gqa(ops, oracle_lib, label, b, hq, hkv, n, causal, has_mask):
+    q, k, v = sawtooth_qkv(b, hq, hkv, n, 64)
+    mask = sawtooth_mask(n) if has_mask else None
+    got = run_f32(ops, "tf32", q, k, v, mask, causal)
+    assert max_abs(got, oracle_lib.flash(0, q, k, v, mask, causal)) < 2e-4  # tests/flash_cuda_masks.rs:289
+
+
+def test_tf32_multi_tile_and_head_dim_gate(ops, oracle_lib):
+    import torch
+    q, k, v = normal_qkv(21, 2, 4, 2, 1000, 64)
+    got = run_f32(ops, "tf32", q, k, v, None, True)
+    exact = oracle_lib.flash(0, q, k, v, None, True)
+    assert max_abs(got, exact) <= 2e-2 and cosine(got, exact) >= 0.999
+    x = torch.zeros(1, 2, 128, 128, device="cuda")
+    assert not ops.supported("tf32", x, x)  # D = 128: the dispatcher takes the exact kernel instead
+
+
 # ----------------------------------------------------------------------------------- bf16 mode
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("n", N_LIST)

@@ -72,6 +72,9 @@ def test_f32_kernels_agree(ref, oracle_lib, attn_lib, n):
     tc = run_ref(ref, "ar_flash_tc_f32", tq, tk, tv, None, False).cpu().numpy()
     assert max_abs(tc, oracle_lib.flash(1, q, k, v)) < 5e-4  # the TF32 rounding model
     assert max_abs(tc, model) < 5e-3  # tests/flash_cuda_tc.rs:159
+    ours_tc = ops.attn_forward("tf32", tq, tk, tv)
+    torch.cuda.synchronize()
+    assert max_abs(ours_tc.cpu().numpy(), tc) < 5e-3
 
 
 @pytest.mark.parametrize("n", N_LIST)

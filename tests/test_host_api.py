@@ -112,6 +112,7 @@ def test_mask_causal_gqa_through_the_operator_api(host, oracle_lib):
     v = sawtooth(b * hkv * n * d, 19).reshape(b, hkv, n, d)
     mask = sawtooth_mask(n)
     out = _t(host, q).attention_with(_t(host, k), _t(host, v), _t(host, mask), 0.0, True, sess).to_list()
+    assert sess.kernel_names() == ["ar_flash_tc_f32"]  # f32 tensors, tensor cores on, D = 64: the TF32 kernel
     assert max_abs(out, oracle_lib.flash(0, q, k, v, mask, True)) < 2e-4
 
 
