@@ -1,0 +1,124 @@
+"""ViT-B/16 inference around the fused attention operator: the caller of the hot path.
+
+Mirrors autorust's `ViT::forward_with` (src/models/vit.rs:118-158) and
+`TransformerBlock::forward_mask_with` / `attn_mask_with` (src/models/transformer.rs:195-312):
+patch embedding (16x16 conv, stride 16) -> [cls | patches] + position embedding -> 12 pre-norm blocks
+(LayerNorm eps 1e-5 -> separate q/k/v projections -> fused attention at S=197, D=64 -> output
+projection -> residual -> LayerNorm -> MLP 3072 with the tanh GELU of src/tensor/nn.rs:1377-1395 ->
+residual) -> LayerNorm of the cls token -> classifier head.
+
+As in the reference, the projections stay library GEMMs (torch / cuBLAS, bf16) and only the attention
+goes to the hand-written kernel; torch supplies memory, GEMMs, LayerNorm and GELU -- it is the harness
+around the operator, not the product.  Weights are random (seeded); no checkpoint is involved.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+
+
+class ViT:
+    def __init__(self, layers=12, embed_dim=768, num_heads=12, in_channels=3, img_size=224, patch_size=16,
+                 num_classes=1000, seed=3, device="cuda", dtype=torch.bfloat16):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.layers, self.embed_dim, self.num_heads, self.patch = layers, embed_dim, num_heads, patch_size
+        self.dtype, self.device = dtype, torch.device(device)
+        n_patches = (img_size // patch_size) ** 2
+
+        def uniform(*shape, fan_in=None):
+            # scaled uniform as the reference's Linear init (src/models/transformer.rs:112-137): U(-1,1)/sqrt(fan_in)
+            bound = 1.0 / math.sqrt(fan_in if fan_in else shape[-1])
+            return ((torch.rand(shape, generator=g) * 2 - 1) * bound).to(self.device, dtype)
+
+        def zeros(*shape):
+            return torch.zeros(shape, device=self.device, dtype=dtype)
+
+        def ones(*shape):
+            return torch.ones(shape, device=self.device, dtype=dtype)
+
+        e = embed_dim
+        self.embed_w = uniform(e, in_channels, patch_size, patch_size, fan_in=in_channels * patch_size * patch_size)
+        self.embed_b = zeros(e)
+        self.cls = ones(1, 1, e)
+        self.pos = uniform(1, n_patches + 1, e, fan_in=e)
+        self.blocks = []
+        for _ in range(layers):
+            self.blocks.append({
+                "ln1": (ones(e), zeros(e)), "ln2": (ones(e), zeros(e)),
+                "q": (uniform(e, e), zeros(e)), "k": (uniform(e, e), zeros(e)), "v": (uniform(e, e), zeros(e)),
+                "o": (uniform(e, e), zeros(e)),
+                "ff1": (uniform(4 * e, e), zeros(4 * e)), "ff2": (uniform(e, 4 * e), zeros(e)),
+            })
+        self.norm = (ones(e), zeros(e))
+        self.head = (uniform(num_classes, e), zeros(num_classes))
+
+    # -- pieces --------------------------------------------------------------------------------
+    def _attention(self, q, k, v, attention):
+        """q, k, v: [B, H, S, D] contiguous.  attention = "fused" (our kernel; bf16 or exact by dtype),
+        "sage", or "torch" (F.scaled_dot_product_attention, the harness's own comparison point)."""
+        if attention == "torch":
+            return F.scaled_dot_product_attention(q, k, v)
+        if attention == "sage":
+            return ops.attn_forward("sage", q, k, v)
+        mode = "bf16" if q.dtype == torch.bfloat16 else "exact"
+        return ops.attn_forward(mode, q, k, v)
+
+    def _block(self, x, blk, attention):
+        B, S, E = x.shape
+        H, D = self.num_heads, E // self.num_heads
+        n1 = F.layer_norm(x, (E,), blk["ln1"][0], blk["ln1"][1], 1e-5)
+        # projections first (plain GEMMs), then the transposed views are materialised for the kernel
+        # (src/models/transformer.rs:277-285, 260-262)
+        q = F.linear(n1, *blk["q"]).view(B, S, H, D).transpose(1, 2).contiguous()
+        k = F.linear(n1, *blk["k"]).view(B, S, H, D).transpose(1, 2).contiguous()
+        v = F.linear(n1, *blk["v"]).view(B, S, H, D).transpose(1, 2).contiguous()
+        a = self._attention(q, k, v, attention).transpose(1, 2).reshape(B, S, E)
+        x = x + F.linear(a, *blk["o"])
+        n2 = F.layer_norm(x, (E,), blk["ln2"][0], blk["ln2"][1], 1e-5)
+        h = F.gelu(F.linear(n2, *blk["ff1"]), approximate="tanh")
+        return x + F.linear(h, *blk["ff2"])
+
+    def forward(self, images: torch.Tensor, attention: str = "fused") -> torch.Tensor:
+        """images [B, 3, 224, 224] -> logits [B, num_classes]."""
+        x = F.conv2d(images.to(self.dtype), self.embed_w, self.embed_b, stride=self.patch)
+        x = x.flatten(2).transpose(1, 2)  # [B, 196, E]
+        x = torch.cat([self.cls.expand(x.shape[0], -1, -1), x], dim=1) + self.pos
+        for blk in self.blocks:
+            x = self._block(x, blk, attention)
+        cls_tok = F.layer_norm(x[:, 0], (self.embed_dim,), self.norm[0], self.norm[1], 1e-5)
+        return F.linear(cls_tok, *self.head)
+
+    def to_float(self) -> "ViT":
+        """An f32 copy of the same weights (for the numerics check)."""
+        other = ViT.__new__(ViT)
+        other.__dict__.update(self.__dict__)
+        other.dtype = torch.float32
+        conv = lambda t: t.float()
+        other.embed_w, other.embed_b, other.cls, other.pos = map(conv, (self.embed_w, self.embed_b, self.cls, self.pos))
+        other.blocks = [{k: (conv(w), conv(b)) for k, (w, b) in blk.items()} for blk in self.blocks]
+        other.norm = tuple(map(conv, self.norm))
+        other.head = tuple(map(conv, self.head))
+        return other
+
+
+def images_per_second(batch=64, iters=10, warmup=3, attention="fused", seed=3) -> dict:
+    """BASELINE config 4: ViT-B/16, batch 64, 224x224x3 inputs ~ U(0,1) (seed 3), bf16 GEMMs."""
+    model = ViT(seed=seed)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.rand(batch, 3, 224, 224, device="cuda", generator=g)
+    for _ in range(warmup):
+        model.forward(x, attention)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        model.forward(x, attention)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {"img_per_s": batch / (ms * 1e-3), "ms_per_batch": ms, "batch": batch, "attention": attention,
+            "model": "ViT-B/16 random-init, bf16 GEMMs (cuBLAS via torch), attention S=197 D=64"}

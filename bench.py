@@ -341,6 +341,11 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg()
+    # the other half of BASELINE's metric: ViT-B/16 images/s around the operator (config 4), rank 0 at N=1 only
+    vit_line = None
+    if rank == 0 and world == 1 and not args.no_vit:
+        from autorust_b200 import vit
+        vit_line = vit.images_per_second(batch=64, iters=10, warmup=3, attention="fused")
 
     if rank == 0:
         line = {
@@ -353,7 +358,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
                        "l2": "inputs (805 MB) exceed L2 (126 MB); no flush needed",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "per_gpu_tops": value / world,
+            "per_gpu_tops": value / world, "vit_b16_bs64": vit_line,
         }
         print(json.dumps(line), flush=True)
 
@@ -365,6 +370,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-vit", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
