@@ -151,7 +151,9 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
       uint32_t w[2] = {0u, 0u};
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        int v = __float2int_rn(__fmul_rn(x[n][i], inv));
+        // round to nearest even through the bits of 1.5 * 2^23: exact for |y| < 2^22 (here |y| <= 127.5),
+        // the same integer __float2int_rn returns, without its quarter-rate conversion unit
+        int v = __float_as_int(__fadd_rn(__fmul_rn(x[n][i], inv), 12582912.0f)) - 0x4B400000;
         v = max(-127, min(127, v));
         w[i >> 2] |= ((uint32_t)v & 0xffu) << (8 * (i & 3));
       }
