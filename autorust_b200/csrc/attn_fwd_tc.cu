@@ -42,9 +42,9 @@ using namespace arptx;
 // Optional cycle accounting (-DAR_TRACE, debug builds only): per-role clock64 deltas accumulated
 // behind the status word.
 #ifdef AR_TRACE
-#define TR_DECL(n) long long tr_##n = 0
-#define TR_T(var) const long long var = clock64()
-#define TR_ADD(n, a, b) tr_##n += (b) - (a)
+#define TR_DECL(n) unsigned tr_##n = 0
+#define TR_T(var) const unsigned var = (unsigned)clock()
+#define TR_ADD(n, a, b) tr_##n += (unsigned)(b) - (unsigned)(a)
 #define TR_FLUSH(slot, n) atomicAdd(((unsigned long long*)status) + 1 + (slot), (unsigned long long)tr_##n)
 #else
 #define TR_DECL(n)
@@ -62,8 +62,21 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG = -1e30f * LOG2E;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr int NUM_THREADS = 384;    // 3 warpgroups: softmax 0, softmax 1, {TMA producer, MMA issuer, 2 idle warps}
-constexpr int SOFTMAX_REGS = 224;   // register budget of the softmax warps after setmaxnreg
-constexpr int SERVICE_REGS = 56;    // ... and of the third warpgroup
+constexpr int SOFTMAX_REGS = 216;   // register budget of the softmax warps after setmaxnreg
+constexpr int SERVICE_REGS = 72;    // ... and of the third warpgroup
+// setmaxnreg moves registers inside the pool the CTA was launched with (168 per thread for 384 threads);
+// an increase that the pool cannot cover waits forever.
+static_assert(8 * 32 * SOFTMAX_REGS + 4 * 32 * SERVICE_REGS <= 168 * NUM_THREADS, "register pool of the CTA");
+
+// One lane of a converged warp (elect.sync).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void commit_one(uint64_t* bar) {
+  if (elect_one()) tc_commit(bar);
+}
 
 // One softmax step of one row: scores of 128 keys (sv, raw accumulator bits) -> P in TMEM, running
 // max m and running sum l updated, O rescaled in place when the max grows by more than the threshold.
@@ -240,7 +253,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler as well
   const int lane = tid & 31;
   const int bh = blockIdx.y;
   const int b = bh / Hq;
@@ -331,7 +344,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop, converged, and one elected lane issues the tcgen05 instructions:
+    // in a region the compiler sees as divergent every one of them is wrapped in an election and its
+    // operands are moved to uniform registers one by one, which costs the issuer more cycles than the
+    // MMAs take.
+    {
       // Descriptor words that never change: the high halves, and the low halves (address >> 4) of the
       // first Q tile, K stage and V stage.  Per instruction only a constant is added to a low word.
       const uint64_t qk_proto = make_sdesc_sw128(0, 16, 1024);
@@ -345,6 +362,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint32_t d = tb + t * 128;
         const uint32_t qa = q_lo0 + t * (C::QK_TILE_BYTES >> 4);
         const uint32_t ka = k_lo0 + ks * (C::QK_TILE_BYTES >> 4);
+        if (!elect_one()) return;
 #pragma unroll
         for (int s = 0; s < C::QK_KSTEPS; s++) {
           const uint32_t off = ((s >> 2) * (BM * 128) + (s & 3) * 32) >> 4;
@@ -355,6 +373,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint32_t d = tb + 256 + t * 128;
         const uint32_t a = tb + t * 128;
         const uint32_t va = v_lo0 + vs * (C::V_TILE_BYTES >> 4);
+        if (!elect_one()) return;
 #pragma unroll
         for (int s = 0; s < C::PV_KSTEPS; s++) {
           if constexpr (MODE == TC_TF32)  // K-major V^T: 8 keys = 32 bytes per step, 4 steps per 128-byte box
@@ -366,28 +385,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       };
       TR_DECL(mma_wait_kv); TR_DECL(mma_wait_p); TR_DECL(mma_issue); TR_T(tm_begin);
       bool ok = true;
-      if (nkv_max > 0) ok = mbar_wait(&k_full[0], 0, abort_flag, status, 0x20);
+      if (nkv_max > 0) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, abort_flag, status, 0x20));
       for (int t = 0; t < 2 && ok; t++) {
         if (nkv[t] == 0) continue;
-        ok = mbar_wait(&q_full[t], 0, abort_flag, status, 0x21);
+        ok = __all_sync(0xffffffffu, mbar_wait(&q_full[t], 0, abort_flag, status, 0x21));
         if (!ok) break;
         tc_fence_after();
         issue_qk(t, 0);
-        tc_commit(&s_full[t]);
+        commit_one(&s_full[t]);
       }
-      if (ok && nkv_max > 0) tc_commit(&k_empty[0]);
+      if (ok && nkv_max > 0) commit_one(&k_empty[0]);
       for (int j = 0; j < nkv_max && ok; j++) {
         const int s = j % ST;
         const int s1 = (j + 1) % ST;
         TR_T(tv0);
-        ok = mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22);
+        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22));
         TR_T(tv1); TR_ADD(mma_wait_kv, tv0, tv1);
         if (!ok) break;
         bool k_next_ready = false;
         for (int t = 0; t < 2 && ok; t++) {
           if (j >= nkv[t]) continue;
           TR_T(tp0);
-          ok = mbar_wait(&p_full[t], j & 1, abort_flag, status, 0x23);
+          ok = __all_sync(0xffffffffu, mbar_wait(&p_full[t], j & 1, abort_flag, status, 0x23));
           TR_T(tp1); TR_ADD(mma_wait_p, tp0, tp1);
           if (!ok) break;
           tc_fence_after();
@@ -397,7 +416,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (j + 1 < nkv[t]) {
             if (!k_next_ready) {
               TR_T(tk0);
-              ok = mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24);
+              ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24));
               TR_T(tk1); TR_ADD(mma_wait_kv, tk0, tk1);
               if (!ok) break;
               tc_fence_after();
@@ -406,17 +425,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             TR_T(tq0);
             issue_qk(t, s1);
             TR_T(tq1); TR_ADD(mma_issue, tq0, tq1);
-            tc_commit(&s_full[t]);
+            commit_one(&s_full[t]);
           } else {
-            tc_commit(&o_full[t]);
+            commit_one(&o_full[t]);
           }
         }
         if (!ok) break;
-        tc_commit(&v_empty[s]);
-        if (j + 1 < nkv_max) tc_commit(&k_empty[s1]);
+        commit_one(&v_empty[s]);
+        if (j + 1 < nkv_max) commit_one(&k_empty[s1]);
       }
 #ifdef AR_TRACE
-      { TR_T(tm_end); TR_DECL(mma_total); TR_ADD(mma_total, tm_begin, tm_end); TR_FLUSH(5, mma_wait_p); TR_FLUSH(6, mma_wait_kv); TR_FLUSH(7, mma_issue); TR_FLUSH(8, mma_total); }
+      if (lane == 0) { TR_T(tm_end); TR_DECL(mma_total); TR_ADD(mma_total, tm_begin, tm_end); TR_FLUSH(5, mma_wait_p); TR_FLUSH(6, mma_wait_kv); TR_FLUSH(7, mma_issue); TR_FLUSH(8, mma_total); }
 #endif
     }
   } else if (warp < 8) {
