@@ -41,7 +41,7 @@ using namespace arptx;
 
 // Optional cycle accounting (-DAR_TRACE, debug builds only): per-role clock64 deltas accumulated
 // behind the status word.
-#ifdef AR_TRACE
+#if defined(AR_TRACE) && AR_TRACE < 3
 #define TR_DECL(n) unsigned tr_##n = 0
 #define TR_T(var) const unsigned var = (unsigned)clock()
 #define TR_ADD(n, a, b) tr_##n += (unsigned)(b) - (unsigned)(a)
@@ -51,6 +51,18 @@ using namespace arptx;
 #define TR_T(var)
 #define TR_ADD(n, a, b)
 #define TR_FLUSH(slot, n)
+#endif
+
+// Timeline of one CTA (-DAR_TRACE=3, debug builds only): clock() at fixed points of a few steps.
+#if defined(AR_TRACE) && AR_TRACE >= 3
+__device__ unsigned g_timeline[4 * 8 * 16];
+#define TL(role, j, ev)                                                                   \
+  do {                                                                                    \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && ((j) >= 20 && (j) < 28))                      \
+      g_timeline[((role) * 8 + ((j) - 20)) * 16 + (ev)] = (unsigned)clock();              \
+  } while (0)
+#else
+#define TL(role, j, ev)
 #endif
 
 constexpr int BM = 128;  // query rows per tile
@@ -85,7 +97,7 @@ __device__ __forceinline__ void commit_one(uint64_t* bar) {
 template <int MODE, int D, bool EDGE>
 __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float& l, float c, int j, int col0, int row,
                                              int N, int causal, const float* __restrict__ mask, uint32_t tS,
-                                             uint32_t tO) {
+                                             uint32_t tO, uint64_t* p_first_half) {
   float mc;  // row maximum of this step in the scaled (log2) domain
   if constexpr (EDGE) {
     // leaves scaled logits in sv and c = 1
@@ -186,6 +198,13 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
         pk[i] = pack_bf16x2(p0, p1);
       }
     }
+    if (qd == 2) {
+      // The stores of the first 64 keys were issued a quarter ago and have landed by now: hand that half
+      // of P to the MMA warp, whose first PV instructions then run under the rest of this loop.
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_first_half);
+    }
     if constexpr (MODE == TC_TF32)
       tmem_st32(tS + qd * 32, pk);
     else
@@ -216,7 +235,7 @@ struct Cfg {
   static constexpr int P_COLS = MODE == TC_TF32 ? BN : BN / 2;  // TMEM columns of P
   static constexpr int STAGES = (2 * QK_TILE_BYTES + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2;
   static constexpr int SMEM_TILES = 2 * QK_TILE_BYTES + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
-  static constexpr int NUM_BARS = 2 + 4 * STAGES + 6;
+  static constexpr int NUM_BARS = 2 + 4 * STAGES + 8;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
   static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
@@ -247,8 +266,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* v_full = k_empty + ST;     // [ST]
   uint64_t* v_empty = v_full + ST;     // [ST]
   uint64_t* s_full = v_empty + ST;     // [2]
-  uint64_t* p_full = s_full + 2;       // [2]
-  uint64_t* o_full = p_full + 2;       // [2]
+  uint64_t* p_half = s_full + 2;       // [tile][half of the keys]: P of 64 keys written by the tile's 128 threads
+  uint64_t* o_full = p_half + 4;       // [2]
   uint32_t* tmem_slot = (uint32_t*)(o_full + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -271,12 +290,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
   const int nkv_max = max(nkv[0], nkv[1]);
 
+#if defined(AR_TRACE) && AR_TRACE >= 3
+  if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    g_timeline[3 * 8 * 16 + 0] = (unsigned)clock();
+    g_timeline[3 * 8 * 16 + 1] = (unsigned)gt;
+  }
+#endif
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; i++) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_half[2 * i], 128);
+      mbar_init(&p_half[2 * i + 1], 128);
       mbar_init(&o_full[i], 1);
     }
     for (int i = 0; i < ST; i++) {
@@ -369,13 +397,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           mma_ss_lohi<C::QK_KIND>(d, qa + off, qk_hi, ka + off, qk_hi, C::IDESC_QK, s > 0);
         }
       };
-      auto issue_pv = [&](int t, int vs, bool acc) {
+      auto issue_pv = [&](int t, int vs, bool acc, int hf) {
         const uint32_t d = tb + 256 + t * 128;
         const uint32_t a = tb + t * 128;
         const uint32_t va = v_lo0 + vs * (C::V_TILE_BYTES >> 4);
         if (!elect_one()) return;
 #pragma unroll
-        for (int s = 0; s < C::PV_KSTEPS; s++) {
+        for (int s2 = 0; s2 < C::PV_KSTEPS / 2; s2++) {
+          const int s = hf * (C::PV_KSTEPS / 2) + s2;
           if constexpr (MODE == TC_TF32)  // K-major V^T: 8 keys = 32 bytes per step, 4 steps per 128-byte box
             mma_ts_lohi<KIND_TF32>(d, a + s * 8, (qk_lo | (va & 0x3fffu)) + (((s >> 2) * C::V_BOX_BYTES + (s & 3) * 32) >> 4),
                                    qk_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
@@ -398,33 +427,42 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int j = 0; j < nkv_max && ok; j++) {
         const int s = j % ST;
         const int s1 = (j + 1) % ST;
+        if (lane == 0) TL(2, j, 0);
         TR_T(tv0);
         ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22));
         TR_T(tv1); TR_ADD(mma_wait_kv, tv0, tv1);
+        if (lane == 0) TL(2, j, 1);
         if (!ok) break;
-        bool k_next_ready = false;
+        // K(j+1) is needed right after the last PV of a tile: see it arrive now, off the critical path
+        if (j + 1 < nkv_max) {
+          TR_T(tk0);
+          ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24));
+          TR_T(tk1); TR_ADD(mma_wait_kv, tk0, tk1);
+          if (!ok) break;
+        }
         for (int t = 0; t < 2 && ok; t++) {
           if (j >= nkv[t]) continue;
-          TR_T(tp0);
-          ok = __all_sync(0xffffffffu, mbar_wait(&p_full[t], j & 1, abort_flag, status, 0x23));
-          TR_T(tp1); TR_ADD(mma_wait_p, tp0, tp1);
+          // P arrives in two halves of 64 keys: the first PV MMAs run under the second half's exponentials
+#pragma unroll
+          for (int hf = 0; hf < 2; hf++) {
+            TR_T(tp0);
+            ok = __all_sync(0xffffffffu, mbar_wait(&p_half[2 * t + hf], j & 1, abort_flag, status, 0x23));
+            TR_T(tp1); TR_ADD(mma_wait_p, tp0, tp1);
+            if (lane == 0 && hf == 1) TL(2, j, 2 + 4 * t);
+            if (!ok) break;
+            tc_fence_after();
+            TR_T(ti0);
+            issue_pv(t, s, j > 0, hf);
+            TR_T(ti1); TR_ADD(mma_issue, ti0, ti1);
+          }
           if (!ok) break;
-          tc_fence_after();
-          TR_T(ti0);
-          issue_pv(t, s, j > 0);
-          TR_T(ti1); TR_ADD(mma_issue, ti0, ti1);
+          if (lane == 0) TL(2, j, 3 + 4 * t);
           if (j + 1 < nkv[t]) {
-            if (!k_next_ready) {
-              TR_T(tk0);
-              ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24));
-              TR_T(tk1); TR_ADD(mma_wait_kv, tk0, tk1);
-              if (!ok) break;
-              tc_fence_after();
-              k_next_ready = true;
-            }
+            if (lane == 0) TL(2, j, 4 + 4 * t);
             TR_T(tq0);
             issue_qk(t, s1);
             TR_T(tq1); TR_ADD(mma_issue, tq0, tq1);
+            if (lane == 0) TL(2, j, 5 + 4 * t);
             commit_one(&s_full[t]);
           } else {
             commit_one(&o_full[t]);
@@ -433,6 +471,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!ok) break;
         commit_one(&v_empty[s]);
         if (j + 1 < nkv_max) commit_one(&k_empty[s1]);
+        if (lane == 0) TL(2, j, 10);
       }
 #ifdef AR_TRACE
       if (lane == 0) { TR_T(tm_end); TR_DECL(mma_total); TR_ADD(mma_total, tm_begin, tm_end); TR_FLUSH(5, mma_wait_p); TR_FLUSH(6, mma_wait_kv); TR_FLUSH(7, mma_issue); TR_FLUSH(8, mma_total); }
@@ -455,9 +494,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     TR_DECL(sm_wait_s); TR_DECL(sm_ld); TR_DECL(sm_compute); TR_DECL(sm_st); TR_DECL(sm_steps); TR_T(tsm_begin);
     bool ok = true;
     for (int j = 0; j < nkv[t]; j++) {
+      if (r == 0) TL(t, j, 0);
       TR_T(ts0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, status, 0x30));
       TR_T(ts1); TR_ADD(sm_wait_s, ts0, ts1);
+      if (r == 0) TL(t, j, 1);
       if (!ok) break;
       tc_fence_after();
       uint32_t sv[BN];
@@ -467,6 +508,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
       TR_T(ts2); TR_ADD(sm_ld, ts1, ts2);
+      if (r == 0) TL(t, j, 2);
       float c = scale_log2;
       if (MODE == TC_SAGE) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
@@ -474,14 +516,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // Two separate instantiations: the interior step must not carry the merge points of the
       // boundary path (that alone costs it ~300 cycles of scheduling freedom).
       if (edge)
-        softmax_step<MODE, D, true>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO);
+        softmax_step<MODE, D, true>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_half[2 * t]);
       else
-        softmax_step<MODE, D, false>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO);
+        softmax_step<MODE, D, false>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_half[2 * t]);
       TR_T(ts3); TR_ADD(sm_compute, ts2, ts3);
+      if (r == 0) TL(t, j, 3);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[t]);
+      mbar_arrive(&p_half[2 * t + 1]);
       TR_T(ts4); TR_ADD(sm_st, ts3, ts4); TR_ADD(sm_steps, 0, 1);
+      if (r == 0) TL(t, j, 4);
     }
 #ifdef AR_TRACE
     if (tid == 0) { TR_T(tsm_end); TR_DECL(sm_total); TR_ADD(sm_total, tsm_begin, tsm_end); TR_FLUSH(0, sm_wait_s); TR_FLUSH(1, sm_ld); TR_FLUSH(2, sm_compute); TR_FLUSH(3, sm_st); TR_FLUSH(4, sm_total); TR_FLUSH(9, sm_steps); }
@@ -525,6 +569,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tb, 512);
+#if defined(AR_TRACE) && AR_TRACE >= 3
+  if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    g_timeline[3 * 8 * 16 + 2] = (unsigned)clock();
+    g_timeline[3 * 8 * 16 + 3] = (unsigned)gt;
+  }
+#endif
 }
 
 template <int MODE, int D>
@@ -564,3 +616,10 @@ cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace ar
+
+#if defined(AR_TRACE) && AR_TRACE >= 3
+extern "C" int ar_debug_read_timeline(unsigned* out, int n) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, ar::g_timeline, (size_t)n * 4);
+}
+#endif
