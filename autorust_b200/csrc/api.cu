@@ -164,6 +164,9 @@ int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t
   if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   ar::PrologueArgs a{q, k, dtype, q8, k8, q_scale, k_scale, k_mean, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, smooth};
+  // this entry point has no workspace: its status goes to the library's own word (ar_attn_last_status(NULL, ...))
+  a.status = status_ptr(nullptr);
+  if (!a.status || cudaMemsetAsync(a.status, 0, sizeof(uint32_t), (cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;
   int launches = 0;
   cudaError_t e = ar::launch_sage_prologue(a, (cudaStream_t)cu_stream, &launches);
   g_launches += (uint64_t)launches;
@@ -232,8 +235,10 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     float* ks = (float*)(ws + L.k_scale);
     float* km = (float*)(ws + L.k_mean);
     ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
+    p.status = status;  // shared with the attention kernel: cleared once, before the first launch
     int launches = 0;
     if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
+    if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
     cudaError_t e = ar::launch_sage_prologue(p, stream, &launches);
     g_launches += (uint64_t)launches;
     if (e != cudaSuccess) return AR_ERR_CUDA;
@@ -253,7 +258,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
         !make_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
       return AR_ERR_CUDA;
   }
-  if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (mode != AR_MODE_SAGE_INT8 && cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
   cudaError_t e = ar::launch_attn_tc(a, stream);
   if (e != cudaSuccess) return AR_ERR_CUDA;
   g_launches++;

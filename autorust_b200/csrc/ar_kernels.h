@@ -45,6 +45,7 @@ struct PrologueArgs {
   float *q_scale, *k_scale, *k_mean;
   int B, Hq, Hkv, S, D;
   int smooth;
+  uint32_t* status = nullptr;  // device word a bounded wait that ran out is recorded in; cleared by the caller
 };
 // Returns the number of kernels launched through *launches.
 cudaError_t launch_sage_prologue(const PrologueArgs& a, cudaStream_t stream, int* launches);

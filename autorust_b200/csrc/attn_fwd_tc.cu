@@ -67,6 +67,10 @@ __device__ unsigned g_timeline[4 * 8 * 16];
 
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per step
+#ifndef AR_NPART
+#define AR_NPART 2
+#endif
+constexpr int NPART = AR_NPART;  // P of a step is handed to the MMA warp in this many parts (1, 2 or 4)
 constexpr float LOG2E = 1.4426950408889634f;
 // The reference's finite sentinel (-1e30), expressed in the log2 domain the softmax works in, so that
 // a logit masked by an additive -1e30 still ties with the initial running max (p = 1 for a fully
@@ -97,7 +101,7 @@ __device__ __forceinline__ void commit_one(uint64_t* bar) {
 template <int MODE, int D, bool EDGE>
 __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float& l, float c, int j, int col0, int row,
                                              int N, int causal, const float* __restrict__ mask, uint32_t tS,
-                                             uint32_t tO, uint64_t* p_first_half) {
+                                             uint32_t tO, uint64_t* p_parts) {
   float mc;  // row maximum of this step in the scaled (log2) domain
   if constexpr (EDGE) {
     // leaves scaled logits in sv and c = 1
@@ -198,12 +202,12 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
         pk[i] = pack_bf16x2(p0, p1);
       }
     }
-    if (qd == 2) {
-      // The stores of the first 64 keys were issued a quarter ago and have landed by now: hand that half
+    if (qd > 0 && qd % (4 / NPART) == 0) {
+      // The stores of the previous part were issued a quarter ago and have landed by now: hand that part
       // of P to the MMA warp, whose first PV instructions then run under the rest of this loop.
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_first_half);
+      mbar_arrive(p_parts + qd / (4 / NPART) - 1);
     }
     if constexpr (MODE == TC_TF32)
       tmem_st32(tS + qd * 32, pk);
@@ -235,7 +239,7 @@ struct Cfg {
   static constexpr int P_COLS = MODE == TC_TF32 ? BN : BN / 2;  // TMEM columns of P
   static constexpr int STAGES = (2 * QK_TILE_BYTES + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2;
   static constexpr int SMEM_TILES = 2 * QK_TILE_BYTES + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
-  static constexpr int NUM_BARS = 2 + 4 * STAGES + 8;
+  static constexpr int NUM_BARS = 2 + 4 * STAGES + 4 + 2 * NPART;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
   static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
@@ -266,8 +270,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* v_full = k_empty + ST;     // [ST]
   uint64_t* v_empty = v_full + ST;     // [ST]
   uint64_t* s_full = v_empty + ST;     // [2]
-  uint64_t* p_half = s_full + 2;       // [tile][half of the keys]: P of 64 keys written by the tile's 128 threads
-  uint64_t* o_full = p_half + 4;       // [2]
+  uint64_t* p_part = s_full + 2;       // [tile][part of the keys]: P of 128 / NPART keys written by the tile's 128 threads
+  uint64_t* o_full = p_part + 2 * NPART;  // [2]
   uint32_t* tmem_slot = (uint32_t*)(o_full + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -303,8 +307,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int i = 0; i < 2; i++) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_half[2 * i], 128);
-      mbar_init(&p_half[2 * i + 1], 128);
+      for (int k2 = 0; k2 < NPART; k2++) mbar_init(&p_part[NPART * i + k2], 128);
       mbar_init(&o_full[i], 1);
     }
     for (int i = 0; i < ST; i++) {
@@ -403,8 +406,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint32_t va = v_lo0 + vs * (C::V_TILE_BYTES >> 4);
         if (!elect_one()) return;
 #pragma unroll
-        for (int s2 = 0; s2 < C::PV_KSTEPS / 2; s2++) {
-          const int s = hf * (C::PV_KSTEPS / 2) + s2;
+        for (int s2 = 0; s2 < C::PV_KSTEPS / NPART; s2++) {
+          const int s = hf * (C::PV_KSTEPS / NPART) + s2;
           if constexpr (MODE == TC_TF32)  // K-major V^T: 8 keys = 32 bytes per step, 4 steps per 128-byte box
             mma_ts_lohi<KIND_TF32>(d, a + s * 8, (qk_lo | (va & 0x3fffu)) + (((s >> 2) * C::V_BOX_BYTES + (s & 3) * 32) >> 4),
                                    qk_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
@@ -442,13 +445,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         for (int t = 0; t < 2 && ok; t++) {
           if (j >= nkv[t]) continue;
-          // P arrives in two halves of 64 keys: the first PV MMAs run under the second half's exponentials
+          // P arrives in NPART parts: the first PV MMAs run under the exponentials of the later parts
 #pragma unroll
-          for (int hf = 0; hf < 2; hf++) {
+          for (int hf = 0; hf < NPART; hf++) {
             TR_T(tp0);
-            ok = __all_sync(0xffffffffu, mbar_wait(&p_half[2 * t + hf], j & 1, abort_flag, status, 0x23));
+            ok = __all_sync(0xffffffffu, mbar_wait(&p_part[NPART * t + hf], j & 1, abort_flag, status, 0x23));
             TR_T(tp1); TR_ADD(mma_wait_p, tp0, tp1);
-            if (lane == 0 && hf == 1) TL(2, j, 2 + 4 * t);
+            if (lane == 0 && hf == NPART - 1) TL(2, j, 2 + 4 * t);
             if (!ok) break;
             tc_fence_after();
             TR_T(ti0);
@@ -516,14 +519,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // Two separate instantiations: the interior step must not carry the merge points of the
       // boundary path (that alone costs it ~300 cycles of scheduling freedom).
       if (edge)
-        softmax_step<MODE, D, true>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_half[2 * t]);
+        softmax_step<MODE, D, true>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
       else
-        softmax_step<MODE, D, false>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_half[2 * t]);
+        softmax_step<MODE, D, false>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
       TR_T(ts3); TR_ADD(sm_compute, ts2, ts3);
       if (r == 0) TL(t, j, 3);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_half[2 * t + 1]);
+      mbar_arrive(&p_part[NPART * t + NPART - 1]);
       TR_T(ts4); TR_ADD(sm_st, ts3, ts4); TR_ADD(sm_steps, 0, 1);
       if (r == 0) TL(t, j, 4);
     }

@@ -5,6 +5,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 
@@ -317,6 +318,121 @@ std::optional<Tensor> fused_attention_ex(const Tensor& q, const Tensor& k, const
   sess.capture_host(call);  // :696-701: record for replay, then run
   call.exec(false);
   return out;
+}
+
+// ------------------------------------------------------------------- streamed host-to-host form
+namespace {
+// Kernel choice of fused_attention_ex for a problem of `b` batches: sage > bf16 > tf32 > scalar.
+int choose_mode(DType dt, bool quantized, int64_t b, int64_t h, int64_t hk, int64_t n, int64_t d, bool causal,
+                bool has_mask) {
+  const Settings settings = global_settings();
+  auto has = [&](int mode) { return ar_attn_supported(mode, (int)dt, b, h, hk, n, d, causal ? 1 : 0, has_mask ? 1 : 0) == 1; };
+  if (quantized && settings.tensor_cores && has(AR_MODE_SAGE_INT8)) return AR_MODE_SAGE_INT8;
+  if (quantized) note_sage_unsupported();
+  if (dt == DType::BFloat16 && settings.tensor_cores && has(AR_MODE_BF16)) return AR_MODE_BF16;
+  if (dt == DType::Float32 && settings.tensor_cores && has(AR_MODE_TF32)) return AR_MODE_TF32;
+  if (dt == DType::Float32 && has(AR_MODE_EXACT_F32)) return AR_MODE_EXACT_F32;
+  return -1;
+}
+struct StreamSet {  // three streams and the events of one call; destroyed on every way out
+  cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+  std::vector<cudaEvent_t> events;
+  cudaEvent_t event() {
+    cudaEvent_t e;
+    cuda_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+    events.push_back(e);
+    return e;
+  }
+  StreamSet() {
+    cuda_check(cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking), "cudaStreamCreate");
+    cuda_check(cudaStreamCreateWithFlags(&run, cudaStreamNonBlocking), "cudaStreamCreate");
+    cuda_check(cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking), "cudaStreamCreate");
+  }
+  ~StreamSet() {
+    for (cudaStream_t s : {in, run, out})
+      if (s) {
+        cudaStreamSynchronize(s);
+        cudaStreamDestroy(s);
+      }
+    for (cudaEvent_t e : events) cudaEventDestroy(e);
+  }
+};
+}  // namespace
+
+void attention_host(AttentionKind kind, const void* q, const void* k, const void* v, void* out, DType dt, int64_t B,
+                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D, const float* mask_host, bool is_causal,
+                    int64_t groups_per_chunk, int device) {
+  if (!q || !k || !v || !out) throw Error("attention_host: null host pointer");
+  if (kind == AttentionKind::Sdpa) throw Error("attention_host: the graph SDPA is outside this library");
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0 || Hq % Hkv != 0) throw Error("attention_host: bad shape");
+  const int dev = resolve_device(device);
+  DeviceGuard guard(dev);
+  const int64_t G = Hq / Hkv;      // query heads per kv head
+  const int64_t groups = B * Hkv;  // independent units: one kv head with its G query heads
+  // A chunk of consecutive groups is an operator call of its own with batch = groups, Hq = G, Hkv = 1:
+  // the q heads of a kv head are adjacent in [B, Hq, S, D], so every chunk is contiguous in q, k, v and out.
+  const int mode = choose_mode(dt, kind == AttentionKind::Sage, 1, G, 1, S, D, is_causal, mask_host != nullptr);
+  if (mode < 0) throw Error("attention_host: no fused kernel covers this call");
+  int64_t per = groups_per_chunk > 0 ? groups_per_chunk : (groups + 15) / 16;
+  if (per > groups) per = groups;
+  const int64_t chunks = (groups + per - 1) / per;
+  const size_t es = itemsize(dt);
+  const size_t q_group = (size_t)(G * S * D) * es, kv_group = (size_t)(S * D) * es;
+  constexpr int SLOTS = 3;
+  const int slots = (int)std::min<int64_t>(SLOTS, chunks);
+  struct Slot {
+    std::shared_ptr<Buffer> q, k, v, o, ws;
+    cudaEvent_t loaded = nullptr, done = nullptr, drained = nullptr;
+  } slot[SLOTS];
+  const size_t ws_bytes = ar_attn_workspace_bytes(mode, (int)dt, per, G, 1, S, D);
+  for (int i = 0; i < slots; i++) {
+    slot[i].q = std::make_shared<Buffer>(dev, q_group * per);
+    slot[i].k = std::make_shared<Buffer>(dev, kv_group * per);
+    slot[i].v = std::make_shared<Buffer>(dev, kv_group * per);
+    slot[i].o = std::make_shared<Buffer>(dev, q_group * per);
+    // every slot gets a workspace of its own: it also carries the status word of the slot's launches
+    slot[i].ws = std::make_shared<Buffer>(dev, ws_bytes ? ws_bytes : 256);
+  }
+  StreamSet st;
+  std::shared_ptr<Buffer> mask_dev;
+  if (mask_host) {
+    mask_dev = std::make_shared<Buffer>(dev, (size_t)(S * S) * 4);
+    cuda_check(cudaMemcpyAsync(mask_dev->ptr(), mask_host, (size_t)(S * S) * 4, cudaMemcpyHostToDevice, st.in), "cudaMemcpyAsync(mask)");
+  }
+  int rc_first = AR_OK;
+  for (int64_t c = 0; c < chunks; c++) {
+    Slot& sl = slot[c % slots];
+    const int64_t g0 = c * per, ng = std::min<int64_t>(per, groups - g0);
+    // upload: the slot is free once the download of the chunk that used it last has finished
+    if (sl.drained) cuda_check(cudaStreamWaitEvent(st.in, sl.drained, 0), "cudaStreamWaitEvent");
+    cuda_check(cudaMemcpyAsync(sl.q->ptr(), (const char*)q + g0 * q_group, q_group * ng, cudaMemcpyHostToDevice, st.in), "cudaMemcpyAsync(q)");
+    cuda_check(cudaMemcpyAsync(sl.k->ptr(), (const char*)k + g0 * kv_group, kv_group * ng, cudaMemcpyHostToDevice, st.in), "cudaMemcpyAsync(k)");
+    cuda_check(cudaMemcpyAsync(sl.v->ptr(), (const char*)v + g0 * kv_group, kv_group * ng, cudaMemcpyHostToDevice, st.in), "cudaMemcpyAsync(v)");
+    sl.loaded = st.event();
+    cuda_check(cudaEventRecord(sl.loaded, st.in), "cudaEventRecord");
+    // kernels
+    cuda_check(cudaStreamWaitEvent(st.run, sl.loaded, 0), "cudaStreamWaitEvent");
+    const int rc = ar_attn_forward(mode, (int)dt, sl.q->ptr(), sl.k->ptr(), sl.v->ptr(), sl.o->ptr(),
+                                   mask_dev ? (const float*)mask_dev->ptr() : nullptr, ng, G, 1, S, D, is_causal ? 1 : 0,
+                                   sl.ws->ptr(), sl.ws->nbytes(), st.run);
+    if (rc != AR_OK && rc_first == AR_OK) rc_first = rc;
+    if (rc != AR_OK) break;
+    sl.done = st.event();
+    cuda_check(cudaEventRecord(sl.done, st.run), "cudaEventRecord");
+    // download
+    cuda_check(cudaStreamWaitEvent(st.out, sl.done, 0), "cudaStreamWaitEvent");
+    cuda_check(cudaMemcpyAsync((char*)out + g0 * q_group, sl.o->ptr(), q_group * ng, cudaMemcpyDeviceToHost, st.out), "cudaMemcpyAsync(out)");
+    sl.drained = st.event();
+    cuda_check(cudaEventRecord(sl.drained, st.out), "cudaEventRecord");
+  }
+  cuda_check(cudaStreamSynchronize(st.in), "cudaStreamSynchronize");
+  cuda_check(cudaStreamSynchronize(st.run), "cudaStreamSynchronize");
+  cuda_check(cudaStreamSynchronize(st.out), "cudaStreamSynchronize");
+  if (rc_first != AR_OK) throw Error(std::string("attention_host: ") + ar_attn_strerror(rc_first));
+  for (int i = 0; i < slots; i++) {
+    const int status = ar_attn_last_status(slot[i].ws->ptr(), st.run);
+    if (status != AR_OK) throw Error(std::string("attention_host: ") + ar_attn_strerror(status));
+  }
 }
 
 Tensor Tensor::attention_kind(const Tensor& key, const Tensor& value, const Tensor* attn_mask, double dropout_p,

@@ -156,6 +156,21 @@ class Session {
 std::optional<Tensor> fused_attention_ex(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* attn_mask,
                                          bool is_causal, bool enable_gqa, bool quantized, Session& sess);
 
+// Host-to-host form of the operator, for callers whose q, k, v live in host memory (pinned, for the
+// copies to overlap) and whose result goes back to host memory.  The (batch, kv head) groups of the
+// operator are independent, so they are streamed through device staging slots: the upload of one
+// chunk of groups, the kernels of the previous chunk and the download of the one before run at the
+// same time on three streams.  The result is bit-identical to
+//   Tensor::from_slice(q), from_slice(k), from_slice(v) -> attention_with -> to_host
+// (src/tensor/mod.rs:2045-2208 between Tensor::from_slice and to_vec), which serialises those
+// steps; the reference has no counterpart of the streamed form.
+// kind: Flash or Sage (Sdpa throws, as the graph SDPA is not part of this library).  q, out: [B, Hq, S, D];
+// k, v: [B, Hkv, S, D]; mask_host: dense additive f32 [S, S] or null.  groups_per_chunk <= 0 picks a
+// chunk size that gives about sixteen chunks.  Returns when `out` is complete.
+void attention_host(AttentionKind kind, const void* q, const void* k, const void* v, void* out, DType dtype,
+                    int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, const float* mask_host, bool is_causal,
+                    int64_t groups_per_chunk = 0, int device = -1);
+
 // Launch counters per kernel family (`selections()` in the reference's kernel modules).
 uint64_t selections(int mode);
 

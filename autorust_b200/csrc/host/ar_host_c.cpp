@@ -83,6 +83,16 @@ int arh_fused_attention_ex(void* q, void* k, void* v, void* mask, int is_causal,
   });
 }
 
+// Streamed host-to-host form (arh::attention_host): kind 1 = flash, 2 = sage; host pointers throughout.
+int arh_attention_host(int kind, const void* q, const void* k, const void* v, void* out, int dtype, int64_t B, int64_t Hq,
+                       int64_t Hkv, int64_t S, int64_t D, const float* mask_host, int is_causal, int64_t groups_per_chunk,
+                       int device) {
+  return guarded([&] {
+    arh::attention_host((arh::AttentionKind)kind, q, k, v, out, (arh::DType)dtype, B, Hq, Hkv, S, D, mask_host,
+                        is_causal != 0, groups_per_chunk, device);
+  });
+}
+
 // Settings: attention 0 sdpa / 1 flash / 2 sage; math_mode 0 fast / 1 exact; tensor_cores -1 = follow math mode.
 void arh_settings_set(int attention, int math_mode, int tensor_cores, int cuda_device) {
   arh::Settings s;

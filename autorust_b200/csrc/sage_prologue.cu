@@ -13,6 +13,7 @@
 // 128-token span, then the spans, each left to right, times 1.0f / S), K - mean is one f32
 // subtraction, and the division and reciprocal are IEEE.
 #include "ar_kernels.h"
+#include "ar_ptx.cuh"
 #include <cuda_bf16.h>
 
 namespace ar {
@@ -162,6 +163,154 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
   }
 }
 
+// The same quantiser as a persistent, software-pipelined kernel: every CTA walks a strided list of
+// 128-token blocks (Q blocks first, then K blocks); one thread brings block i + STAGES - 1 into a
+// shared-memory ring with a bulk copy while the CTA reduces and stores block i, so that each SM keeps
+// tens of KB of reads in flight the whole time instead of one load-reduce-store round per CTA.
+// Bit-for-bit the arithmetic of quantize_kernel.  Needs 16-byte aligned Q and K.
+template <int DTYPE, int D>
+struct QuantPipe {
+  static constexpr int ES = DTYPE == 1 ? 2 : 4;
+  static constexpr int BLOCK_BYTES = 128 * D * ES;
+  static constexpr int STAGES = DTYPE == 1 ? 3 : 2;
+  static constexpr int SMEM_BYTES = STAGES * BLOCK_BYTES + 128;  // + alignment slack
+  static constexpr int CTAS_PER_SM = (200 * 1024) / SMEM_BYTES >= 2 ? 2 : 1;
+};
+
+template <int DTYPE>
+__device__ __forceinline__ void load8_shared(const uint8_t* p, float* x) {
+  if constexpr (DTYPE == 1) {
+    const uint4 w = *(const uint4*)p;
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      x[2 * i] = __uint_as_float(u[i] << 16);
+      x[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  } else {
+    const float4 a = *(const float4*)p;
+    const float4 b = *(const float4*)(p + 16);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+  }
+}
+
+template <int DTYPE, int D>
+__global__ void __launch_bounds__(256) quantize_pipe_kernel(const void* __restrict__ Q, const void* __restrict__ K,
+                                                            const float* __restrict__ k_mean, int8_t* __restrict__ q8,
+                                                            int8_t* __restrict__ k8, float* __restrict__ q_scale,
+                                                            float* __restrict__ k_scale, int S, int BHq, int BHk,
+                                                            int smooth, uint32_t* status) {
+  using P = QuantPipe<DTYPE, D>;
+  constexpr int CH = D / 8;
+  constexpr int NCHUNK = 128 * CH / 256;
+  constexpr int ST = P::STAGES;
+  extern __shared__ uint8_t qp_smem_raw[];
+  uint8_t* ring = (uint8_t*)(((uintptr_t)qp_smem_raw + 127) & ~(uintptr_t)127);
+  __shared__ uint64_t full[ST];
+  __shared__ float warp_max[2][8];
+  __shared__ uint32_t abort_flag;
+  const int tid = threadIdx.x;
+  const int nblk = (S + 127) / 128;
+  const int q_items = BHq * nblk, items = (BHq + BHk) * nblk;
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < ST; i++) arptx::mbar_init(&full[i], 1);
+    arptx::fence_mbar_init();
+  }
+  __syncthreads();
+  // item w -> (tensor, bh, block); the bytes of a block are contiguous in [BH, S, D]
+  auto issue = [&](int w, int stage) {
+    const bool is_k = w >= q_items;
+    const int r = is_k ? w - q_items : w;
+    const int bh = r / nblk, blk = r - bh * nblk;
+    const int rows = min(128, S - blk * 128);
+    const uint8_t* src = (const uint8_t*)(is_k ? K : Q) + ((size_t)bh * S + (size_t)blk * 128) * D * P::ES;
+    const uint32_t bytes = (uint32_t)rows * D * P::ES;
+    arptx::mbar_arrive_expect_tx(&full[stage], bytes);
+    arptx::bulk_load(ring + stage * P::BLOCK_BYTES, src, bytes, &full[stage]);
+  };
+  if (tid == 0) {
+    for (int i = 0; i < ST - 1; i++) {
+      const int w = blockIdx.x + i * gridDim.x;
+      if (w < items) issue(w, i);
+    }
+  }
+  const int c = tid % CH;
+  int it = 0;
+  for (int w = blockIdx.x; w < items; w += gridDim.x, it++) {
+    const int stage = it % ST;
+    // the stage that block it + ST - 1 goes to was read in iteration it - 1; every thread is past that
+    // read (the barrier at the end of the previous iteration), and the fence orders those generic-proxy
+    // reads before the bulk copy's writes
+    if (tid == 0) {
+      const int wn = w + (ST - 1) * gridDim.x;
+      if (wn < items) {
+        arptx::fence_proxy_async_smem();
+        issue(wn, (it + ST - 1) % ST);
+      }
+    }
+    const bool is_k = w >= q_items;
+    const int r = is_k ? w - q_items : w;
+    const int bh = r / nblk, blk = r - bh * nblk;
+    const int t0 = blk * 128;
+    float mu[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) mu[i] = 0.f;
+    if (is_k && smooth) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) mu[i] = k_mean[(size_t)bh * D + c * 8 + i];
+    }
+    const bool ok = arptx::mbar_wait(&full[stage], (uint32_t)(it / ST) & 1u, &abort_flag, status, 0x40);
+    if (!__syncthreads_and(ok)) break;  // a copy that never lands: the status word says so, the CTA leaves together
+    const uint8_t* blockp = ring + stage * P::BLOCK_BYTES;
+    float x[NCHUNK][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int n = 0; n < NCHUNK; n++) {
+      const int idx = tid + 256 * n;
+      if (t0 + idx / CH < S) {
+        load8_shared<DTYPE>(blockp + (size_t)idx * 8 * P::ES, x[n]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          x[n][i] = x[n][i] - mu[i];
+          amax = fmaxf(amax, fabsf(x[n][i]));
+        }
+      }
+    }
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+    if ((tid & 31) == 0) warp_max[it & 1][tid >> 5] = amax;
+    __syncthreads();  // warp maxima visible; every thread has finished reading this stage
+    amax = warp_max[it & 1][0];
+#pragma unroll
+    for (int wv = 1; wv < 8; wv++) amax = fmaxf(amax, warp_max[it & 1][wv]);
+    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (tid == 0) (is_k ? k_scale : q_scale)[(size_t)bh * nblk + blk] = scale;
+    int8_t* dst = (is_k ? k8 : q8) + ((size_t)bh * S + t0) * D;
+#pragma unroll
+    for (int n = 0; n < NCHUNK; n++) {
+      const int idx = tid + 256 * n;
+      if (t0 + idx / CH < S) {
+        uint32_t wd[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          int v = __float_as_int(__fadd_rn(__fmul_rn(x[n][i], inv), 12582912.0f)) - 0x4B400000;
+          v = max(-127, min(127, v));
+          wd[i >> 2] |= ((uint32_t)v & 0xffu) << (8 * (i & 3));
+        }
+        *(uint2*)(dst + (size_t)idx * 8) = make_uint2(wd[0], wd[1]);
+      }
+    }
+  }
+  // copies issued for stages that were never consumed (only after an abort) must land before the
+  // shared memory goes back
+  if (tid == 0 && abort_flag) {
+    for (int i = 0; i < ST; i++) arptx::mbar_wait_quiet(&full[i], 0);
+  }
+}
+
 __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst,
                                                           int64_t n8) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
@@ -207,8 +356,31 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  quantize_kernel<DTYPE, D><<<dim3(nblk, bhq + bhk, 1), 256, 0, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale,
-                                                                         a.k_scale, a.S, bhq, a.smooth);
+  if ((((uintptr_t)a.q | (uintptr_t)a.k) & 15u) == 0) {
+    // bulk copies need 16-byte aligned sources: the pipelined kernel, one or two CTAs per SM
+    using P = QuantPipe<DTYPE, D>;
+    auto kern = quantize_pipe_kernel<DTYPE, D>;
+    static bool configured[64] = {};
+    static int sm_count[64] = {};
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM_BYTES);
+      if (e != cudaSuccess) return e;
+      e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return e;
+      configured[dev] = true;
+    }
+    const int items = (bhq + bhk) * nblk;
+    int grid = (dev < 64 ? sm_count[dev] : 148) * P::CTAS_PER_SM;
+    if (grid > items) grid = items;
+    kern<<<grid, 256, P::SMEM_BYTES, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale, a.k_scale, a.S, bhq, bhk,
+                                               a.smooth, a.status);
+  } else {
+    quantize_kernel<DTYPE, D><<<dim3(nblk, bhq + bhk, 1), 256, 0, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale,
+                                                                           a.k_scale, a.S, bhq, a.smooth);
+  }
   (*launches)++;
   return cudaGetLastError();
 }

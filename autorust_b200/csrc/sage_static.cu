@@ -119,6 +119,9 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
   float* ks = (float*)(ws + o_ks);
   float* km = (float*)(ws + o_km);
   ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
+  // the status word is the one part of the shared scratch that must start at zero; both kernels report to it
+  p.status = (uint32_t*)ws;
+  if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
   int launches = 0;
   if (ar::launch_sage_prologue(p, stream, &launches) != cudaSuccess) return AR_ERR_CUDA;
   const void* v16 = v;
@@ -143,8 +146,6 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
       !tile_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hkv, S, D) ||
       !tile_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
     return AR_ERR_CUDA;
-  // the status word is the one part of the shared scratch that must start at zero
-  if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
   if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;
   ar::count_launches(AR_MODE_SAGE_INT8, launches + 1);
   return AR_OK;

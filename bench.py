@@ -331,7 +331,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         e2e_value = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
         e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d_bytes"] * world,
                "d2h_bytes_per_step": e2e["d2h_bytes"] * world, "ms_per_step": e2e["ms_per_step"],
-               "api": e2e["api"]}
+               "api": e2e["api"], "ms_per_step_tensor_api": e2e["ms_per_step_tensor_api"],
+               "tensor_api": e2e["tensor_api"], "streamed_equals_tensor_api": e2e["streamed_equals_tensor_api"]}
         if world > 1:
             t = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)

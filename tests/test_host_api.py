@@ -185,3 +185,51 @@ def test_allocation_cache_reuses_buffers(host):
     del b
     host.load().arh_empty_cache(-1)
     assert host.load().arh_cached_bytes(-1) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,per", [("flash_f32", 0), ("flash_f32", 3), ("sage_bf16", 1), ("sage_bf16", 0)])
+def test_streamed_host_call_is_bit_identical_to_the_tensor_api(host, kind, per):
+    """arh::attention_host streams chunks of (batch, kv head) groups through staging slots; whatever the
+    chunking (a ragged last chunk included), the result has the bits of from_slice x3 -> attention_with
+    -> to_list, because every group is an operator call of its own."""
+    import torch
+    host.Settings.set()
+    sess = host.Session()
+    if kind == "flash_f32":  # GQA + mask + causal on the TF32 kernel
+        b, hq, hkv, n, d = 2, 8, 4, 200, 64
+        q, k, v = normal_qkv(41, b, hq, hkv, n, d)
+        mask = sawtooth_mask(n)
+        want = _t(host, q).flash_attention_with(_t(host, k), _t(host, v), _t(host, mask), 0.0, True, sess).to_list()
+        out = np.empty_like(q)
+        host.attention_host(host.FLASH, q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data, host.FLOAT32,
+                            b, hq, hkv, n, d, mask.ctypes.data, True, per)
+        assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+    else:  # Sage, bf16, pinned host memory
+        b, hq, hkv, n, d = 3, 4, 2, 300, 128
+        q, k, v = (torch.from_numpy(a).to(torch.bfloat16).pin_memory() for a in normal_qkv(42, b, hq, hkv, n, d, 2.0))
+        shape_q, shape_kv = (b, hq, n, d), (b, hkv, n, d)
+        tq = host.Tensor.from_host_ptr(q.data_ptr(), host.BFLOAT16, shape_q)
+        tk = host.Tensor.from_host_ptr(k.data_ptr(), host.BFLOAT16, shape_kv)
+        tv = host.Tensor.from_host_ptr(v.data_ptr(), host.BFLOAT16, shape_kv)
+        want = torch.empty_like(q)
+        tq.sage_attention_with(tk, tv, None, 0.0, False, sess).to_host_ptr(want.data_ptr())
+        assert sess.kernel_names() == ["ar_flash_sage"]
+        out = torch.empty_like(q).pin_memory()
+        host.attention_host(host.SAGE, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), host.BFLOAT16,
+                            b, hq, hkv, n, d, None, False, per)
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_streamed_host_call_rejects_what_the_operator_rejects(host):
+    q = np.zeros((1, 2, 16, 64), np.float32)
+    with pytest.raises(host.TgError, match="TGERR"):
+        host.attention_host(host.SDPA, q.ctypes.data, q.ctypes.data, q.ctypes.data, q.ctypes.data, host.FLOAT32,
+                            1, 2, 2, 16, 64)
+    with pytest.raises(host.TgError, match="bad shape"):
+        host.attention_host(host.FLASH, q.ctypes.data, q.ctypes.data, q.ctypes.data, q.ctypes.data, host.FLOAT32,
+                            1, 3, 2, 16, 64)
+    with pytest.raises(host.TgError, match="no fused kernel"):  # bf16 at a head size without a kernel
+        host.attention_host(host.FLASH, q.ctypes.data, q.ctypes.data, q.ctypes.data, q.ctypes.data, host.BFLOAT16,
+                            1, 2, 2, 16, 96)
