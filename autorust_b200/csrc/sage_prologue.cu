@@ -14,6 +14,7 @@
 // subtraction, and the division and reciprocal are IEEE.
 #include "ar_kernels.h"
 #include "ar_ptx.cuh"
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 namespace ar {
@@ -94,6 +95,81 @@ __global__ void __launch_bounds__(MEAN_SLOTS * D) k_mean_kernel(const void* __re
     // ordered behind this round's reads by the two barriers above
   }
   if (tid < D) k_mean[(size_t)blockIdx.x * D + tid] = total * (1.0f / (float)S);
+}
+
+// The same mean with the spans of one (batch, kv head) pair spread over a cluster of MEAN_CLUSTER CTAs, so
+// that a handful of heads still fills the GPU.  Every CTA leaves the sums of its spans in its own shared
+// memory; CTA 0 of the cluster then adds all of them in span order through distributed shared memory --
+// the order, and therefore every bit, of the single-CTA kernel.  grid = (MEAN_CLUSTER, B * Hkv).
+constexpr int MEAN_CLUSTER = 8;
+template <int DTYPE, int D>
+__global__ void __launch_bounds__(MEAN_SLOTS * D) k_mean_cluster_kernel(const void* __restrict__ K,
+                                                                        float* __restrict__ k_mean, int S, int per) {
+  namespace cg = cooperative_groups;
+  constexpr int CH = D / 8;
+  __shared__ float run_sums[MEAN_SLOTS][8][D];
+  extern __shared__ float my_spans[];  // [per][D]: sums of the spans this CTA owns; then [nspan][D], used by CTA 0
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int tid = threadIdx.x;
+  const int slot = tid / D;
+  const int g = (tid % D) / CH;
+  const int c = tid % CH;
+  const size_t base = (size_t)blockIdx.y * S * D;
+  const int nspan = (S + 127) / 128;
+  const int first = rank * per, last = min(nspan, first + per);
+  for (int span0 = first; span0 < last; span0 += MEAN_SLOTS) {
+    const int span = span0 + slot;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    if (span < last) {
+      const int t0 = span * 128 + g * 16;
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        float x[8][8];
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+          if (t0 + half * 8 + t < S) load8<DTYPE>(K, base + (size_t)(t0 + half * 8 + t) * D + c * 8, x[t]);
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+          if (t0 + half * 8 + t < S) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] += x[t][i];
+          }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) run_sums[slot][g][c * 8 + i] = acc[i];
+    __syncthreads();
+    if (span < last) {
+      // thread (slot, d): the 8 run sums of its span, left to right
+      const int d = tid % D;
+      float sum = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < 8; gg++) sum += run_sums[slot][gg][d];
+      my_spans[(size_t)(span - first) * D + d] = sum;
+    }
+    __syncthreads();  // run_sums is rewritten by the next round
+  }
+  cluster.sync();  // every CTA's span sums are in place
+  if (rank == 0) {
+    // all threads fetch the other CTAs' sums side by side (remote loads are slow one at a time) ...
+    float* all_spans = my_spans + (size_t)per * D;  // [nspan][D]
+    for (int i = tid; i < nspan * D; i += MEAN_SLOTS * D) {
+      const int sp = i / D, r = sp / per;
+      const float* theirs = cluster.map_shared_rank(my_spans, r);
+      all_spans[i] = theirs[(size_t)(sp - r * per) * D + (i - sp * D)];
+    }
+    __syncthreads();
+    // ... and one thread per channel adds them in span order
+    if (tid < D) {
+      float total = 0.f;
+      for (int sp = 0; sp < nspan; sp++) total += all_spans[(size_t)sp * D + tid];
+      k_mean[(size_t)blockIdx.y * D + tid] = total * (1.0f / (float)S);
+    }
+  }
+  cluster.sync();  // nobody's shared memory goes away while CTA 0 reads it
 }
 
 // One CTA per (tensor row block of 128 tokens, bh).  blockIdx.y < BHq: Q, else K.
@@ -348,7 +424,39 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
   const int bhq = a.B * a.Hq, bhk = a.B * a.Hkv;
   *launches = 0;
   if (a.smooth) {
-    k_mean_kernel<DTYPE, D><<<bhk, MEAN_SLOTS * D, 0, stream>>>(a.k, a.k_mean, a.S);
+    const int per = (nblk + MEAN_CLUSTER - 1) / MEAN_CLUSTER;  // spans per CTA of a cluster
+    const size_t span_bytes = (size_t)per * D * sizeof(float);
+    const size_t mean_smem = span_bytes + (size_t)nblk * D * sizeof(float);
+    // one CTA per pair streams well once there are about as many pairs as SMs; the cluster form is for the
+    // few-pair calls (a chunk of the streamed host path, a single sequence), where it fills one wave
+    if (bhk * MEAN_CLUSTER <= 148 && nblk >= 2 * MEAN_CLUSTER && mean_smem <= 40 * 1024) {
+      // 16 KB of static shared memory plus up to 40 KB here: above the 48 KB a kernel gets without asking
+      static bool mean_configured[64] = {};
+      int mdev = 0;
+      cudaError_t me = cudaGetDevice(&mdev);
+      if (me != cudaSuccess) return me;
+      if (mdev < 64 && !mean_configured[mdev]) {
+        me = cudaFuncSetAttribute(k_mean_cluster_kernel<DTYPE, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 40 * 1024);
+        if (me != cudaSuccess) return me;
+        mean_configured[mdev] = true;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(MEAN_CLUSTER, bhk, 1);
+      cfg.blockDim = dim3(MEAN_SLOTS * D, 1, 1);
+      cfg.dynamicSmemBytes = mean_smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = MEAN_CLUSTER;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaError_t le = cudaLaunchKernelEx(&cfg, k_mean_cluster_kernel<DTYPE, D>, a.k, a.k_mean, a.S, per);
+      if (le != cudaSuccess) return le;
+    } else {  // short sequences: one CTA per (batch, kv head) pair
+      k_mean_kernel<DTYPE, D><<<bhk, MEAN_SLOTS * D, 0, stream>>>(a.k, a.k_mean, a.S);
+    }
     (*launches)++;
   } else {
     cudaError_t e = cudaMemsetAsync(a.k_mean, 0, sizeof(float) * (size_t)bhk * D, stream);

@@ -166,7 +166,9 @@ def test_fully_masked_row_returns_mean_of_v(ops, oracle_lib):
 # ------------------------------------------------------------------------------- Sage prologue
 PROLOGUE_SHAPES = [(1, 2, 2, 256, 128, True), (2, 4, 2, 300, 128, True), (1, 2, 2, 197, 64, True),
                    (1, 2, 1, 1000, 128, False), (1, 3, 3, 1, 128, True), (1, 2, 2, 129, 64, False),
-                   (1, 2, 2, 4096, 128, True)]
+                   (1, 2, 2, 4096, 128, True),
+                   # the K mean over a cluster of CTAs with a ragged split of the spans; then too many heads for it
+                   (1, 2, 1, 2500, 128, True), (1, 20, 20, 2048, 64, True)]
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,S,D,bf16", PROLOGUE_SHAPES)
