@@ -9,7 +9,7 @@ from pathlib import Path
 
 LIB_DIR = Path(__file__).resolve().parent / "lib"
 
-MODE_EXACT_F32, MODE_TF32, MODE_BF16, MODE_SAGE_INT8 = 0, 1, 2, 3
+MODE_EXACT_F32, MODE_TF32, MODE_BF16, MODE_SAGE_INT8, MODE_SAGE_FP8 = 0, 1, 2, 3, 4
 DTYPE_F32, DTYPE_BF16 = 0, 1
 
 AR_OK = 0
@@ -31,7 +31,9 @@ SYMBOLS = (
     "ar_attn_workspace_bytes",
     "ar_attn_forward",
     "ar_sage_quantize",
+    "ar_sage_quantize_fp8",
     "ar_sage_attention_prequantized",
+    "ar_sage_attention_prequantized_fp8",
     "ar_sage_forward_static",
     "ar_attn_last_status",
     "ar_attn_selections",
@@ -70,6 +72,10 @@ def load() -> ctypes.CDLL:
     L.ar_sage_quantize.restype = ci
     L.ar_sage_attention_prequantized.argtypes = [p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]
     L.ar_sage_attention_prequantized.restype = ci
+    L.ar_sage_quantize_fp8.argtypes = L.ar_sage_quantize.argtypes
+    L.ar_sage_quantize_fp8.restype = ci
+    L.ar_sage_attention_prequantized_fp8.argtypes = L.ar_sage_attention_prequantized.argtypes
+    L.ar_sage_attention_prequantized_fp8.restype = ci
     L.ar_sage_forward_static.argtypes = [ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p]
     L.ar_sage_forward_static.restype = ci
     L.ar_attn_last_status.argtypes = [p, p]

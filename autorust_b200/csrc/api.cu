@@ -11,7 +11,7 @@
 
 namespace {
 
-std::atomic<uint64_t> g_selected[4];
+std::atomic<uint64_t> g_selected[5];
 std::atomic<uint64_t> g_launches;
 
 // Device status block used when the caller passes no workspace (word 0 is the status word).
@@ -111,6 +111,7 @@ bool mode_has_kernel(int mode, int dtype, int64_t B, int64_t Hq, int64_t S, int6
     case AR_MODE_TF32: return dtype == AR_DTYPE_F32 && ar::attn_tc_has(ar::TC_TF32, (int)D);
     case AR_MODE_BF16: return dtype == AR_DTYPE_BF16 && ar::attn_tc_has(ar::TC_BF16, (int)D);
     case AR_MODE_SAGE_INT8: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE, (int)D);
+    case AR_MODE_SAGE_FP8: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE_FP8, (int)D);
     default: return false;
   }
 }
@@ -128,7 +129,7 @@ namespace ar {
 // Lets other translation units of the library feed the launch counters.
 void count_launches(int mode, int kernels) {
   g_launches += (uint64_t)kernels;
-  if (mode >= 0 && mode < 4) g_selected[mode]++;
+  if (mode >= 0 && mode < 5) g_selected[mode]++;
 }
 }  // namespace ar
 
@@ -147,15 +148,16 @@ int ar_attn_supported(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, i
 
 size_t ar_attn_workspace_bytes(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
   if (check_shape(B, Hq, Hkv, S, D) != AR_OK) return 0;
-  if (mode == AR_MODE_SAGE_INT8) return sage_layout(dtype, B, Hq, Hkv, S, D).total;
+  if (mode == AR_MODE_SAGE_INT8 || mode == AR_MODE_SAGE_FP8) return sage_layout(dtype, B, Hq, Hkv, S, D).total;
   if (mode == AR_MODE_TF32)  // status block + the transposed copy of V, rows padded to a multiple of 4 keys
     return STATUS_BYTES + align_up(sizeof(float) * (size_t)(B * Hkv * D) * (size_t)((S + 3) / 4 * 4), 256);
   return 0;
 }
 
-int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale, float* k_scale,
-                     float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
-                     void* cu_stream) {
+namespace {
+int sage_quantize_any(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale, float* k_scale,
+                      float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
+                      int fp8, void* cu_stream) {
   if (!q || !k || !q8 || !k8 || !q_scale || !k_scale || !k_mean) return AR_ERR_NULL;
   int rc = check_shape(B, Hq, Hkv, S, D);
   if (rc != AR_OK) return rc;
@@ -164,6 +166,7 @@ int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t
   if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   ar::PrologueArgs a{q, k, dtype, q8, k8, q_scale, k_scale, k_mean, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, smooth};
+  a.fp8 = fp8;
   // this entry point has no workspace: its status goes to the library's own word (ar_attn_last_status(NULL, ...))
   a.status = status_ptr(nullptr);
   if (!a.status || cudaMemsetAsync(a.status, 0, sizeof(uint32_t), (cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;
@@ -171,6 +174,19 @@ int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t
   cudaError_t e = ar::launch_sage_prologue(a, (cudaStream_t)cu_stream, &launches);
   g_launches += (uint64_t)launches;
   return e == cudaSuccess ? AR_OK : AR_ERR_CUDA;
+}
+}  // namespace
+
+int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale, float* k_scale,
+                     float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
+                     void* cu_stream) {
+  return sage_quantize_any(q, k, dtype, q8, k8, q_scale, k_scale, k_mean, B, Hq, Hkv, S, D, block, smooth, 0, cu_stream);
+}
+int ar_sage_quantize_fp8(const void* q, const void* k, int dtype, uint8_t* q8, uint8_t* k8, float* q_scale,
+                         float* k_scale, float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                         int block, int smooth, void* cu_stream) {
+  return sage_quantize_any(q, k, dtype, (int8_t*)q8, (int8_t*)k8, q_scale, k_scale, k_mean, B, Hq, Hkv, S, D, block, smooth,
+                           1, cu_stream);
 }
 
 int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
@@ -226,7 +242,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
         !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B * Hkv, S, D) ||
         !make_map_ex(&a.tm_v, vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, S_pad, D, B * Hkv, 32, (int)D))
       return AR_ERR_CUDA;
-  } else {  // AR_MODE_SAGE_INT8
+  } else {  // AR_MODE_SAGE_INT8, AR_MODE_SAGE_FP8
     const SageLayout L = sage_layout(dtype, B, Hq, Hkv, S, D);
     uint8_t* ws = (uint8_t*)workspace;
     int8_t* q8 = (int8_t*)(ws + L.q8);
@@ -235,6 +251,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     float* ks = (float*)(ws + L.k_scale);
     float* km = (float*)(ws + L.k_mean);
     ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
+    p.fp8 = mode == AR_MODE_SAGE_FP8;
     p.status = status;  // shared with the attention kernel: cleared once, before the first launch
     int launches = 0;
     if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
@@ -249,7 +266,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
       if (e != cudaSuccess) return AR_ERR_CUDA;
       v16 = ws + L.v16;
     }
-    a.mode = ar::TC_SAGE;
+    a.mode = mode == AR_MODE_SAGE_FP8 ? ar::TC_SAGE_FP8 : ar::TC_SAGE;
     a.out_f32 = dtype == AR_DTYPE_F32;
     a.q_scale = qs;
     a.k_scale = ks;
@@ -258,7 +275,8 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
         !make_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
       return AR_ERR_CUDA;
   }
-  if (mode != AR_MODE_SAGE_INT8 && cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (mode != AR_MODE_SAGE_INT8 && mode != AR_MODE_SAGE_FP8 && cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess)
+    return AR_ERR_CUDA;
   cudaError_t e = ar::launch_attn_tc(a, stream);
   if (e != cudaSuccess) return AR_ERR_CUDA;
   g_launches++;
@@ -266,14 +284,14 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   return AR_OK;
 }
 
-int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const float* q_scale, const float* k_scale,
-                                   const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
-                                   int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
-                                   void* cu_stream) {
+namespace {
+int sage_prequantized_any(int mode, const void* q8, const void* k8, const float* q_scale, const float* k_scale,
+                          const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B, int64_t Hq,
+                          int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word, void* cu_stream) {
   if (!q8 || !k8 || !q_scale || !k_scale || !v_bf16 || !o) return AR_ERR_NULL;
   int rc = check_shape(B, Hq, Hkv, S, D);
   if (rc != AR_OK) return rc;
-  if (!mode_has_kernel(AR_MODE_SAGE_INT8, AR_DTYPE_BF16, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
+  if (!mode_has_kernel(mode, AR_DTYPE_BF16, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
   if (out_dtype != AR_DTYPE_F32 && out_dtype != AR_DTYPE_BF16) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q8) || !aligned16(k8) || !aligned16(v_bf16) || !aligned16(o)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
@@ -282,7 +300,7 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
   if (!status) return AR_ERR_CUDA;
   ar::TcArgs a;
   memset(&a, 0, sizeof(a));
-  a.mode = ar::TC_SAGE;
+  a.mode = mode == AR_MODE_SAGE_FP8 ? ar::TC_SAGE_FP8 : ar::TC_SAGE;
   a.D = (int)D;
   a.out = o;
   a.out_f32 = out_dtype == AR_DTYPE_F32;
@@ -299,8 +317,24 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
   if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
   if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;
   g_launches++;
-  g_selected[AR_MODE_SAGE_INT8]++;
+  g_selected[mode]++;
   return AR_OK;
+}
+}  // namespace
+
+int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const float* q_scale, const float* k_scale,
+                                   const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
+                                   int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
+                                   void* cu_stream) {
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, out_dtype, mask, B, Hq, Hkv, S, D,
+                               causal, status_word, cu_stream);
+}
+int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, const float* q_scale,
+                                       const float* k_scale, const void* v_bf16, void* o, int out_dtype,
+                                       const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                                       int causal, void* status_word, void* cu_stream) {
+  return sage_prequantized_any(AR_MODE_SAGE_FP8, q8, k8, q_scale, k_scale, v_bf16, o, out_dtype, mask, B, Hq, Hkv, S, D,
+                               causal, status_word, cu_stream);
 }
 
 int ar_attn_last_status(void* workspace, void* cu_stream) {
@@ -324,7 +358,7 @@ int ar_debug_read_trace(void* workspace, unsigned long long* out31, int clear) {
 }
 #endif
 
-uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 4) ? g_selected[mode].load() : 0; }
+uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 5) ? g_selected[mode].load() : 0; }
 uint64_t ar_attn_launch_count(void) { return g_launches.load(); }
 
 const char* ar_attn_strerror(int status) {

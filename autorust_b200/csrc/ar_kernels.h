@@ -7,12 +7,12 @@
 namespace ar {
 
 // Tensor-core forward (attn_fwd_tc.cu): bf16 or Sage INT8 QK^T, bf16 PV.
-enum TcMode { TC_BF16 = 0, TC_SAGE = 1, TC_TF32 = 2 };
+enum TcMode { TC_BF16 = 0, TC_SAGE = 1, TC_TF32 = 2, TC_SAGE_FP8 = 3 };  // TC_SAGE: INT8 operands; TC_SAGE_FP8: E4M3
 
 struct TcArgs {
   int mode;             // TcMode
   int D;                // 64 or 128
-  CUtensorMap tm_q;     // [B*Hq, S, D]   bf16 (TC_BF16) or int8 (TC_SAGE), 128-byte swizzle, box 128 rows
+  CUtensorMap tm_q;     // [B*Hq, S, D]   bf16 (TC_BF16), int8 (TC_SAGE) or e4m3 (TC_SAGE_FP8), 128-byte swizzle, box 128 rows
   CUtensorMap tm_k;     // [B*Hkv, S, D]  same element type as tm_q
   CUtensorMap tm_v;     // [B*Hkv, S, D]  bf16; TC_TF32: the transposed copy [B*Hkv, D, S_pad] f32, box 32 keys x D rows
   void* out;            // [B*Hq, S, D]   bf16 or f32
@@ -45,6 +45,7 @@ struct PrologueArgs {
   float *q_scale, *k_scale, *k_mean;
   int B, Hq, Hkv, S, D;
   int smooth;
+  int fp8 = 0;                 // 0: INT8, scale amax/127 (the default); 1: FP8 E4M3, scale amax/448
   uint32_t* status = nullptr;  // device word a bounded wait that ran out is recorded in; cleared by the caller
 };
 // Returns the number of kernels launched through *launches.

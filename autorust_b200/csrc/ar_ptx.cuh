@@ -173,7 +173,7 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
-enum MmaKind { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
+enum MmaKind { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2, KIND_F8 = 3 };
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]
 template <int KIND>
@@ -239,6 +239,13 @@ __device__ __forceinline__ void mma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
         "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
+  } else if constexpr (KIND == KIND_F8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
   } else {
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
@@ -268,7 +275,7 @@ __device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, ui
 
 // Instruction descriptor (32 bit) for kind::f16 / kind::tf32 / kind::i8, dense, no negate.
 //   [4,6) D format: 0 f16, 1 f32, 2 s32      [7,10) A format   [10,13) B format
-//   (f16 kind: 0 f16, 1 bf16; tf32 kind: 2; i8 kind: 0 u8, 1 s8)
+//   (f16 kind: 0 f16, 1 bf16; tf32 kind: 2; i8 kind: 0 u8, 1 s8; f8f6f4 kind: 0 e4m3, 1 e5m2)
 //   [15] A major (0 = K, 1 = MN)   [16] B major   [17,23) N>>3   [24,29) M>>4
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t dfmt, uint32_t afmt, uint32_t bfmt, uint32_t a_mn,
                                                   uint32_t b_mn, uint32_t M, uint32_t N) {

@@ -32,6 +32,9 @@
 // Sage: S_t is the exact s32 product of the INT8 tiles the prologue wrote; it is dequantised
 // by q_scale[q block] * k_scale[k block] / sqrt(D), one scalar per 128x128 tile
 // (src/runtime/cuda_flash_sage.rs:315-322 does the same per row pair).
+// Sage FP8 (the variant the reference selects on sm_89 and later, src/runtime/cuda_flash_sage.rs:77-79,92-97):
+// Q and K are E4M3 with scales amax / 448, QK^T is kind::f8f6f4 with f32 accumulation, and the softmax reads
+// f32 scores as in the bf16 kernel -- no integer conversion.
 #include "ar_kernels.h"
 #include "ar_ptx.cuh"
 
@@ -221,7 +224,8 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
 
 template <int MODE, int D>
 struct Cfg {
-  static constexpr int QK_ESIZE = MODE == TC_SAGE ? 1 : MODE == TC_TF32 ? 4 : 2;
+  static constexpr bool QUANT = MODE == TC_SAGE || MODE == TC_SAGE_FP8;  // 8-bit Q and K with per-block scales
+  static constexpr int QK_ESIZE = QUANT ? 1 : MODE == TC_TF32 ? 4 : 2;
   static constexpr int QK_ROW_BYTES = D * QK_ESIZE;
   static_assert(QK_ROW_BYTES % 128 == 0, "Q/K rows must fill whole 128-byte swizzle atoms");
   static constexpr int QK_BOXES = QK_ROW_BYTES / 128;
@@ -242,11 +246,12 @@ struct Cfg {
   static constexpr int NUM_BARS = 2 + 4 * STAGES + 4 + 2 * NPART;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-  static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
+  static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_SAGE_FP8 ? KIND_F8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
   static constexpr int PV_KIND = MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
-  static constexpr uint32_t IDESC_QK = MODE == TC_SAGE   ? make_idesc(2, 1, 1, 0, 0, BM, BN)
-                                       : MODE == TC_TF32 ? make_idesc(1, 2, 2, 0, 0, BM, BN)
-                                                         : make_idesc(1, 1, 1, 0, 0, BM, BN);
+  static constexpr uint32_t IDESC_QK = MODE == TC_SAGE       ? make_idesc(2, 1, 1, 0, 0, BM, BN)  // s8 x s8 -> s32
+                                       : MODE == TC_SAGE_FP8 ? make_idesc(1, 0, 0, 0, 0, BM, BN)  // e4m3 x e4m3 -> f32
+                                       : MODE == TC_TF32     ? make_idesc(1, 2, 2, 0, 0, BM, BN)
+                                                             : make_idesc(1, 1, 1, 0, 0, BM, BN);
   static constexpr uint32_t IDESC_PV = MODE == TC_TF32 ? make_idesc(1, 2, 2, 0, 0, BM, D) : make_idesc(1, 1, 1, 0, 1, BM, D);
 };
 
@@ -492,7 +497,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float scale_log2 = (1.0f / sqrtf((float)D)) * LOG2E;
     const int nblk = nkv_all;
     float qs = 1.f;
-    if (MODE == TC_SAGE && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
+    if (C::QUANT && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
     float m = NEG, l = 0.f;
     TR_DECL(sm_wait_s); TR_DECL(sm_ld); TR_DECL(sm_compute); TR_DECL(sm_st); TR_DECL(sm_steps); TR_T(tsm_begin);
     bool ok = true;
@@ -513,7 +518,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       TR_T(ts2); TR_ADD(sm_ld, ts1, ts2);
       if (r == 0) TL(t, j, 2);
       float c = scale_log2;
-      if (MODE == TC_SAGE) c *= qs * k_scale[(size_t)kvbh * nblk + j];
+      if (C::QUANT) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
       // Two separate instantiations: the interior step must not carry the merge points of the
@@ -605,7 +610,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
 
 bool attn_tc_has(int mode, int D) {
   if (mode == TC_BF16) return D == 64 || D == 128;
-  if (mode == TC_SAGE) return D == 128;
+  if (mode == TC_SAGE || mode == TC_SAGE_FP8) return D == 128;
   if (mode == TC_TF32) return D == 64;  // the reference's only head size; two f32 query tiles of D=128 do not fit
   return false;
 }
@@ -614,6 +619,7 @@ cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
   if (a.mode == TC_BF16 && a.D == 128) return launch_one<TC_BF16, 128>(a, stream);
   if (a.mode == TC_BF16 && a.D == 64) return launch_one<TC_BF16, 64>(a, stream);
   if (a.mode == TC_SAGE && a.D == 128) return launch_one<TC_SAGE, 128>(a, stream);
+  if (a.mode == TC_SAGE_FP8 && a.D == 128) return launch_one<TC_SAGE_FP8, 128>(a, stream);
   if (a.mode == TC_TF32 && a.D == 64) return launch_one<TC_TF32, 64>(a, stream);
   return cudaErrorInvalidValue;
 }

@@ -5,7 +5,9 @@
 // inv = 1 / scale, q8 = clamp(rn(x * inv), -127, 127).  The reference applies it per query row /
 // per key row in shared memory, once per query block, and never smooths K; here it runs once per
 // tensor, over blocks of 128 tokens (the MMA tile), after subtracting the token mean of K, and
-// writes INT8 tensors and f32 scales to global memory for the attention kernel.
+// writes INT8 tensors and f32 scales to global memory for the attention kernel.  The FP8 form (the reference's
+// AR_FP8 variant, src/runtime/cuda_flash_sage.rs:92-97,126-129) differs in two places only: scale = amax / 448 and
+// the rounding is cvt.rn.satfinite to E4M3.
 //
 // Both kernels are bandwidth-bound and move 16 bytes per thread per access.  Arithmetic that
 // decides bits is kept free of fused multiply-adds and fast-math: every tensor is widened to f32
@@ -37,6 +39,30 @@ __device__ __forceinline__ void load8(const void* base, size_t idx, float* x) {
     x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
     x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
   }
+}
+
+// Eight values times inv, quantised and packed into eight bytes.  INT8: round to nearest even through the
+// bits of 1.5 * 2^23 (exact for |y| < 2^22, here |y| <= 127.5; the same integer __float2int_rn returns,
+// without its quarter-rate conversion unit), clamped to +-127.  FP8: cvt.rn.satfinite to E4M3 (+-448).
+__device__ __forceinline__ uint2 quantize8(const float (&x)[8], float inv, int fp8) {
+  uint32_t w[2] = {0u, 0u};
+  if (fp8) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float lo = __fmul_rn(x[2 * i], inv), hi = __fmul_rn(x[2 * i + 1], inv);
+      uint16_t h;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h) : "f"(hi), "f"(lo));  // first source -> upper byte
+      w[i >> 1] |= (uint32_t)h << (16 * (i & 1));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      int v = __float_as_int(__fadd_rn(__fmul_rn(x[i], inv), 12582912.0f)) - 0x4B400000;
+      v = max(-127, min(127, v));
+      w[i >> 2] |= ((uint32_t)v & 0xffu) << (8 * (i & 3));
+    }
+  }
+  return make_uint2(w[0], w[1]);
 }
 
 // k_mean[bh, d]: one CTA per (batch, kv head); MEAN_SLOTS spans of 128 tokens in flight per round.
@@ -177,7 +203,7 @@ template <int DTYPE, int D>
 __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ Q, const void* __restrict__ K,
                                                        const float* __restrict__ k_mean, int8_t* __restrict__ q8,
                                                        int8_t* __restrict__ k8, float* __restrict__ q_scale,
-                                                       float* __restrict__ k_scale, int S, int BHq, int smooth) {
+                                                       float* __restrict__ k_scale, int S, int BHq, int smooth, int fp8) {
   constexpr int CH = D / 8;
   constexpr int NCHUNK = 128 * CH / 256;  // chunks per thread: 8 (D=128) or 4 (D=64)
   __shared__ float warp_max[8];
@@ -218,23 +244,14 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
   amax = warp_max[0];
 #pragma unroll
   for (int w = 1; w < 8; w++) amax = fmaxf(amax, warp_max[w]);
-  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  const float scale = amax > 0.f ? __fdiv_rn(amax, fp8 ? 448.0f : 127.0f) : 1.0f;
   const float inv = __fdiv_rn(1.0f, scale);
   if (tid == 0) (is_k ? k_scale : q_scale)[(size_t)bh * nblk + blockIdx.x] = scale;
 #pragma unroll
   for (int n = 0; n < NCHUNK; n++) {
     const int tok = t0 + (tid + 256 * n) / CH;
     if (tok < S) {
-      uint32_t w[2] = {0u, 0u};
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        // round to nearest even through the bits of 1.5 * 2^23: exact for |y| < 2^22 (here |y| <= 127.5),
-        // the same integer __float2int_rn returns, without its quarter-rate conversion unit
-        int v = __float_as_int(__fadd_rn(__fmul_rn(x[n][i], inv), 12582912.0f)) - 0x4B400000;
-        v = max(-127, min(127, v));
-        w[i >> 2] |= ((uint32_t)v & 0xffu) << (8 * (i & 3));
-      }
-      *(uint2*)(dst + base + (size_t)tok * D + c * 8) = make_uint2(w[0], w[1]);
+      *(uint2*)(dst + base + (size_t)tok * D + c * 8) = quantize8(x[n], inv, fp8);
     }
   }
 }
@@ -276,7 +293,7 @@ __global__ void __launch_bounds__(256) quantize_pipe_kernel(const void* __restri
                                                             const float* __restrict__ k_mean, int8_t* __restrict__ q8,
                                                             int8_t* __restrict__ k8, float* __restrict__ q_scale,
                                                             float* __restrict__ k_scale, int S, int BHq, int BHk,
-                                                            int smooth, uint32_t* status) {
+                                                            int smooth, int fp8, uint32_t* status) {
   using P = QuantPipe<DTYPE, D>;
   constexpr int CH = D / 8;
   constexpr int NCHUNK = 128 * CH / 256;
@@ -361,7 +378,7 @@ __global__ void __launch_bounds__(256) quantize_pipe_kernel(const void* __restri
     amax = warp_max[it & 1][0];
 #pragma unroll
     for (int wv = 1; wv < 8; wv++) amax = fmaxf(amax, warp_max[it & 1][wv]);
-    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float scale = amax > 0.f ? __fdiv_rn(amax, fp8 ? 448.0f : 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, scale);
     if (tid == 0) (is_k ? k_scale : q_scale)[(size_t)bh * nblk + blk] = scale;
     int8_t* dst = (is_k ? k8 : q8) + ((size_t)bh * S + t0) * D;
@@ -369,14 +386,7 @@ __global__ void __launch_bounds__(256) quantize_pipe_kernel(const void* __restri
     for (int n = 0; n < NCHUNK; n++) {
       const int idx = tid + 256 * n;
       if (t0 + idx / CH < S) {
-        uint32_t wd[2] = {0u, 0u};
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          int v = __float_as_int(__fadd_rn(__fmul_rn(x[n][i], inv), 12582912.0f)) - 0x4B400000;
-          v = max(-127, min(127, v));
-          wd[i >> 2] |= ((uint32_t)v & 0xffu) << (8 * (i & 3));
-        }
-        *(uint2*)(dst + (size_t)idx * 8) = make_uint2(wd[0], wd[1]);
+        *(uint2*)(dst + (size_t)idx * 8) = quantize8(x[n], inv, fp8);
       }
     }
   }
@@ -484,10 +494,10 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
     int grid = (dev < 64 ? sm_count[dev] : 148) * P::CTAS_PER_SM;
     if (grid > items) grid = items;
     kern<<<grid, 256, P::SMEM_BYTES, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale, a.k_scale, a.S, bhq, bhk,
-                                               a.smooth, a.status);
+                                               a.smooth, a.fp8, a.status);
   } else {
     quantize_kernel<DTYPE, D><<<dim3(nblk, bhq + bhk, 1), 256, 0, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale,
-                                                                           a.k_scale, a.S, bhq, a.smooth);
+                                                                           a.k_scale, a.S, bhq, a.smooth, a.fp8);
   }
   (*launches)++;
   return cudaGetLastError();

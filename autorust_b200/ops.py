@@ -9,7 +9,7 @@ import torch
 from . import _abi
 
 _MODE_NAMES = {"exact": _abi.MODE_EXACT_F32, "tf32": _abi.MODE_TF32, "bf16": _abi.MODE_BF16,
-               "sage": _abi.MODE_SAGE_INT8}
+               "sage": _abi.MODE_SAGE_INT8, "sage_fp8": _abi.MODE_SAGE_FP8}
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -82,30 +82,32 @@ def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
     return out
 
 
-def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=None):
-    """The Sage prologue on its own: returns (q8, k8, q_scale, k_scale, k_mean)."""
+def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=None, fp8: bool = False):
+    """The Sage prologue on its own: returns (q8, k8, q_scale, k_scale, k_mean).  fp8: E4M3 bit patterns in
+    uint8 tensors and scales amax / 448 instead of INT8 and amax / 127."""
     L = _abi.load()
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
     nblk = (S + 127) // 128
     dev = q.device
-    q8 = torch.empty(q.shape, dtype=torch.int8, device=dev)
-    k8 = torch.empty(k.shape, dtype=torch.int8, device=dev)
+    q8 = torch.empty(q.shape, dtype=torch.uint8 if fp8 else torch.int8, device=dev)
+    k8 = torch.empty(k.shape, dtype=torch.uint8 if fp8 else torch.int8, device=dev)
     qs = torch.empty((B, Hq, nblk), dtype=torch.float32, device=dev)
     ks = torch.empty((B, Hkv, nblk), dtype=torch.float32, device=dev)
     km = torch.empty((B, Hkv, D), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         s = stream if stream is not None else torch.cuda.current_stream()
-        rc = L.ar_sage_quantize(q.data_ptr(), k.data_ptr(), _dtype_code(q), q8.data_ptr(), k8.data_ptr(),
-                                qs.data_ptr(), ks.data_ptr(), km.data_ptr(), B, Hq, Hkv, S, D, 128, int(smooth),
-                                s.cuda_stream)
+        fn = L.ar_sage_quantize_fp8 if fp8 else L.ar_sage_quantize
+        rc = fn(q.data_ptr(), k.data_ptr(), _dtype_code(q), q8.data_ptr(), k8.data_ptr(), qs.data_ptr(), ks.data_ptr(),
+                km.data_ptr(), B, Hq, Hkv, S, D, 128, int(smooth), s.cuda_stream)
     _abi.check(rc, "ar_sage_quantize")
     return q8, k8, qs, ks, km
 
 
 def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None, causal=False, stream=None,
                                 out_dtype=torch.bfloat16):
-    """The Sage attention kernel alone, on the tensors sage_quantize returned (v must be bf16)."""
+    """The Sage attention kernel alone, on the tensors sage_quantize returned (v must be bf16); uint8 q8 / k8
+    (the FP8 prologue's output) select the FP8 kernel."""
     L = _abi.load()
     B, Hq, S, D = q8.shape
     Hkv = k8.shape[1]
@@ -115,10 +117,10 @@ def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None
         out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=q8.device)
     with torch.cuda.device(q8.device):
         s = stream if stream is not None else torch.cuda.current_stream()
-        rc = L.ar_sage_attention_prequantized(q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(),
-                                              v.data_ptr(), out.data_ptr(), _dtype_code(out),
-                                              mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D,
-                                              int(causal), None, s.cuda_stream)
+        fn = L.ar_sage_attention_prequantized_fp8 if q8.dtype == torch.uint8 else L.ar_sage_attention_prequantized
+        rc = fn(q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v.data_ptr(), out.data_ptr(),
+                _dtype_code(out), mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal), None,
+                s.cuda_stream)
     _abi.check(rc, "ar_sage_attention_prequantized")
     return out
 

@@ -42,7 +42,9 @@ enum ar_attn_mode {
   AR_MODE_EXACT_F32 = 0, /* scalar-FFMA f32 kernel        src/runtime/cuda_flash.rs:48-142     */
   AR_MODE_TF32 = 1,      /* f32 tensors, TF32 tensor core src/runtime/cuda_flash_tc.rs:92-376  */
   AR_MODE_BF16 = 2,      /* bf16 in/out, f32 softmax      src/runtime/cuda_flash_bf16.rs:98-428 */
-  AR_MODE_SAGE_INT8 = 3  /* INT8 QK^T, bf16 PV            src/runtime/cuda_flash_sage.rs:86-415 */
+  AR_MODE_SAGE_INT8 = 3, /* INT8 QK^T, bf16 PV            src/runtime/cuda_flash_sage.rs:86-415 */
+  AR_MODE_SAGE_FP8 = 4   /* FP8 E4M3 QK^T, bf16 PV: the AR_FP8 variant of the same file (:92-97,126-129),
+                            the one the reference's dispatcher takes on sm_89 and later (:77-79) */
 };
 
 /* Element types of q/k/v/o. */
@@ -83,8 +85,8 @@ size_t ar_attn_workspace_bytes(int mode, int dtype, int64_t B, int64_t Hq, int64
  * Replaces `cuda_flash{,_tc,_bf16,_sage}::run_ex` (src/runtime/cuda_flash_bf16.rs:495-580,
  * cuda_flash_tc.rs:446-527, cuda_flash_sage.rs:452-516, cuda_flash.rs:203-285).
  * dtype: element type of q, k, v and o.  EXACT_F32 and TF32 want AR_DTYPE_F32, BF16 wants
- * AR_DTYPE_BF16, SAGE_INT8 takes either.  Sage runs the quantise prologue
- * (ar_sage_quantize, 128-token blocks, K smoothing) into the workspace first.
+ * AR_DTYPE_BF16, SAGE_INT8 and SAGE_FP8 take either.  Sage runs the quantise prologue
+ * (ar_sage_quantize[_fp8], 128-token blocks, K smoothing) into the workspace first.
  * workspace may be NULL when ar_attn_workspace_bytes() is 0. */
 int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
                     int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
@@ -101,6 +103,13 @@ int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t
                      float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
                      void* cu_stream);
 
+/* The same prologue for AR_MODE_SAGE_FP8: scale = amax > 0 ? amax / 448 : 1 and q8 = E4M3(x * (1 / scale)),
+ * round to nearest even, saturating at +-448 (`__nv_cvt_float2_to_fp8x2(.., __NV_SATFINITE, __NV_E4M3)` in
+ * `ar_q4`, src/runtime/cuda_flash_sage.rs:126-129).  q8, k8 hold E4M3 bit patterns; everything else as above. */
+int ar_sage_quantize_fp8(const void* q, const void* k, int dtype, uint8_t* q8, uint8_t* k8, float* q_scale,
+                         float* k_scale, float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                         int block, int smooth, void* cu_stream);
+
 /* The Sage attention kernel alone, on tensors ar_sage_quantize already produced (for callers that
  * keep quantised K across calls, and for timing the kernel apart from its prologue): INT8 QK^T,
  * dequantised per 128x128 tile by q_scale * k_scale / sqrt(D), online softmax, bf16 P.V.
@@ -111,6 +120,13 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
                                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
                                    void* cu_stream);
+
+/* The FP8 attention kernel alone, on tensors ar_sage_quantize_fp8 produced: E4M3 QK^T with f32 accumulation
+ * (`ar_mma_qk` under AR_FP8, src/runtime/cuda_flash_sage.rs:140-160), otherwise as above. */
+int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, const float* q_scale,
+                                       const float* k_scale, const void* v_bf16, void* o, int out_dtype,
+                                       const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                                       int causal, void* status_word, void* cu_stream);
 
 /* Size of the scratch ar_sage_forward_static keeps inside the library, per GPU. */
 #define AR_SAGE_STATIC_SCRATCH_BYTES (32u << 20)

@@ -40,6 +40,12 @@ def lib() -> ctypes.CDLL:
         L.ar_oracle_flash.restype = ci
         L.ar_oracle_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, i64, ci]
         L.ar_oracle_sage_quantize.restype = ci
+        L.ar_oracle_sage_quantize_fp8.argtypes = L.ar_oracle_sage_quantize.argtypes
+        L.ar_oracle_sage_quantize_fp8.restype = ci
+        L.ar_oracle_f32_to_e4m3.argtypes = [p, p, i64]
+        L.ar_oracle_f32_to_e4m3.restype = None
+        L.ar_oracle_e4m3_to_f32.argtypes = [p, p, i64]
+        L.ar_oracle_e4m3_to_f32.restype = None
         L.ar_oracle_rows_f32.argtypes = [ci, p, p, i64, p, p, p, i64, i64, ci]
         L.ar_oracle_rows_f32.restype = ci
         L.ar_cpu_sdpa_f32.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, ci, i64, i64]
@@ -90,7 +96,7 @@ def sdpa_f32(q, k, v, mask=None, causal=False):
 
 
 def flash(mode: int, q, k, v, mask=None, causal=False, block=128, smooth=True, out_bf16=None):
-    """The fused kernels' semantics with mode rounding: 0 exact f32, 1 tf32, 2 bf16, 3 sage.
+    """The fused kernels' semantics with mode rounding: 0 exact f32, 1 tf32, 2 bf16, 3 sage (INT8), 4 sage FP8.
     q/k/v: float32 arrays, or uint16 arrays holding bf16 bit patterns.  Returns f32, or uint16 bf16
     bits when the output dtype is bf16 (default: same as the input dtype)."""
     in_bf16 = q.dtype == np.uint16
@@ -113,8 +119,23 @@ def flash(mode: int, q, k, v, mask=None, causal=False, block=128, smooth=True, o
     return out
 
 
-def sage_quantize(q, k, block=128, smooth=True):
-    """Returns (q8, k8, q_scale, k_scale, k_mean) as the prologue specifies them."""
+def f32_to_e4m3(x):
+    """E4M3 bit patterns (uint8) of a float32 array: round to nearest even, saturating at +-448."""
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(x.shape, np.uint8)
+    lib().ar_oracle_f32_to_e4m3(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def e4m3_to_f32(b):
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(b.shape, np.float32)
+    lib().ar_oracle_e4m3_to_f32(_ptr(b), _ptr(out), b.size)
+    return out
+
+
+def sage_quantize(q, k, block=128, smooth=True, fp8=False):
+    """Returns (q8, k8, q_scale, k_scale, k_mean) as the prologue specifies them (fp8: E4M3 bits in uint8)."""
     in_bf16 = q.dtype == np.uint16
     dt = np.uint16 if in_bf16 else np.float32
     q = np.ascontiguousarray(q, dt)
@@ -122,13 +143,14 @@ def sage_quantize(q, k, block=128, smooth=True):
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
     nblk = (S + block - 1) // block
-    q8 = np.zeros(q.shape, np.int8)
-    k8 = np.zeros(k.shape, np.int8)
+    q8 = np.zeros(q.shape, np.uint8 if fp8 else np.int8)
+    k8 = np.zeros(k.shape, np.uint8 if fp8 else np.int8)
     qs = np.zeros((B, Hq, nblk), np.float32)
     ks = np.zeros((B, Hkv, nblk), np.float32)
     km = np.zeros((B, Hkv, D), np.float32)
-    rc = lib().ar_oracle_sage_quantize(_ptr(q), _ptr(k), BF16 if in_bf16 else F32, _ptr(q8), _ptr(k8), _ptr(qs),
-                                       _ptr(ks), _ptr(km), B, Hq, Hkv, S, D, block, int(smooth))
+    fn = lib().ar_oracle_sage_quantize_fp8 if fp8 else lib().ar_oracle_sage_quantize
+    rc = fn(_ptr(q), _ptr(k), BF16 if in_bf16 else F32, _ptr(q8), _ptr(k8), _ptr(qs), _ptr(ks), _ptr(km), B, Hq, Hkv, S, D,
+            block, int(smooth))
     if rc != 0:
         raise ValueError("ar_oracle_sage_quantize rejected the arguments")
     return q8, k8, qs, ks, km

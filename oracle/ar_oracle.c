@@ -150,8 +150,50 @@ int ar_oracle_sdpa_f32(const float* q, const float* k, const float* v, const flo
  * q_scale: [B,Hq,nblk]  k_scale: [B,Hkv,nblk]  k_mean: [B,Hkv,D]
  * nblk = ceil(S / block).  smooth = 0 leaves K as it is (k_mean written as 0).
  * ------------------------------------------------------------------------ */
+/* FP8 E4M3 (the OCP "FN" form the reference uses: __NV_E4M3, src/runtime/cuda_flash_sage.rs:126-129): 1 sign,
+ * 4 exponent bits (bias 7), 3 mantissa bits, no infinities, 0x7f = NaN, largest finite 448 = 0x7e, subnormals
+ * m/8 * 2^-6.  Encoding rounds to nearest, ties to even, and saturates at +-448 (__NV_SATFINITE); it reproduces
+ * the value table of the reference's host emulation (tests/sage_int8.rs:245-262). */
+static inline uint8_t f32_to_e4m3(float x) {
+  const uint8_t sign = signbit(x) ? 0x80 : 0x00;
+  float a = fabsf(x);
+  if (isnan(a)) return (uint8_t)(sign | 0x7f);
+  if (a >= 448.0f) return (uint8_t)(sign | 0x7e); /* 464 and above would round past the top; 448..464 round to 448 */
+  if (a < 0.015625f) {                            /* below the smallest normal 2^-6: multiples of 2^-9 */
+    const float r = nearbyintf(a * 512.0f);       /* 0..8; 8 is the smallest normal, whose bits are 0x08 as well */
+    return (uint8_t)(sign | (uint8_t)(int)r);
+  }
+  int e;
+  const float f = frexpf(a, &e); /* a = f * 2^e, f in [0.5, 1) */
+  int ex = e - 1;                /* a = (2f) * 2^ex, 2f in [1, 2) */
+  int mant = (int)nearbyintf((2.0f * f - 1.0f) * 8.0f);
+  if (mant == 8) {
+    mant = 0;
+    ex += 1;
+  }
+  if (ex > 8 || (ex == 8 && mant == 7)) return (uint8_t)(sign | 0x7e);
+  return (uint8_t)(sign | ((ex + 7) << 3) | mant);
+}
+static inline float e4m3_to_f32(uint8_t b) {
+  const int ex = (b >> 3) & 0xf, mant = b & 7;
+  float v;
+  if (ex == 0)
+    v = ldexpf((float)mant / 8.0f, -6);
+  else if (ex == 15 && mant == 7)
+    v = NAN;
+  else
+    v = ldexpf(1.0f + (float)mant / 8.0f, ex - 7);
+  return (b & 0x80) ? -v : v;
+}
+void ar_oracle_f32_to_e4m3(const float* src, uint8_t* dst, int64_t n) {
+  for (int64_t i = 0; i < n; i++) dst[i] = f32_to_e4m3(src[i]);
+}
+void ar_oracle_e4m3_to_f32(const uint8_t* src, float* dst, int64_t n) {
+  for (int64_t i = 0; i < n; i++) dst[i] = e4m3_to_f32(src[i]);
+}
+
 static void quantize_tensor(const void* x, int dtype, const float* mean /* [BH, D] or NULL */, int8_t* x8,
-                            float* scales, int64_t BH, int64_t S, int64_t D, int64_t block) {
+                            float* scales, int64_t BH, int64_t S, int64_t D, int64_t block, int fp8) {
   const int64_t nblk = (S + block - 1) / block;
 #pragma omp parallel for collapse(2) schedule(static)
   for (int64_t bh = 0; bh < BH; bh++) {
@@ -166,13 +208,17 @@ static void quantize_tensor(const void* x, int dtype, const float* mean /* [BH, 
           float a = fabsf(val);
           if (a > amax) amax = a;
         }
-      const float scale = (amax > 0.f) ? amax / 127.0f : 1.0f;
+      const float scale = (amax > 0.f) ? amax / (fp8 ? 448.0f : 127.0f) : 1.0f;
       const float inv = 1.0f / scale;
       scales[bh * nblk + blk] = scale;
       for (int64_t t = t0; t < t1; t++)
         for (int64_t d = 0; d < D; d++) {
           float val = load_elem(x, dtype, (bh * S + t) * D + d);
           if (mu) val = val - mu[d];
+          if (fp8) {
+            x8[(bh * S + t) * D + d] = (int8_t)f32_to_e4m3(val * inv);
+            continue;
+          }
           float r = nearbyintf(val * inv); /* default rounding mode: ties to even */
           if (r < -127.f) r = -127.f;
           if (r > 127.f) r = 127.f;
@@ -202,17 +248,29 @@ void ar_oracle_k_mean(const void* k, int dtype, float* k_mean, int64_t BH, int64
   }
 }
 
-int ar_oracle_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale,
-                            float* k_scale, float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
-                            int64_t block, int smooth) {
+static int sage_quantize_any(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale,
+                             float* k_scale, float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                             int64_t block, int smooth, int fp8) {
   if (block <= 0) return -1;
   if (smooth)
     ar_oracle_k_mean(k, dtype, k_mean, B * Hkv, S, D);
   else
     memset(k_mean, 0, sizeof(float) * (size_t)(B * Hkv * D));
-  quantize_tensor(q, dtype, NULL, q8, q_scale, B * Hq, S, D, block);
-  quantize_tensor(k, dtype, smooth ? k_mean : NULL, k8, k_scale, B * Hkv, S, D, block);
+  quantize_tensor(q, dtype, NULL, q8, q_scale, B * Hq, S, D, block, fp8);
+  quantize_tensor(k, dtype, smooth ? k_mean : NULL, k8, k_scale, B * Hkv, S, D, block, fp8);
   return 0;
+}
+int ar_oracle_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale,
+                            float* k_scale, float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                            int64_t block, int smooth) {
+  return sage_quantize_any(q, k, dtype, q8, k8, q_scale, k_scale, k_mean, B, Hq, Hkv, S, D, block, smooth, 0);
+}
+/* The FP8 form: E4M3 bit patterns in q8 / k8, scales amax / 448 (src/runtime/cuda_flash_sage.rs:92-97). */
+int ar_oracle_sage_quantize_fp8(const void* q, const void* k, int dtype, uint8_t* q8, uint8_t* k8, float* q_scale,
+                                float* k_scale, float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,
+                                int64_t D, int64_t block, int smooth) {
+  return sage_quantize_any(q, k, dtype, (int8_t*)q8, (int8_t*)k8, q_scale, k_scale, k_mean, B, Hq, Hkv, S, D, block,
+                           smooth, 1);
 }
 
 /* ------------------------------------------------------------------------
@@ -224,6 +282,8 @@ int ar_oracle_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8,
  *   mode 3  Sage           int8 QK^T (exact s32), s = (float)acc * (sq*sk*scale),
  *                          V -> bf16 rn, P -> bf16 rn, f32 accumulate
  *                          (src/runtime/cuda_flash_sage.rs:261,315-322)
+ *   mode 4  Sage FP8       E4M3 Q and K (scales amax/448), f32 dot of the decoded values, otherwise as mode 3
+ *                          (the AR_FP8 variant; host emulation tests/sage_int8.rs:277-320)
  * Common (src/runtime/cuda_flash_bf16.rs:244-251,335-348): scale = 1/sqrt(D)
  * multiplied in f32; additive [N,N] f32 mask added first, then key >= N or
  * (causal and key > row) overrides the logit with the finite -1e30; running
@@ -242,7 +302,7 @@ int ar_oracle_flash(int mode, int in_dtype, int out_dtype, const void* q, const 
   int8_t *q8 = NULL, *k8 = NULL;
   float *qs = NULL, *ks = NULL, *kmean = NULL;
   int64_t nblk = 0;
-  if (mode == 3) {
+  if (mode == 3 || mode == 4) {
     if (block <= 0) return -1;
     nblk = (N + block - 1) / block;
     q8 = (int8_t*)malloc((size_t)(B * Hq * N * D));
@@ -250,7 +310,7 @@ int ar_oracle_flash(int mode, int in_dtype, int out_dtype, const void* q, const 
     qs = (float*)malloc(sizeof(float) * (size_t)(B * Hq * nblk));
     ks = (float*)malloc(sizeof(float) * (size_t)(B * Hkv * nblk));
     kmean = (float*)malloc(sizeof(float) * (size_t)(B * Hkv * D));
-    ar_oracle_sage_quantize(q, k, in_dtype, q8, k8, qs, ks, kmean, B, Hq, Hkv, N, D, block, smooth);
+    sage_quantize_any(q, k, in_dtype, q8, k8, qs, ks, kmean, B, Hq, Hkv, N, D, block, smooth, mode == 4);
   }
 #pragma omp parallel for collapse(2) schedule(dynamic)
   for (int64_t bh = 0; bh < B * Hq; bh++) {
@@ -272,6 +332,14 @@ int ar_oracle_flash(int mode, int in_dtype, int out_dtype, const void* q, const 
           const int8_t* c = k8 + (kvh * N + j) * D;
           for (int64_t t = 0; t < D; t++) acc += (int32_t)a[t] * (int32_t)c[t];
           sc = (float)acc * (qs[bh * nblk + i / block] * ks[kvh * nblk + j / block] * scale);
+        } else if (mode == 4) {
+          /* products of two E4M3 values are exact in f32; the sum is kept in double so that the model does
+           * not depend on an accumulation order */
+          double acc = 0.0;
+          const uint8_t* a = (const uint8_t*)q8 + (bh * N + i) * D;
+          const uint8_t* c = (const uint8_t*)k8 + (kvh * N + j) * D;
+          for (int64_t t = 0; t < D; t++) acc += (double)(e4m3_to_f32(a[t]) * e4m3_to_f32(c[t]));
+          sc = (float)acc * (qs[bh * nblk + i / block] * ks[kvh * nblk + j / block] * scale);
         } else {
           float dot = 0.f;
           for (int64_t t = 0; t < D; t++) {
@@ -291,7 +359,7 @@ int ar_oracle_flash(int mode, int in_dtype, int out_dtype, const void* q, const 
         float p = expf(s[j] - mx);
         l += p;
         if (mode == 1) p = round_tf32(p);
-        if (mode == 2 || mode == 3) p = round_bf16(p);
+        if (mode == 2 || mode == 3 || mode == 4) p = round_bf16(p);
         s[j] = p;
       }
       const float inv = (l > 0.f) ? 1.0f / l : 0.f;
@@ -300,7 +368,7 @@ int ar_oracle_flash(int mode, int in_dtype, int out_dtype, const void* q, const 
         for (int64_t j = 0; j < N; j++) {
           float vv = load_elem(v, in_dtype, (kvh * N + j) * D + t);
           if (mode == 1) vv = round_tf32(vv);
-          if (mode == 3) vv = round_bf16(vv);
+          if (mode == 3 || mode == 4) vv = round_bf16(vv);
           acc += s[j] * vv;
         }
         const float o = acc * inv;

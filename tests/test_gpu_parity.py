@@ -230,6 +230,69 @@ def test_sage_with_mask(ops, oracle_lib):
     assert max_abs(got, want) < 2e-3
 
 
+# ------------------------------------------------------------------------- Sage, FP8 variant
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,bf16", [(1, 2, 2, 256, 128, True), (2, 4, 2, 300, 128, True),
+                                               (1, 2, 1, 1000, 128, False), (1, 3, 3, 1, 128, True),
+                                               (1, 2, 1, 2500, 128, True)])
+@pytest.mark.parametrize("smooth", [True, False])
+def test_sage_fp8_prologue_bit_exact(ops, oracle_lib, B, Hq, Hkv, S, D, bf16, smooth):
+    """E4M3 tensors (cvt.rn.satfinite on the GPU, the oracle's codec on the CPU), scales amax / 448 and the K
+    mean: every bit."""
+    import torch
+    q, k, _ = normal_qkv(S + D + 1, B, Hq, Hkv, S, D, k_offset_sigma=2.0)
+    if bf16:
+        qi, ki = oracle_lib.f32_to_bf16(q), oracle_lib.f32_to_bf16(k)
+        tq, tk = to_dev_bf16(qi), to_dev_bf16(ki)
+    else:
+        qi, ki = q, k
+        tq, tk = to_dev(q), to_dev(k)
+    want = oracle_lib.sage_quantize(qi, ki, 128, smooth, fp8=True)
+    got = ops.sage_quantize(tq, tk, smooth, fp8=True)
+    torch.cuda.synchronize()
+    for name, g, w in zip(("q8", "k8", "q_scale", "k_scale", "k_mean"), got, want):
+        g = g.cpu().numpy()
+        if g.dtype == np.float32:
+            assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), name
+        else:
+            assert np.array_equal(g, w), name
+
+
+@pytest.mark.parametrize("n", [8, 33, 100, 789, 1024])  # tests/sage_int8.rs:334 (the fp8 case), plus a multi-tile length
+def test_sage_fp8_matches_quantised_model(ops, oracle_lib, n):
+    q, k, v = sawtooth_qkv(1, 2, 2, n, 128)
+    got = run_f32(ops, "sage_fp8", q, k, v)
+    want = oracle_lib.flash(4, q, k, v, None, False, block=128, smooth=True)
+    assert max_abs(got, want) < 5e-3  # tests/sage_int8.rs:382
+
+
+@pytest.mark.parametrize("n,causal,hq,hkv", [(512, False, 2, 2), (1000, False, 4, 2), (700, True, 4, 2)])
+def test_sage_fp8_normal_inputs_with_k_offset(ops, oracle_lib, n, causal, hq, hkv):
+    q, k, v = normal_qkv(2, 1, hq, hkv, n, 128, k_offset_sigma=2.0)
+    qb, kb, vb = (oracle_lib.f32_to_bf16(x) for x in (q, k, v))
+    got = oracle_lib.bf16_to_f32(run_bf16(ops, "sage_fp8", qb, kb, vb, None, causal))
+    model = oracle_lib.bf16_to_f32(oracle_lib.flash(4, qb, kb, vb, None, causal, block=128, smooth=True))
+    assert max_abs(got, model) < 2e-2 and cosine(got, model) > 0.9999
+    exact = oracle_lib.flash(0, oracle_lib.bf16_to_f32(qb), oracle_lib.bf16_to_f32(kb), oracle_lib.bf16_to_f32(vb),
+                             None, causal)
+    assert cosine(got, exact) >= 0.998  # three mantissa bits per operand: coarser than INT8 on these inputs
+
+
+def test_sage_fp8_with_mask_and_prequantized_entry(ops, oracle_lib):
+    import torch
+    q, k, v = sawtooth_qkv(1, 2, 2, 200, 128)
+    mask = sawtooth_mask(200)
+    got = run_f32(ops, "sage_fp8", q, k, v, mask, True)
+    want = oracle_lib.flash(4, q, k, v, mask, True, block=128, smooth=True)
+    assert max_abs(got, want) < 5e-3
+    # the two-call form gives the bits of the one-call form
+    qb, kb, vb = (to_dev_bf16(oracle_lib.f32_to_bf16(x)) for x in (q, k, v))
+    one = ops.attn_forward("sage_fp8", qb, kb, vb, None, False)
+    q8, k8, qs, ks, _ = ops.sage_quantize(qb, kb, True, fp8=True)
+    two = ops.sage_attention_prequantized(q8, k8, qs, ks, vb)
+    torch.cuda.synchronize()
+    assert q8.dtype == torch.uint8 and torch.equal(one.view(torch.int16), two.view(torch.int16))
+
+
 # -------------------------------------------------- full benchmark sizes: sampled + properties
 def _sample_check(oracle_lib, q, k, v, out, causal, pairs, rows, Hq, Hkv):
     worst, cos_min = 0.0, 1.0

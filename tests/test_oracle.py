@@ -156,6 +156,75 @@ def test_sage_model_per_row_matches_reference_sage_ref(oracle_lib, n):
     assert max_abs(got, _sage_ref(q, k, v, oracle_lib)) < 2e-3  # tests/sage_int8.rs:148
 
 
+def _e4m3_table():
+    """tests/sage_int8.rs:245-262 (`e4m3_values`): subnormals, normals, the finite top row (448 max)."""
+    vals = [m / 8.0 * 2.0 ** -6 for m in range(8)]
+    vals += [(1.0 + m / 8.0) * 2.0 ** (e - 7) for e in range(1, 15) for m in range(8)]
+    vals += [(1.0 + m / 8.0) * 2.0 ** 8 for m in range(7)]
+    return np.array(sorted(set(vals)), np.float32)
+
+
+def _e4m3_nearest(x):
+    """tests/sage_int8.rs:264-277 (`e4m3`): the nearest table value, sign restored."""
+    vals = _e4m3_table().astype(np.float64)
+    a = np.abs(x.astype(np.float64))
+    return (vals[np.abs(a[..., None] - vals).argmin(-1)] * np.where(x < 0, -1.0, 1.0)).astype(np.float32)
+
+
+def test_e4m3_codec_matches_reference_value_table(oracle_lib):
+    vals = _e4m3_table()
+    assert len(vals) == 127 and vals.max() == 448.0
+    both = np.concatenate([vals, -vals[1:]])
+    assert np.array_equal(oracle_lib.e4m3_to_f32(oracle_lib.f32_to_e4m3(both)), both)  # every value is a fixed point
+    assert np.array_equal(np.sort(oracle_lib.e4m3_to_f32(np.arange(0, 0x7f, dtype=np.uint8))), vals)  # and nothing else
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal(100000) * rng.choice([0.004, 0.3, 20.0, 300.0], 100000)).astype(np.float32)
+    got = oracle_lib.e4m3_to_f32(oracle_lib.f32_to_e4m3(x))
+    want = _e4m3_nearest(x)
+    # equal wherever the nearest value is unique; on ties both are at the same distance
+    assert np.all(np.abs(got.astype(np.float64) - x) <= np.abs(want.astype(np.float64) - x))
+    assert np.mean(got == want) > 0.9999
+    # ties go to the even mantissa; values past the top saturate at 448 (satfinite)
+    assert oracle_lib.e4m3_to_f32(oracle_lib.f32_to_e4m3(np.array([1.0625, 1.1875, 460.0, 1e9, -1e9], np.float32))).tolist() \
+        == [1.0, 1.25, 448.0, 448.0, -448.0]
+
+
+def _sage_ref_fp8(q, k, v, oracle_lib):
+    """tests/sage_int8.rs:279-320 (`sage_ref_fp8`): per-row scales max/448, E4M3 operands."""
+    B, H, N, D = q.shape
+    out = np.zeros_like(q)
+    for b in range(B):
+        for h in range(H):
+            sq = np.abs(q[b, h]).max(axis=1)
+            sk = np.abs(k[b, h]).max(axis=1)
+            sq = np.where(sq > 0, sq / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+            sk = np.where(sk > 0, sk / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+            qe = _e4m3_nearest((q[b, h] / sq[:, None]).astype(np.float32))
+            ke = _e4m3_nearest((k[b, h] / sk[:, None]).astype(np.float32))
+            s = (qe @ ke.T).astype(np.float32) * (sq[:, None] * sk[None, :] * np.float32(0.125))
+            p = np.exp(s - s.max(axis=1, keepdims=True)).astype(np.float32)
+            acc = _bf16_round(p, oracle_lib) @ _bf16_round(v[b, h], oracle_lib)
+            out[b, h] = acc / p.sum(axis=1, keepdims=True)
+    return out
+
+
+@pytest.mark.parametrize("n", [8, 33, 100])
+def test_sage_fp8_model_per_row_matches_reference_sage_ref_fp8(oracle_lib, n):
+    b, h, d = 1, 6, 64
+    q = sawtooth(b * h * n * d, 3).reshape(b, h, n, d)
+    k = sawtooth(b * h * n * d, 11).reshape(b, h, n, d)
+    v = sawtooth(b * h * n * d, 19).reshape(b, h, n, d)
+    got = oracle_lib.flash(4, q, k, v, None, False, block=1, smooth=False)
+    assert max_abs(got, _sage_ref_fp8(q, k, v, oracle_lib)) < 3e-3  # inside the 5e-3 of tests/sage_int8.rs:382
+
+
+def test_sage_fp8_block_model_stays_close_to_exact(oracle_lib):
+    q, k, v = normal_qkv(2, 1, 2, 2, 512, 128, k_offset_sigma=2.0)
+    exact = oracle_lib.flash(0, q, k, v, None, False)
+    fp8 = oracle_lib.flash(4, q, k, v, None, False, block=128, smooth=True)
+    assert max_abs(fp8, exact) < 4e-2 and cosine(fp8, exact) > 0.998  # three mantissa bits: coarser than INT8
+
+
 def test_sage_block_model_stays_close_to_exact(oracle_lib):
     q, k, v = normal_qkv(2, 1, 2, 2, 512, 128, k_offset_sigma=2.0)
     exact = oracle_lib.flash(0, q, k, v, None, False)
