@@ -91,6 +91,8 @@ Settings Settings::from_env() {
   s.async_pipeline = !(as == "0" || as == "false");
   const std::string cd = env_str("CUDA_DEVICE");
   s.cuda_device = cd.empty() ? 0 : std::atoi(cd.c_str());
+  const std::string sg = env_str("AUTORUST_SAGE");
+  s.sage_fp8 = sg == "fp8" || sg == "e4m3";
   return s;
 }
 Settings Settings::with_math_mode(MathMode m) const {
@@ -279,7 +281,8 @@ std::optional<Tensor> fused_attention_ex(const Tensor& q, const Tensor& k, const
     return ar_attn_supported(mode, (int)dt, b, h, hk, n, d, is_causal ? 1 : 0, attn_mask ? 1 : 0) == 1;
   };
   // kernel choice, in the reference's priority order sage > bf16 > tf32 > scalar (:548-693)
-  const bool sage = quantized && settings.tensor_cores && has(AR_MODE_SAGE_INT8);
+  const int sage_mode = settings.sage_fp8 ? AR_MODE_SAGE_FP8 : AR_MODE_SAGE_INT8;
+  const bool sage = quantized && settings.tensor_cores && has(sage_mode);
   if (quantized && !sage) note_sage_unsupported();
   const bool bf16 = dt == DType::BFloat16 && settings.tensor_cores && has(AR_MODE_BF16);
   const bool tc = dt == DType::Float32 && settings.tensor_cores && has(AR_MODE_TF32);
@@ -287,7 +290,7 @@ std::optional<Tensor> fused_attention_ex(const Tensor& q, const Tensor& k, const
   int mode;
   const char* kname;
   if (sage) {
-    mode = AR_MODE_SAGE_INT8; kname = "ar_flash_sage";
+    mode = sage_mode; kname = "ar_flash_sage";  // one kernel name for both operand formats, as in the reference
   } else if (bf16) {
     mode = AR_MODE_BF16; kname = "ar_flash_bf16";
   } else if (tc) {
@@ -327,6 +330,7 @@ int choose_mode(DType dt, bool quantized, int64_t b, int64_t h, int64_t hk, int6
                 bool has_mask) {
   const Settings settings = global_settings();
   auto has = [&](int mode) { return ar_attn_supported(mode, (int)dt, b, h, hk, n, d, causal ? 1 : 0, has_mask ? 1 : 0) == 1; };
+  if (quantized && settings.tensor_cores && settings.sage_fp8 && has(AR_MODE_SAGE_FP8)) return AR_MODE_SAGE_FP8;
   if (quantized && settings.tensor_cores && has(AR_MODE_SAGE_INT8)) return AR_MODE_SAGE_INT8;
   if (quantized) note_sage_unsupported();
   if (dt == DType::BFloat16 && settings.tensor_cores && has(AR_MODE_BF16)) return AR_MODE_BF16;

@@ -45,6 +45,11 @@ struct Settings {
   bool tensor_cores = true;    // AUTORUST_TENSOR_CORES / AUTORUST_TC; default follows math_mode
   bool async_pipeline = true;  // AUTORUST_ASYNC (kept for parity; the TMA pipeline is always asynchronous)
   int cuda_device = 0;         // CUDA_DEVICE
+  // Which operand format `sage` means.  The reference takes FP8 E4M3 whenever the device has it
+  // (`fp8_available()`, sm_89 and later: src/runtime/cuda_flash_sage.rs:77-79, src/models/flash_attention.rs:563),
+  // which on this hardware is always; INT8 is kept as the default here because it is the variant the
+  // benchmark configuration names.  AUTORUST_SAGE=fp8 selects the reference's choice.
+  bool sage_fp8 = false;
   // Parses the environment the way Settings::from_env does (src/settings.rs:174-282).
   static Settings from_env();
   Settings with_math_mode(MathMode m) const;  // src/settings.rs:285-290

@@ -102,6 +102,13 @@ void arh_settings_set(int attention, int math_mode, int tensor_cores, int cuda_d
   s.cuda_device = cuda_device;
   arh::set_global_settings(s);
 }
+// `sage` operand format: 0 INT8 (default), 1 FP8 E4M3 (the reference's choice on sm_89 and later).
+void arh_settings_set_sage_fp8(int fp8) {
+  arh::Settings s = arh::global_settings();
+  s.sage_fp8 = fp8 != 0;
+  arh::set_global_settings(s);
+}
+int arh_settings_get_sage_fp8(void) { return arh::global_settings().sage_fp8 ? 1 : 0; }
 void arh_settings_from_env(void) { arh::set_global_settings(arh::Settings::from_env()); }
 void arh_settings_get(int* attention, int* math_mode, int* tensor_cores, int* async_pipeline, int* cuda_device) {
   const arh::Settings& s = arh::global_settings();

@@ -64,6 +64,9 @@ def load() -> ctypes.CDLL:
     L.arh_settings_set.argtypes = [ci, ci, ci, ci]
     L.arh_settings_set.restype = None
     L.arh_settings_from_env.restype = None
+    L.arh_settings_set_sage_fp8.argtypes = [ci]
+    L.arh_settings_set_sage_fp8.restype = None
+    L.arh_settings_get_sage_fp8.restype = ci
     L.arh_settings_get.argtypes = [ctypes.POINTER(ci)] * 5
     L.arh_settings_get.restype = None
     L.arh_selections.argtypes = [ci]
@@ -88,14 +91,17 @@ class Settings:
     """`Settings` as far as the attention path reads it (src/settings.rs:82-143)."""
 
     @staticmethod
-    def set(attention: int = FLASH, exact_math: bool = False, tensor_cores: bool | None = None, cuda_device: int = 0):
+    def set(attention: int = FLASH, exact_math: bool = False, tensor_cores: bool | None = None, cuda_device: int = 0,
+            sage_fp8: bool = False):
+        """sage_fp8: `sage` means FP8 E4M3 operands (what the reference picks on sm_89 and later) instead of INT8."""
         load().arh_settings_set(attention, int(exact_math), -1 if tensor_cores is None else int(tensor_cores),
                                 cuda_device)
+        load().arh_settings_set_sage_fp8(int(sage_fp8))
 
     @staticmethod
     def from_env():
         """Re-reads AUTORUST_ATTN / AUTORUST_MATH / AUTORUST_TENSOR_CORES / AUTORUST_TC / AUTORUST_ASYNC /
-        CUDA_DEVICE (src/settings.rs:174-282)."""
+        CUDA_DEVICE / AUTORUST_SAGE (src/settings.rs:174-282)."""
         load().arh_settings_from_env()
 
     @staticmethod
@@ -103,8 +109,11 @@ class Settings:
         vals = [ctypes.c_int() for _ in range(5)]
         load().arh_settings_get(*[ctypes.byref(v) for v in vals])
         a, m, tc, asy, dev = (v.value for v in vals)
-        return {"attention": ("sdpa", "flash", "sage")[a], "math_mode": "exact" if m else "fast",
-                "tensor_cores": bool(tc), "async_pipeline": bool(asy), "cuda_device": dev}
+        out = {"attention": ("sdpa", "flash", "sage")[a], "math_mode": "exact" if m else "fast",
+               "tensor_cores": bool(tc), "async_pipeline": bool(asy), "cuda_device": dev}
+        if load().arh_settings_get_sage_fp8():
+            out["sage_fp8"] = True
+        return out
 
 
 class Session:

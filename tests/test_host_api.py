@@ -233,3 +233,46 @@ def test_streamed_host_call_rejects_what_the_operator_rejects(host):
     with pytest.raises(host.TgError, match="no fused kernel"):  # bf16 at a head size without a kernel
         host.attention_host(host.FLASH, q.ctypes.data, q.ctypes.data, q.ctypes.data, q.ctypes.data, host.BFLOAT16,
                             1, 2, 2, 16, 96)
+
+
+def test_sage_operand_format_setting(host, monkeypatch):
+    """AUTORUST_SAGE=fp8 asks for what the reference does on sm_89 and later (FP8 E4M3,
+    src/models/flash_attention.rs:563); unset, `sage` stays INT8."""
+    monkeypatch.delenv("AUTORUST_SAGE", raising=False)
+    host.Settings.from_env()
+    assert "sage_fp8" not in host.Settings.get()
+    monkeypatch.setenv("AUTORUST_SAGE", "fp8")
+    host.Settings.from_env()
+    assert host.Settings.get().get("sage_fp8") is True
+    host.Settings.set()
+    assert "sage_fp8" not in host.Settings.get()
+
+
+@pytest.mark.gpu
+def test_sage_fp8_through_the_operator_api(host, oracle_lib):
+    import torch
+    from autorust_b200 import _abi
+    b, hq, hkv, n, d = 1, 4, 2, 300, 128
+    q, k, v = (torch.from_numpy(a).to(torch.bfloat16).pin_memory() for a in normal_qkv(43, b, hq, hkv, n, d, 2.0))
+    want_bits = oracle_lib.flash(4, *(oracle_lib.f32_to_bf16(t.float().numpy()) for t in (q, k, v)), None, False,
+                                 block=128, smooth=True)
+    try:
+        host.Settings.set(sage_fp8=True)
+        sess = host.Session()
+        before = host.selections(_abi.MODE_SAGE_FP8)
+        tq = host.Tensor.from_host_ptr(q.data_ptr(), host.BFLOAT16, (b, hq, n, d))
+        tk = host.Tensor.from_host_ptr(k.data_ptr(), host.BFLOAT16, (b, hkv, n, d))
+        tv = host.Tensor.from_host_ptr(v.data_ptr(), host.BFLOAT16, (b, hkv, n, d))
+        out = torch.empty_like(q)
+        tq.sage_attention_with(tk, tv, None, 0.0, False, sess).to_host_ptr(out.data_ptr())
+        assert sess.kernel_names() == ["ar_flash_sage"]
+        assert host.selections(_abi.MODE_SAGE_FP8) == before + 1
+        got = out.float().numpy()
+        assert max_abs(got, oracle_lib.bf16_to_f32(want_bits)) < 2e-2
+        # and the streamed host-to-host form follows the same setting, bit for bit
+        out2 = torch.empty_like(q).pin_memory()
+        host.attention_host(host.SAGE, q.data_ptr(), k.data_ptr(), v.data_ptr(), out2.data_ptr(), host.BFLOAT16,
+                            b, hq, hkv, n, d, None, False, 1)
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    finally:
+        host.Settings.set()
