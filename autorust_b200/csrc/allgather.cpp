@@ -5,15 +5,27 @@
 #include <cuda_runtime.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <string>
+#include <vector>
 
 namespace {
 thread_local std::string g_err;
 struct Comm {
   ncclComm_t comm;
   int rank, world;
+  // copy-engine gather: the local buffer, the peers' buffers mapped here, a word for the closing all-reduce
+  void* local = nullptr;
+  size_t bytes = 0;
+  std::vector<void*> peer;
+  int* fence_word = nullptr;
 };
+bool cuda_ok(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  g_err = std::string(what) + ": " + cudaGetErrorString(e);
+  return false;
+}
 bool check(ncclResult_t r, const char* what) {
   if (r == ncclSuccess) return true;
   g_err = std::string(what) + ": " + ncclGetErrorString(r);
@@ -40,9 +52,25 @@ void* ar_gather_init(const void* id, int rank, int world) {
   }
   ncclUniqueId u;
   std::memcpy(&u, id, sizeof(u));
+  // The gather runs beside the attention kernel, whose CTAs fill an SM each: every CTA NCCL takes is an SM the
+  // attention kernel loses for the length of the gather.  Capping them (AR_GATHER_MAX_CTAS) was measured on two
+  // GPUs and loses more than it wins -- 32: 4.15 ms per step, 8: 4.76, 4: 6.13, 2: 10.2 -- so the default stays
+  // NCCL's own choice; the copy-engine path below takes no SM at all.
+  ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+  if (const char* e = std::getenv("AR_GATHER_MAX_CTAS")) {
+    const int v = std::atoi(e);
+    if (v > 0) {
+      cfg.minCTAs = 1;
+      cfg.maxCTAs = v;
+    }
+  }
   ncclComm_t c;
-  if (!check(ncclCommInitRank(&c, world, u, rank), "ncclCommInitRank")) return nullptr;
-  return new Comm{c, rank, world};
+  if (!check(ncclCommInitRankConfig(&c, world, u, rank, &cfg), "ncclCommInitRankConfig")) return nullptr;
+  Comm* out = new Comm();
+  out->comm = c;
+  out->rank = rank;
+  out->world = world;
+  return out;
 }
 
 int ar_gather_allgather_into(void* comm, const void* send, void* recv, int64_t elems_per_rank, int dtype,
@@ -64,9 +92,92 @@ int ar_gather_allgather(void* comm, void* o_full, int64_t elems_per_rank, int dt
   return ar_gather_allgather_into(comm, mine, o_full, elems_per_rank, dtype, cu_stream);  // in place
 }
 
+int ar_gather_p2p_open(void* comm, size_t bytes) {
+  if (!comm || bytes == 0) return -2;
+  Comm* c = static_cast<Comm*>(comm);
+  if (c->local) {
+    g_err = "ar_gather_p2p_open: already open";
+    return -5;
+  }
+  if (!cuda_ok(cudaMalloc(&c->local, bytes), "cudaMalloc")) return -6;
+  c->bytes = bytes;
+  // every rank's IPC handle, all-gathered through the communicator (device staging on both sides)
+  cudaIpcMemHandle_t mine;
+  if (!cuda_ok(cudaIpcGetMemHandle(&mine, c->local), "cudaIpcGetMemHandle")) return -6;
+  const size_t hb = sizeof(cudaIpcMemHandle_t);
+  unsigned char* dev = nullptr;
+  if (!cuda_ok(cudaMalloc((void**)&dev, hb * (size_t)(c->world + 1) + 16), "cudaMalloc")) return -6;
+  std::vector<cudaIpcMemHandle_t> all((size_t)c->world);
+  bool ok = cuda_ok(cudaMemcpy(dev, &mine, hb, cudaMemcpyHostToDevice), "cudaMemcpy") &&
+            check(ncclAllGather(dev, dev + hb, hb, ncclUint8, c->comm, nullptr), "ncclAllGather(handles)") &&
+            cuda_ok(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize") &&
+            cuda_ok(cudaMemcpy(all.data(), dev + hb, hb * (size_t)c->world, cudaMemcpyDeviceToHost), "cudaMemcpy");
+  cudaFree(dev);
+  if (!ok) return -6;
+  c->peer.assign((size_t)c->world, nullptr);
+  for (int r = 0; r < c->world; r++) {
+    if (r == c->rank) {
+      c->peer[(size_t)r] = c->local;
+      continue;
+    }
+    if (!cuda_ok(cudaIpcOpenMemHandle(&c->peer[(size_t)r], all[(size_t)r], cudaIpcMemLazyEnablePeerAccess),
+                 "cudaIpcOpenMemHandle"))
+      return -6;
+  }
+  if (!cuda_ok(cudaMalloc((void**)&c->fence_word, sizeof(int)), "cudaMalloc")) return -6;
+  if (!cuda_ok(cudaMemset(c->fence_word, 0, sizeof(int)), "cudaMemset")) return -6;
+  return 0;
+}
+
+void* ar_gather_p2p_buffer(void* comm) { return comm ? static_cast<Comm*>(comm)->local : nullptr; }
+
+int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream) {
+  if (!comm) return -2;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->local || offset > c->bytes || bytes > c->bytes - offset) return -5;
+  const char* src = static_cast<const char*>(c->local) + offset;
+  // one copy per peer, starting with the next rank so that the ranks do not all write to the same peer at once
+  for (int i = 1; i < c->world; i++) {
+    const int r = (c->rank + i) % c->world;
+    if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset, src, bytes, cudaMemcpyDeviceToDevice,
+                                 (cudaStream_t)cu_stream),
+                 "cudaMemcpyAsync(peer)"))
+      return -6;
+  }
+  return 0;
+}
+
+int ar_gather_p2p_fence(void* comm, void* cu_stream) {
+  if (!comm) return -2;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->fence_word) return -5;
+  // Stream order on every rank puts its pushes before its part of this all-reduce, and the all-reduce cannot
+  // finish anywhere before every rank has started its part.
+  return check(ncclAllReduce(c->fence_word, c->fence_word, 1, ncclInt32, ncclMax, c->comm, (cudaStream_t)cu_stream),
+               "ncclAllReduce(fence)")
+             ? 0
+             : -6;
+}
+
+void ar_gather_p2p_close(void* comm) {
+  if (!comm) return;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->local) return;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->world; r++)
+    if (r != c->rank && c->peer[(size_t)r]) cudaIpcCloseMemHandle(c->peer[(size_t)r]);
+  c->peer.clear();
+  if (c->fence_word) cudaFree(c->fence_word);
+  c->fence_word = nullptr;
+  cudaFree(c->local);
+  c->local = nullptr;
+  c->bytes = 0;
+}
+
 void ar_gather_destroy(void* comm) {
   if (!comm) return;
   Comm* c = static_cast<Comm*>(comm);
+  ar_gather_p2p_close(comm);
   ncclCommDestroy(c->comm);
   delete c;
 }

@@ -74,6 +74,13 @@ def load() -> ctypes.CDLL:
     L.ar_gather_init.restype = p
     L.ar_gather_allgather.argtypes = [p, p, i64, ci, p]
     L.ar_gather_allgather_into.argtypes = [p, p, p, i64, ci, p]
+    L.ar_gather_p2p_open.argtypes = [p, ctypes.c_size_t]
+    L.ar_gather_p2p_buffer.argtypes = [p]
+    L.ar_gather_p2p_buffer.restype = p
+    L.ar_gather_p2p_push.argtypes = [p, ctypes.c_size_t, ctypes.c_size_t, p]
+    L.ar_gather_p2p_fence.argtypes = [p, p]
+    L.ar_gather_p2p_close.argtypes = [p]
+    L.ar_gather_p2p_close.restype = None
     L.ar_gather_destroy.argtypes = [p]
     L.ar_gather_destroy.restype = None
     L.ar_gather_last_error.restype = ctypes.c_char_p
@@ -100,6 +107,7 @@ class Gather:
         if not self._h:
             raise RuntimeError("ar_gather_init: " + L.ar_gather_last_error().decode())
         self.rank, self.world = rank, world
+        self._p2p = None
 
     def allgather_into(self, send, recv, stream=None) -> None:
         """recv[r] <- rank r's `send` (contiguous CUDA tensors, bf16 or f32), asynchronously on `stream`."""
@@ -123,8 +131,47 @@ class Gather:
         if rc != 0:
             raise RuntimeError("ar_gather_allgather: " + load().ar_gather_last_error().decode())
 
+    # ---- the same gather on the copy engines (no SM taken from the attention kernel) ----------------
+    def p2p_open(self, shape, dtype):
+        """Collective.  Allocates this rank's buffer for the GATHERED tensor (same shape on every rank), maps the
+        peers' buffers, and returns the local buffer as a torch tensor: the attention kernel writes this rank's
+        slabs straight into it and p2p_push() sends them to the same place on every peer."""
+        import math
+        import torch
+        esize = torch.empty((), dtype=dtype).element_size()
+        nbytes = math.prod(shape) * esize
+        if load().ar_gather_p2p_open(self._h, nbytes) != 0:
+            raise RuntimeError("ar_gather_p2p_open: " + load().ar_gather_last_error().decode())
+        ptr = load().ar_gather_p2p_buffer(self._h)
+
+        class _Raw:  # torch adopts foreign device memory through the CUDA array interface
+            __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+
+        self._p2p = torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
+        return self._p2p.view(dtype).view(*shape)
+
+    def p2p_push(self, part, stream=None) -> None:
+        """Queues the copy of `part` (a contiguous piece of the tensor p2p_open returned) to every peer."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        if not part.is_contiguous():
+            raise ValueError("p2p_push: the piece must be contiguous")
+        off = part.data_ptr() - self._p2p.data_ptr()
+        rc = load().ar_gather_p2p_push(self._h, off, part.numel() * part.element_size(), s.cuda_stream)
+        if rc != 0:
+            raise RuntimeError("ar_gather_p2p_push: " + load().ar_gather_last_error().decode())
+
+    def p2p_fence(self, stream=None) -> None:
+        """Collective.  After this point of `stream`, every push queued by any rank before its own fence has
+        landed here."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        if load().ar_gather_p2p_fence(self._h, s.cuda_stream) != 0:
+            raise RuntimeError("ar_gather_p2p_fence: " + load().ar_gather_last_error().decode())
+
     def close(self) -> None:
         if self._h:
+            self._p2p = None
             load().ar_gather_destroy(self._h)
             self._h = None
 

@@ -227,11 +227,34 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     km = torch.empty((B, H, D), dtype=torch.float32, device=device)
     stream = torch.cuda.current_stream()
     comm_stream = torch.cuda.Stream() if world > 1 else None
-    gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device) if world > 1 else None
+    gathered = None
     gather = None
+    p2p = False
     if world > 1:
         from autorust_b200 import multi_gpu
         gather = multi_gpu.Gather(rank, world, local_rank)  # NCCL communicator of libar_gather.so
+        if args.gather == "p2p":
+            # copy-engine gather: this rank's outputs land in gathered[rank] and are pushed to the peers piece by piece
+            gathered = gather.p2p_open((world, B * H, S, D), torch.bfloat16)
+            p2p = True
+        else:
+            gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device)
+    # N > 1, copy-engine gather: pieces of the flattened (batch, head) axis, each a whole number of waves of CTAs
+    # as far as possible, with a short last piece so that little is left to push when the step's last kernel ends.
+    pieces = []
+    if p2p:
+        import math
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        ctas_per_head = (S + 255) // 256                      # one CTA per pair of 128-row query tiles
+        unit = sms // math.gcd(sms, ctas_per_head)            # heads whose CTAs fill whole waves (37 here: 8 waves)
+        sizes = [unit] * ((B * H) // unit)
+        rem = B * H - sum(sizes)
+        sizes += [rem - 8, 8] if rem > 8 else ([rem] if rem else [])  # a short last piece: little left to push at the end
+        edges = [0]
+        for n in sizes:
+            edges.append(edges[-1] + n)
+        pieces = [(edges[i], edges[i + 1]) for i in range(len(edges) - 1)]
+    q8f, k8f, qsf, ksf, vf = (t.view(B * H, *t.shape[2:]) for t in (q8, k8, qs, ks, v))
     kernel_events: list = []
 
     def quantise(b0, b1):
@@ -246,7 +269,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             e1 = torch.cuda.Event(enable_timing=True)
             e0.record(stream)
         rc = L.ar_sage_attention_prequantized(q8[b0:b1].data_ptr(), k8[b0:b1].data_ptr(), qs[b0:b1].data_ptr(),
-                                              ks[b0:b1].data_ptr(), v[b0:b1].data_ptr(), out[b0:b1].data_ptr(),
+                                              ks[b0:b1].data_ptr(), v[b0:b1].data_ptr(),
+                                              out[b0:b1].data_ptr(),
                                               _abi.DTYPE_BF16, None, b1 - b0, H, H, S, D, int(w["causal"]), None,
                                               stream.cuda_stream)
         _abi.check(rc, "ar_sage_attention_prequantized")
@@ -254,12 +278,39 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             e1.record(stream)
             kernel_events.append((e0, e1, b1 - b0))
 
+    def attend_heads(h0, h1, record):
+        """The attention kernel over heads [h0, h1) of the flattened (batch, head) axis, written into the shared
+        gather buffer."""
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        rc = L.ar_sage_attention_prequantized(q8f[h0:h1].data_ptr(), k8f[h0:h1].data_ptr(), qsf[h0:h1].data_ptr(),
+                                              ksf[h0:h1].data_ptr(), vf[h0:h1].data_ptr(),
+                                              gathered[rank, h0:h1].data_ptr(), _abi.DTYPE_BF16, None, 1, h1 - h0,
+                                              h1 - h0, S, D, int(w["causal"]), None, stream.cuda_stream)
+        _abi.check(rc, "ar_sage_attention_prequantized")
+        if record:
+            e1.record(stream)
+            kernel_events.append((e0, e1, (h1 - h0) / H))
+
     def step(record=False):
         """Prologue + attention over this rank's batch (the two C-ABI calls ar_attn_forward makes for
         the Sage mode, issued apart so the attention kernel can be bracketed by events)."""
         if world == 1:
             quantise(0, B)
             attend(0, B, record)
+            return
+        if p2p:
+            quantise(0, B)  # the prologue once for the whole batch, then the attention kernel piece by piece
+            for (h0, h1) in pieces:
+                attend_heads(h0, h1, record)
+                done = torch.cuda.Event()
+                done.record(stream)
+                comm_stream.wait_event(done)
+                gather.p2p_push(gathered[rank, h0:h1], comm_stream)
+            gather.p2p_fence(comm_stream)
+            stream.wait_stream(comm_stream)
             return
         for c in range(B):  # one batch element per chunk; gather chunk c while chunk c+1 computes
             quantise(c, c + 1)
@@ -305,8 +356,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     value = ops_per_step_rank * world / (ms_per_step * 1e-3) / 1e12
 
     # roofline of the dominant kernel: its launches inside the timed region, bracketed by events
-    kern_ms = [e0.elapsed_time(e1) * (B / nb) for (e0, e1, nb) in kernel_events]  # scaled to a full-batch launch
-    kern_ms_avg = sum(kern_ms) / len(kern_ms)
+    # every event pair covers `nb` batch elements' worth of the kernel; scaled to a full-batch launch
+    kern_ms_avg = sum(e0.elapsed_time(e1) for (e0, e1, _) in kernel_events) / sum(nb for (_, _, nb) in kernel_events) * B
     peaks = measured_peaks()
     i8_peak = int8_peak_tops(torch, device) if rank == 0 else None
     achieved = ops_per_step_rank / (kern_ms_avg * 1e-3) / 1e12
@@ -358,8 +409,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
             "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (BASELINE config 3)",
-                       **w, "global_batch": B * world, "partition": "batch-interleaved over ranks, bf16 output "
-                       "all-gather over NCCL overlapped per batch element" if world > 1 else "single GPU",
+                       **w, "global_batch": B * world, "partition": ("batch-interleaved over ranks; bf16 outputs gathered per batch "
+                       "element under the next element's kernels, " + ("by peer-to-peer copies on the copy engines "
+                       "(CUDA IPC over NVLink) closed by a 4-byte NCCL all-reduce" if p2p else "by NCCL all-gather"))
+                       if world > 1 else "single GPU",
                        "l2": "inputs (805 MB) exceed L2 (126 MB); no flush needed",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
@@ -376,6 +429,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-vit", action="store_true")
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: how the output slabs reach the other ranks (copy engines, or NCCL's all-gather kernels)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

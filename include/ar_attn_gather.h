@@ -39,6 +39,32 @@ int ar_gather_allgather(void* comm, void* o_full, int64_t elems_per_rank, int dt
 int ar_gather_allgather_into(void* comm, const void* send, void* recv, int64_t elems_per_rank, int dtype,
                              void* cu_stream);
 
+/* ---- The same gather on the copy engines.
+ * NCCL's all-gather kernels take SMs, and the attention kernel fills an SM with each CTA, so a gather that runs
+ * beside the next chunk's attention costs that chunk the SMs NCCL holds.  This form takes none: every rank owns one
+ * buffer of the gathered size, the buffers are mapped into each other's address spaces once (CUDA IPC over the
+ * NVLink peers), the attention kernel writes its slab straight into the local buffer, and a push is world - 1
+ * peer-to-peer cudaMemcpyAsync calls.  NCCL remains the control plane: it ships the IPC handles and closes a
+ * round of pushes (a 4-byte all-reduce queued behind them). */
+
+/* Allocates this rank's buffer of `bytes` (the same on every rank) and opens the peers' buffers.  Collective:
+ * every rank calls it, with its device current.  0 on success. */
+int ar_gather_p2p_open(void* comm, size_t bytes);
+
+/* This rank's buffer (device memory owned by the library until ar_gather_p2p_close), or NULL. */
+void* ar_gather_p2p_buffer(void* comm);
+
+/* Copies [offset, offset + bytes) of the local buffer to the same range of every peer's buffer, asynchronously on
+ * `cu_stream`, after whatever that stream holds (the event of the kernel that produced the range). */
+int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream);
+
+/* Queues on `cu_stream` the point after which every push that any rank queued before ITS fence has landed in
+ * this rank's buffer.  Collective. */
+int ar_gather_p2p_fence(void* comm, void* cu_stream);
+
+/* Unmaps the peers' buffers and frees the local one.  Collective in effect: no peer may still push. */
+void ar_gather_p2p_close(void* comm);
+
 /* Destroys the communicator. */
 void ar_gather_destroy(void* comm);
 

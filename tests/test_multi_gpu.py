@@ -109,8 +109,32 @@ def _gpu_rank(rank, world, port, seed, result):
                                              v[sh.kv_begin:sh.kv_end].contiguous(), sh, gather, causal=True, chunks=chunks)
             torch.cuda.synchronize()
             got[(mode, chunks)] = full.reshape(B * H, S, D)
+    # the same gather on the copy engines: slabs written straight into the shared-layout buffer, pushed to the
+    # peer in two pieces, closed by the fence; every rank must end up with the whole tensor
+    hq_local = sh.q_end - sh.q_begin
+    buf = gather.p2p_open((world, hq_local, S, D), torch.bfloat16)
+    side = torch.cuda.Stream()
+    half = hq_local // 2
+    for c in range(2):
+        lo, hi = c * half, (c + 1) * half
+        ops.attn_forward("bf16", q[sh.q_begin + lo:sh.q_begin + hi].view(1, half, S, D),
+                         k[sh.kv_begin + lo:sh.kv_begin + hi].view(1, half, S, D),
+                         v[sh.kv_begin + lo:sh.kv_begin + hi].view(1, half, S, D), None, True,
+                         out=buf[rank, lo:hi].view(1, half, S, D))
+        done = torch.cuda.Event()
+        done.record()
+        side.wait_event(done)
+        gather.p2p_push(buf[rank, lo:hi], side)
+    gather.p2p_fence(side)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    ref_all = ops.attn_forward("bf16", q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
+    torch.cuda.synchronize()
+    p2p_ok = torch.equal(buf.reshape(B * H, S, D).view(torch.int16), ref_all.reshape(B * H, S, D).view(torch.int16))
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(p2p_ok))
     if rank == 0:
-        ok = True
+        ok = all(flags)
         for mode in ("bf16", "sage"):
             ref = ops.attn_forward(mode, q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
             torch.cuda.synchronize()
