@@ -30,6 +30,7 @@ SYMBOLS = (
     "ar_attn_supported",
     "ar_attn_workspace_bytes",
     "ar_attn_forward",
+    "ar_attn_forward_strided",
     "ar_sage_quantize",
     "ar_sage_quantize_fp8",
     "ar_sage_attention_prequantized",
@@ -68,6 +69,8 @@ def load() -> ctypes.CDLL:
     L.ar_attn_workspace_bytes.restype = sz
     L.ar_attn_forward.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, sz, p]
     L.ar_attn_forward.restype = ci
+    L.ar_attn_forward_strided.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, p, p, p, p, ctypes.c_size_t, p]
+    L.ar_attn_forward_strided.restype = ci
     L.ar_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, ci, p]
     L.ar_sage_quantize.restype = ci
     L.ar_sage_attention_prequantized.argtypes = [p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]

@@ -17,20 +17,6 @@ std::atomic<uint64_t> g_launches;
 // Device status block used when the caller passes no workspace (word 0 is the status word).
 __device__ __align__(256) uint32_t g_status_word[64];
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
-}
-
 // 1 when the current device is compute capability 10.x.
 bool device_ok() {
   int dev = 0;
@@ -48,31 +34,11 @@ bool device_ok() {
   return ok;
 }
 
-// [BH, S, D] row-major tensor; boxes of 128 rows x 128 bytes, 128-byte swizzle.
-bool make_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t BH, int64_t S, int64_t D) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * esize, (cuuint64_t)D * esize * (cuuint64_t)S};
-  cuuint32_t box[3] = {(cuuint32_t)(128 / esize), 128u, 1u};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return enc(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// General form: a [dim2, dim1, dim0] tensor with dim0 contiguous; boxes of box1 x box0 elements.
-bool make_map_ex(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t dim0, int64_t dim1, int64_t dim2,
-                 int box0, int box1) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)dim0, (cuuint64_t)dim1, (cuuint64_t)dim2};
-  cuuint64_t strides[2] = {(cuuint64_t)dim0 * esize, (cuuint64_t)dim0 * esize * (cuuint64_t)dim1};
-  cuuint32_t box[3] = {(cuuint32_t)box0, (cuuint32_t)box1, 1u};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return enc(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+// Dense [B, H, S, D] tensor: rank-4 map with boxes of 128 rows x 128 bytes (ar::make_tile_map).
+bool make_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t B, int64_t H, int64_t S,
+              int64_t D) {
+  int tm = 0;
+  return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, 128 / esize, 128, &tm);
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -219,6 +185,9 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   memset(&a, 0, sizeof(a));
   a.D = (int)D;
   a.out = o;
+  a.o_sb = (long long)Hq * S * D;
+  a.o_sh = (long long)S * D;
+  a.o_ss = D;
   a.mask = mask;
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
@@ -226,9 +195,9 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   if (mode == AR_MODE_BF16) {
     a.mode = ar::TC_BF16;
     a.out_f32 = 0;
-    if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hq, S, D) ||
-        !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D) ||
-        !make_map(&a.tm_v, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+    if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hq, S, D) ||
+        !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D) ||
+        !make_map(&a.tm_v, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
       return AR_ERR_CUDA;
   } else if (mode == AR_MODE_TF32) {
     const int64_t S_pad = (S + 3) / 4 * 4;
@@ -238,9 +207,10 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     g_launches++;
     a.mode = ar::TC_TF32;
     a.out_f32 = 1;
-    if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B * Hq, S, D) ||
-        !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B * Hkv, S, D) ||
-        !make_map_ex(&a.tm_v, vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, S_pad, D, B * Hkv, 32, (int)D))
+    if (!make_map(&a.tm_q, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, Hq, S, D) ||
+        !make_map(&a.tm_k, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, Hkv, S, D) ||
+        !ar::make_tile_map(&a.tm_v, vt, (int)CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, Hkv, D, S_pad, Hkv * D * S_pad, D * S_pad,
+                           S_pad, 32, (int)D, nullptr))
       return AR_ERR_CUDA;
   } else {  // AR_MODE_SAGE_INT8, AR_MODE_SAGE_FP8
     const SageLayout L = sage_layout(dtype, B, Hq, Hkv, S, D);
@@ -270,15 +240,63 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     a.out_f32 = dtype == AR_DTYPE_F32;
     a.q_scale = qs;
     a.k_scale = ks;
-    if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hq, S, D) ||
-        !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hkv, S, D) ||
-        !make_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+    if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
+        !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
+        !make_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
       return AR_ERR_CUDA;
   }
   if (mode != AR_MODE_SAGE_INT8 && mode != AR_MODE_SAGE_FP8 && cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess)
     return AR_ERR_CUDA;
   cudaError_t e = ar::launch_attn_tc(a, stream);
   if (e != cudaSuccess) return AR_ERR_CUDA;
+  g_launches++;
+  g_selected[mode]++;
+  return AR_OK;
+}
+
+int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
+                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, const int64_t* q_strides,
+                            const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+                            void* workspace, size_t workspace_bytes, void* cu_stream) {
+  if (!q || !k || !v || !o || !q_strides || !k_strides || !v_strides || !o_strides) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  const int64_t dq[3] = {Hq * S * D, S * D, D}, dkv[3] = {Hkv * S * D, S * D, D};
+  const bool dense = memcmp(q_strides, dq, sizeof(dq)) == 0 && memcmp(o_strides, dq, sizeof(dq)) == 0 &&
+                     memcmp(k_strides, dkv, sizeof(dkv)) == 0 && memcmp(v_strides, dkv, sizeof(dkv)) == 0;
+  if (dense) return ar_attn_forward(mode, dtype, q, k, v, o, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes, cu_stream);
+  // strided tensors: the bf16 kernel, whose loads are all TMA tiles and whose output is written row by row
+  if (mode != AR_MODE_BF16) return AR_ERR_UNSUPPORTED;
+  if (!mode_has_kernel(mode, dtype, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(workspace)) return AR_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; i++)
+    if (o_strides[i] <= 0 || (o_strides[i] * 2) % 16 != 0) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  uint32_t* status = status_ptr(workspace);
+  if (!status) return AR_ERR_CUDA;
+  ar::TcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.mode = ar::TC_BF16;
+  a.D = (int)D;
+  a.out = o;
+  a.o_sb = o_strides[0];
+  a.o_sh = o_strides[1];
+  a.o_ss = o_strides[2];
+  a.out_f32 = 0;
+  a.mask = mask;
+  a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
+  a.causal = causal ? 1 : 0;
+  a.status = status;
+  int tq = 0, tk = 0, tv = 0;
+  const int bf16 = (int)CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (!ar::make_tile_map(&a.tm_q, q, bf16, 2, B, Hq, S, D, q_strides[0], q_strides[1], q_strides[2], 64, 128, &tq) ||
+      !ar::make_tile_map(&a.tm_k, k, bf16, 2, B, Hkv, S, D, k_strides[0], k_strides[1], k_strides[2], 64, 128, &tk) ||
+      !ar::make_tile_map(&a.tm_v, v, bf16, 2, B, Hkv, S, D, v_strides[0], v_strides[1], v_strides[2], 64, 128, &tv))
+    return AR_ERR_ALIGNMENT;  // strides that are not 16-byte multiples, or that the copy engine cannot express
+  a.token_major = tq | (tk << 1) | (tv << 2);
+  if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;
   g_launches++;
   g_selected[mode]++;
   return AR_OK;
@@ -303,6 +321,9 @@ int sage_prequantized_any(int mode, const void* q8, const void* k8, const float*
   a.mode = mode == AR_MODE_SAGE_FP8 ? ar::TC_SAGE_FP8 : ar::TC_SAGE;
   a.D = (int)D;
   a.out = o;
+  a.o_sb = (long long)Hq * S * D;
+  a.o_sh = (long long)S * D;
+  a.o_ss = D;
   a.out_f32 = out_dtype == AR_DTYPE_F32;
   a.mask = mask;
   a.q_scale = q_scale;
@@ -310,9 +331,9 @@ int sage_prequantized_any(int mode, const void* q8, const void* k8, const float*
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
   a.status = status;
-  if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hq, S, D) ||
-      !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hkv, S, D) ||
-      !make_map(&a.tm_v, v_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+  if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
+      !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
+      !make_map(&a.tm_v, v_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
     return AR_ERR_CUDA;
   if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
   if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;

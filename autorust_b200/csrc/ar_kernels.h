@@ -12,10 +12,15 @@ enum TcMode { TC_BF16 = 0, TC_SAGE = 1, TC_TF32 = 2, TC_SAGE_FP8 = 3 };  // TC_S
 struct TcArgs {
   int mode;             // TcMode
   int D;                // 64 or 128
-  CUtensorMap tm_q;     // [B*Hq, S, D]   bf16 (TC_BF16), int8 (TC_SAGE) or e4m3 (TC_SAGE_FP8), 128-byte swizzle, box 128 rows
-  CUtensorMap tm_k;     // [B*Hkv, S, D]  same element type as tm_q
-  CUtensorMap tm_v;     // [B*Hkv, S, D]  bf16; TC_TF32: the transposed copy [B*Hkv, D, S_pad] f32, box 32 keys x D rows
-  void* out;            // [B*Hq, S, D]   bf16 or f32
+  // Rank-4 tensor maps over (D, then token and head in the order of their strides, batch): 128-byte swizzle, box
+  // of 128 tokens x 128 bytes.  token_major bit t set: tensor t (0 q, 1 k, 2 v) has the head stride below the token
+  // stride ([B, S, H, D] memory), so its coordinates go (x, head, token, batch) instead of (x, token, head, batch).
+  CUtensorMap tm_q;     // bf16 (TC_BF16), int8 (TC_SAGE), e4m3 (TC_SAGE_FP8) or f32 (TC_TF32)
+  CUtensorMap tm_k;     // same element type as tm_q
+  CUtensorMap tm_v;     // bf16; TC_TF32: the transposed copy [B, Hkv, D, S_pad] f32, box 32 keys x D rows
+  int token_major;
+  void* out;            // bf16 or f32; element (b, h, row, d) at out + b * o_sb + h * o_sh + row * o_ss + d
+  long long o_sb, o_sh, o_ss;
   int out_f32;
   const float* mask;    // [S, S] additive or null
   const float* q_scale; // TC_SAGE: [B*Hq, nblk]
@@ -25,6 +30,14 @@ struct TcArgs {
   uint32_t* status;     // device status word
 };
 cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream);
+// Rank-4 tile map (128-byte swizzle) of a tensor indexed (batch, head, row, inner) whose element lies at
+// batch * sb + head * sh + row * sr + inner (strides in elements, inner contiguous): box of box_inner x box_rows.
+// The two middle dimensions are entered in the order of their strides; *token_major_bit is 1 when the head comes
+// first.  `cu_dtype` is a CUtensorMapDataType.  False when the strides do not suit TMA (16-byte multiples, base
+// 16-byte aligned) or the driver refuses.
+bool make_tile_map(CUtensorMap* m, const void* ptr, int cu_dtype, int esize, long long B, long long H, long long rows,
+                   long long inner, long long sb, long long sh, long long sr, int box_inner, int box_rows,
+                   int* token_major_bit);
 bool attn_tc_has(int mode, int D);
 
 // Exact f32 forward on FFMA (attn_fwd_exact.cu).

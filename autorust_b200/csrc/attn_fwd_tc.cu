@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
-                   int causal, int out_f32, uint32_t* status) {
+                   int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
+                   uint32_t* status) {
   using C = Cfg<MODE, D>;
   constexpr int ST = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -286,7 +287,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int bh = blockIdx.y;
   const int b = bh / Hq;
   const int h = bh - b * Hq;
-  const int kvbh = b * Hkv + h / (Hq / Hkv);
+  const int kvh = h / (Hq / Hkv);
+  const int kvbh = b * Hkv + kvh;
+  // coordinates of a tile in a rank-4 map: token and head in the order of the tensor's strides
+  auto load_tile = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x, int tok, int head, int tensor) {
+    if ((token_major >> tensor) & 1)
+      tma_load_4d(dst, m, bar, x, head, tok, b);
+    else
+      tma_load_4d(dst, m, bar, x, tok, head, b);
+  };
   // causal: heavy (late) query tiles first, so that the last CTAs of the grid are the light ones
   const int qblock = causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
   const int q0 = qblock * (2 * BM);
@@ -345,8 +354,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (nkv[t] == 0) continue;
         mbar_arrive_expect_tx(&q_full[t], C::QK_TILE_BYTES);
         for (int bx = 0; bx < C::QK_BOXES; bx++)
-          tma_load_3d(sQ + t * C::QK_TILE_BYTES + bx * (BM * 128), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS,
-                      q0 + t * BM, bh);
+          load_tile(sQ + t * C::QK_TILE_BYTES + bx * (BM * 128), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS, q0 + t * BM, h, 0);
       }
       int issued = 0;
       for (int j = 0; j < nkv_max; j++) {
@@ -355,15 +363,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (n > 0 && !mbar_wait(&k_empty[s], (n - 1) & 1, abort_flag, status, 0x10)) break;
         mbar_arrive_expect_tx(&k_full[s], C::QK_TILE_BYTES);
         for (int bx = 0; bx < C::QK_BOXES; bx++)
-          tma_load_3d(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN,
-                      kvbh);
+          load_tile(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN, kvh, 1);
         if (n > 0 && !mbar_wait(&v_empty[s], (n - 1) & 1, abort_flag, status, 0x11)) break;
         mbar_arrive_expect_tx(&v_full[s], C::V_TILE_BYTES);
         for (int bx = 0; bx < C::V_BOXES; bx++) {
           if constexpr (MODE == TC_TF32)  // transposed V: x = key, y = d
-            tma_load_3d(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], j * BN + bx * 32, 0, kvbh);
+            load_tile(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], j * BN + bx * 32, 0, kvh, 2);
           else
-            tma_load_3d(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], bx * 64, j * BN, kvbh);
+            load_tile(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], bx * 64, j * BN, kvh, 2);
         }
         issued = j + 1;
       }
@@ -543,7 +550,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (ok) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        const size_t obase = ((size_t)bh * N + row) * D;
+        const size_t obase = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)row * o_ss);
 #pragma unroll
         for (int cch = 0; cch < D / 32; cch++) {
           uint32_t ov[32];
@@ -602,11 +609,43 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   }
   dim3 grid((a.S + 2 * BM - 1) / (2 * BM), a.B * a.Hq, 1);
   kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale, a.k_scale, a.S,
-                                                     a.Hq, a.Hkv, a.causal, a.out_f32, a.status);
+                                                     a.Hq, a.Hkv, a.causal, a.out_f32, a.token_major, a.o_sb, a.o_sh,
+                                                     a.o_ss, a.status);
   return cudaGetLastError();
 }
 
 }  // namespace
+
+bool make_tile_map(CUtensorMap* m, const void* ptr, int cu_dtype, int esize, long long B, long long H, long long rows,
+                   long long inner, long long sb, long long sh, long long sr, int box_inner, int box_rows,
+                   int* token_major_bit) {
+  typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiledFn enc = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  if (!enc || B <= 0 || H <= 0 || rows <= 0 || inner <= 0) return false;
+  const long long strides_el[3] = {sr, sh, sb};
+  for (long long st : strides_el)
+    if (st <= 0 || (st * esize) % 16 != 0) return false;
+  if (((uintptr_t)ptr & 15u) != 0) return false;
+  const bool head_first = sh < sr;  // [B, S, H, D]-style memory: consecutive heads are closer than consecutive rows
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)(head_first ? H : rows), (cuuint64_t)(head_first ? rows : H),
+                        (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)(head_first ? sh : sr) * esize, (cuuint64_t)(head_first ? sr : sh) * esize,
+                           (cuuint64_t)sb * esize};
+  cuuint32_t box[4] = {(cuuint32_t)box_inner, head_first ? 1u : (cuuint32_t)box_rows,
+                       head_first ? (cuuint32_t)box_rows : 1u, 1u};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (token_major_bit) *token_major_bit = head_first ? 1 : 0;
+  return enc(m, (CUtensorMapDataType)cu_dtype, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 bool attn_tc_has(int mode, int D) {
   if (mode == TC_BF16) return D == 64 || D == 128;

@@ -58,24 +58,9 @@ int static_scratch(void** out) {
 
 inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-bool tile_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t BH, int64_t S, int64_t D) {
-  static EncodeTiledFn enc = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  if (!enc) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * esize, (cuuint64_t)D * esize * (cuuint64_t)S};
-  cuuint32_t box[3] = {(cuuint32_t)(128 / esize), 128u, 1u};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return enc(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+bool tile_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t B, int64_t H, int64_t S,
+              int64_t D) {
+  return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, 128 / esize, 128, nullptr);
 }
 
 }  // namespace
@@ -135,6 +120,9 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
   a.mode = ar::TC_SAGE;
   a.D = (int)D;
   a.out = o;
+  a.o_sb = (long long)Hq * S * D;
+  a.o_sh = (long long)S * D;
+  a.o_ss = D;
   a.out_f32 = dtype == AR_DTYPE_F32;
   a.mask = mask;
   a.q_scale = qs;
@@ -142,9 +130,9 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
   a.status = (uint32_t*)ws;
-  if (!tile_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hq, S, D) ||
-      !tile_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B * Hkv, S, D) ||
-      !tile_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B * Hkv, S, D))
+  if (!tile_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
+      !tile_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
+      !tile_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
     return AR_ERR_CUDA;
   if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;
   ar::count_launches(AR_MODE_SAGE_INT8, launches + 1);

@@ -4,6 +4,8 @@ libar_attn.so and raises when the library or a B200 is missing.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _abi
@@ -77,6 +79,42 @@ def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
                                s.cuda_stream)
     _abi.check(rc, "ar_attn_forward")
     # keep the scratch alive until the stream has consumed it
+    if workspace is not None:
+        workspace.record_stream(s)
+    return out
+
+
+def attn_forward_views(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None = None,
+                       causal: bool = False, out: torch.Tensor | None = None, mode="bf16",
+                       stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+    """The forward on [B, H, S, D] VIEWS (ar_attn_forward_strided): any batch, head and token strides with the last
+    dimension contiguous -- e.g. `proj(x).view(B, S, H, D).transpose(1, 2)` or a slice of a fused QKV projection --
+    are read in place through TMA.  `out` may be such a view too; when it is not given the result is allocated as
+    [B, S, H, D] memory and returned as its [B, H, S, D] view, so that `.transpose(1, 2).reshape(B, S, H * D)` is free."""
+    L = _abi.load()
+    for t in (q, k, v):
+        if t.dim() != 4 or not t.is_cuda or t.stride(3) != 1:
+            raise ValueError("q, k, v must be 4-D CUDA tensors [B, H, S, D] with a contiguous last dimension")
+    if k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:] or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("shape or dtype mismatch between q, k, v")
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    if out is None:
+        out = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device).transpose(1, 2)
+    if tuple(out.shape) != (B, Hq, S, D) or out.stride(3) != 1 or out.dtype != q.dtype:
+        raise ValueError("out must be a [B, H, S, D] view of q's dtype with a contiguous last dimension")
+    m = mode_code(mode)
+    need = int(L.ar_attn_workspace_bytes(m, _dtype_code(q), B, Hq, Hkv, S, D))
+    workspace = torch.empty(need, dtype=torch.uint8, device=q.device) if need else None
+    arr = ctypes.c_int64 * 3
+    strides = [arr(t.stride(0), t.stride(1), t.stride(2)) for t in (q, k, v, out)]
+    with torch.cuda.device(q.device):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_attn_forward_strided(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                       mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal),
+                                       strides[0], strides[1], strides[2], strides[3],
+                                       workspace.data_ptr() if workspace is not None else None, need, s.cuda_stream)
+    _abi.check(rc, "ar_attn_forward_strided")
     if workspace is not None:
         workspace.record_stream(s)
     return out

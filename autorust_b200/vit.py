@@ -3,9 +3,15 @@
 Mirrors autorust's `ViT::forward_with` (src/models/vit.rs:118-158) and
 `TransformerBlock::forward_mask_with` / `attn_mask_with` (src/models/transformer.rs:195-312):
 patch embedding (16x16 conv, stride 16) -> [cls | patches] + position embedding -> 12 pre-norm blocks
-(LayerNorm eps 1e-5 -> separate q/k/v projections -> fused attention at S=197, D=64 -> output
+(LayerNorm eps 1e-5 -> q/k/v projections -> fused attention at S=197, D=64 -> output
 projection -> residual -> LayerNorm -> MLP 3072 with the tanh GELU of src/tensor/nn.rs:1377-1395 ->
 residual) -> LayerNorm of the cls token -> classifier head.
+
+The reference projects q, k and v separately and materialises the transposed [B, H, S, D] views before the
+kernel (src/models/transformer.rs:260-262, 277-285).  With bf16 weights the default path here runs the three
+projections as one GEMM over the concatenated weights (the same numbers: the rows of the product do not mix)
+and hands the kernel VIEWS of that [B, S, 3E] buffer; the kernel's output lands in [B, S, H, D] memory, which is
+the [B, S, E] the output projection reads.  The four copies per block are gone (`copies=True` keeps them).
 
 As in the reference, the projections stay library GEMMs (torch / cuBLAS, bf16) and only the attention
 goes to the hand-written kernel; torch supplies memory, GEMMs, LayerNorm and GELU -- it is the harness
@@ -53,6 +59,9 @@ class ViT:
                 "o": (uniform(e, e), zeros(e)),
                 "ff1": (uniform(4 * e, e), zeros(4 * e)), "ff2": (uniform(e, 4 * e), zeros(e)),
             })
+        for blk in self.blocks:  # the three projection weights side by side, for the one-GEMM form
+            blk["qkv"] = (torch.cat([blk["q"][0], blk["k"][0], blk["v"][0]], 0).contiguous(),
+                          torch.cat([blk["q"][1], blk["k"][1], blk["v"][1]], 0).contiguous())
         self.norm = (ones(e), zeros(e))
         self.head = (uniform(num_classes, e), zeros(num_classes))
 
@@ -67,10 +76,18 @@ class ViT:
         mode = "bf16" if q.dtype == torch.bfloat16 else "exact"
         return ops.attn_forward(mode, q, k, v)
 
-    def _block(self, x, blk, attention):
+    def _block(self, x, blk, attention, copies=False):
         B, S, E = x.shape
         H, D = self.num_heads, E // self.num_heads
         n1 = F.layer_norm(x, (E,), blk["ln1"][0], blk["ln1"][1], 1e-5)
+        if attention == "fused" and not copies and x.dtype == torch.bfloat16:
+            qkv = F.linear(n1, *blk["qkv"])  # [B, S, 3E]; q, k, v are views of it, read in place by the kernel
+            q, k, v = (qkv[..., i * E:(i + 1) * E].view(B, S, H, D).transpose(1, 2) for i in range(3))
+            a = ops.attn_forward_views(q, k, v).transpose(1, 2).reshape(B, S, E)  # [B, S, H, D] memory: no copy
+            x = x + F.linear(a, *blk["o"])
+            n2 = F.layer_norm(x, (E,), blk["ln2"][0], blk["ln2"][1], 1e-5)
+            h = F.gelu(F.linear(n2, *blk["ff1"]), approximate="tanh")
+            return x + F.linear(h, *blk["ff2"])
         # projections first (plain GEMMs), then the transposed views are materialised for the kernel
         # (src/models/transformer.rs:277-285, 260-262)
         q = F.linear(n1, *blk["q"]).view(B, S, H, D).transpose(1, 2).contiguous()
@@ -82,13 +99,14 @@ class ViT:
         h = F.gelu(F.linear(n2, *blk["ff1"]), approximate="tanh")
         return x + F.linear(h, *blk["ff2"])
 
-    def forward(self, images: torch.Tensor, attention: str = "fused") -> torch.Tensor:
-        """images [B, 3, 224, 224] -> logits [B, num_classes]."""
+    def forward(self, images: torch.Tensor, attention: str = "fused", copies: bool = False) -> torch.Tensor:
+        """images [B, 3, 224, 224] -> logits [B, num_classes].  copies=True: the reference's form, with separate
+        projections and materialised transposed views around the kernel."""
         x = F.conv2d(images.to(self.dtype), self.embed_w, self.embed_b, stride=self.patch)
         x = x.flatten(2).transpose(1, 2)  # [B, 196, E]
         x = torch.cat([self.cls.expand(x.shape[0], -1, -1), x], dim=1) + self.pos
         for blk in self.blocks:
-            x = self._block(x, blk, attention)
+            x = self._block(x, blk, attention, copies)
         cls_tok = F.layer_norm(x[:, 0], (self.embed_dim,), self.norm[0], self.norm[1], 1e-5)
         return F.linear(cls_tok, *self.head)
 
@@ -105,20 +123,22 @@ class ViT:
         return other
 
 
-def images_per_second(batch=64, iters=10, warmup=3, attention="fused", seed=3) -> dict:
+def images_per_second(batch=64, iters=10, warmup=3, attention="fused", seed=3, copies=False) -> dict:
     """BASELINE config 4: ViT-B/16, batch 64, 224x224x3 inputs ~ U(0,1) (seed 3), bf16 GEMMs."""
     model = ViT(seed=seed)
     g = torch.Generator(device="cuda").manual_seed(seed)
     x = torch.rand(batch, 3, 224, 224, device="cuda", generator=g)
     for _ in range(warmup):
-        model.forward(x, attention)
+        model.forward(x, attention, copies)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
-        model.forward(x, attention)
+        model.forward(x, attention, copies)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
     return {"img_per_s": batch / (ms * 1e-3), "ms_per_batch": ms, "batch": batch, "attention": attention,
+            "layout": "separate projections, transposed copies" if copies or attention != "fused"
+            else "one QKV GEMM, kernel reads and writes [B, S, H, D] views",
             "model": "ViT-B/16 random-init, bf16 GEMMs (cuBLAS via torch), attention S=197 D=64"}

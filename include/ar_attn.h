@@ -92,6 +92,20 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
                     int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
                     size_t workspace_bytes, void* cu_stream);
 
+/* ar_attn_forward on tensors that are views: element (b, h, s, d) of q lies at
+ * q + b * q_strides[0] + h * q_strides[1] + s * q_strides[2] + d (strides in elements, d contiguous), likewise k, v
+ * and o.  This is how the caller of the operator holds them: the projections write [B, S, H, D] (or one fused
+ * [B, S, 3, H, D]) and the reference materialises the transposed views before it launches
+ * (src/models/transformer.rs:260-262, 277-285); here the copy engine reads the tiles through the strides and the
+ * output rows are written where the output projection wants them, so the four copies per block disappear.
+ * Strided tensors are taken by AR_MODE_BF16 (all loads are TMA tiles); with dense strides every mode is accepted and
+ * the call is ar_attn_forward.  Every stride times the element size must be a multiple of 16 bytes
+ * (AR_ERR_ALIGNMENT otherwise). */
+int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
+                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, const int64_t* q_strides,
+                            const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+                            void* workspace, size_t workspace_bytes, void* cu_stream);
+
 /* The Sage prologue on its own: optional K mean-smoothing, then symmetric INT8 quantisation of
  * Q and K with one f32 scale per `block` consecutive tokens
  * (scale = amax > 0 ? amax / 127 : 1; q8 = clamp(rn(x * (1 / scale)), -127, 127): the scalar

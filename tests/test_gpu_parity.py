@@ -230,6 +230,64 @@ def test_sage_with_mask(ops, oracle_lib):
     assert max_abs(got, want) < 2e-3
 
 
+# ------------------------------------------------------- views: strided q, k, v and output
+@pytest.mark.parametrize("layout", ["bshd", "fused_qkv", "dense", "mixed"])
+@pytest.mark.parametrize("S,D,causal", [(197, 64, False), (300, 128, True)])
+def test_strided_views_give_the_bits_of_the_contiguous_call(ops, layout, S, D, causal):
+    """ar_attn_forward_strided reads [B, H, S, D] views in place (the projection output's [B, S, H, D] memory, a
+    slice of a fused [B, S, 3, H, D] projection, GQA included) and writes the output through strides: the result
+    must have the bits of the call on materialised copies."""
+    import torch
+    B, Hq, Hkv = 2, 4, 2
+    g = torch.Generator(device="cuda").manual_seed(S + D)
+    if layout == "fused_qkv":  # one buffer [B, S, (Hq + 2 Hkv) * D]
+        buf = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda", generator=g).to(torch.bfloat16)
+        q = buf[..., :Hq * D].view(B, S, Hq, D).transpose(1, 2)
+        k = buf[..., Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D).transpose(1, 2)
+        v = buf[..., (Hq + Hkv) * D:].view(B, S, Hkv, D).transpose(1, 2)
+    elif layout == "bshd":
+        q = torch.randn(B, S, Hq, D, device="cuda", generator=g).to(torch.bfloat16).transpose(1, 2)
+        k = torch.randn(B, S, Hkv, D, device="cuda", generator=g).to(torch.bfloat16).transpose(1, 2)
+        v = torch.randn(B, S, Hkv, D, device="cuda", generator=g).to(torch.bfloat16).transpose(1, 2)
+    elif layout == "mixed":  # q as the projection wrote it, k and v from a cache in [B, H, S_max, D] with S_max > S
+        q = torch.randn(B, S, Hq, D, device="cuda", generator=g).to(torch.bfloat16).transpose(1, 2)
+        cache = torch.randn(2, B, Hkv, S + 59, D, device="cuda", generator=g).to(torch.bfloat16)
+        k, v = cache[0, :, :, :S], cache[1, :, :, :S]
+    else:
+        q = torch.randn(B, Hq, S, D, device="cuda", generator=g).to(torch.bfloat16)
+        k = torch.randn(B, Hkv, S, D, device="cuda", generator=g).to(torch.bfloat16)
+        v = torch.randn(B, Hkv, S, D, device="cuda", generator=g).to(torch.bfloat16)
+    want = ops.attn_forward("bf16", q.contiguous(), k.contiguous(), v.contiguous(), None, causal)
+    got = ops.attn_forward_views(q, k, v, None, causal)
+    torch.cuda.synchronize()
+    assert ops.last_status(None) == 0
+    assert got.shape == want.shape and got.transpose(1, 2).is_contiguous()  # [B, S, H, D] memory
+    assert torch.equal(got.contiguous().view(torch.int16), want.view(torch.int16))
+    # an output view inside a larger buffer
+    big = torch.zeros(B, S, Hq * D + 64, device="cuda", dtype=torch.bfloat16)
+    out = big[..., :Hq * D].view(B, S, Hq, D).transpose(1, 2)
+    ops.attn_forward_views(q, k, v, None, causal, out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out.contiguous().view(torch.int16), want.view(torch.int16))
+    assert bool((big[..., Hq * D:] == 0).all())  # nothing written past the rows
+
+
+def test_strided_call_rejects_what_it_cannot_read(ops):
+    import torch
+    from autorust_b200 import _abi
+    q = torch.randn(1, 2, 64, 64, device="cuda").to(torch.bfloat16)
+    odd = torch.randn(1, 64, 2, 72, device="cuda").to(torch.bfloat16)[..., :64].transpose(1, 2)  # token stride 144 elements: fine
+    ops.attn_forward_views(odd, odd, odd)
+    bad = torch.randn(1, 64, 2, 68, device="cuda").to(torch.bfloat16)[..., :64].transpose(1, 2)  # head stride 136 bytes
+    with pytest.raises(_abi.AttnLibraryError):
+        ops.attn_forward_views(bad, bad, bad)
+    f32 = torch.randn(1, 64, 2, 72, device="cuda")[..., :64].transpose(1, 2)
+    with pytest.raises(_abi.AttnLibraryError):  # strided tensors are the bf16 kernel's; the other modes want dense ones
+        ops.attn_forward_views(f32, f32, f32, mode="exact")
+    torch.cuda.synchronize()
+    del q
+
+
 # ------------------------------------------------------------------------- Sage, FP8 variant
 @pytest.mark.parametrize("B,Hq,Hkv,S,D,bf16", [(1, 2, 2, 256, 128, True), (2, 4, 2, 300, 128, True),
                                                (1, 2, 1, 1000, 128, False), (1, 3, 3, 1, 128, True),
