@@ -99,28 +99,46 @@ int ar_gather_p2p_open(void* comm, size_t bytes) {
     g_err = "ar_gather_p2p_open: already open";
     return -5;
   }
-  if (!cuda_ok(cudaMalloc(&c->local, bytes), "cudaMalloc")) return -6;
+  // The handle exchange below is a collective: a rank that failed locally still takes part in it (with a zero
+  // "ok" byte), so that all ranks leave this function together and with the same verdict.
+  struct Packet {
+    cudaIpcMemHandle_t handle;
+    unsigned char ok;
+    unsigned char pad[15];
+  };
+  Packet mine;
+  std::memset(&mine, 0, sizeof(mine));
+  bool local_ok = cuda_ok(cudaMalloc(&c->local, bytes), "cudaMalloc");
+  if (local_ok) local_ok = cuda_ok(cudaIpcGetMemHandle(&mine.handle, c->local), "cudaIpcGetMemHandle");
+  mine.ok = local_ok ? 1 : 0;
   c->bytes = bytes;
-  // every rank's IPC handle, all-gathered through the communicator (device staging on both sides)
-  cudaIpcMemHandle_t mine;
-  if (!cuda_ok(cudaIpcGetMemHandle(&mine, c->local), "cudaIpcGetMemHandle")) return -6;
-  const size_t hb = sizeof(cudaIpcMemHandle_t);
+  const size_t hb = sizeof(Packet);
   unsigned char* dev = nullptr;
-  if (!cuda_ok(cudaMalloc((void**)&dev, hb * (size_t)(c->world + 1) + 16), "cudaMalloc")) return -6;
-  std::vector<cudaIpcMemHandle_t> all((size_t)c->world);
-  bool ok = cuda_ok(cudaMemcpy(dev, &mine, hb, cudaMemcpyHostToDevice), "cudaMemcpy") &&
+  std::vector<Packet> all((size_t)c->world);
+  bool ok = cuda_ok(cudaMalloc((void**)&dev, hb * (size_t)(c->world + 1)), "cudaMalloc") &&
+            cuda_ok(cudaMemcpy(dev, &mine, hb, cudaMemcpyHostToDevice), "cudaMemcpy") &&
             check(ncclAllGather(dev, dev + hb, hb, ncclUint8, c->comm, nullptr), "ncclAllGather(handles)") &&
             cuda_ok(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize") &&
             cuda_ok(cudaMemcpy(all.data(), dev + hb, hb * (size_t)c->world, cudaMemcpyDeviceToHost), "cudaMemcpy");
-  cudaFree(dev);
-  if (!ok) return -6;
+  if (dev) cudaFree(dev);
+  for (int r = 0; ok && r < c->world; r++)
+    if (!all[(size_t)r].ok) {
+      g_err = "ar_gather_p2p_open: rank " + std::to_string(r) + " could not allocate or export its buffer";
+      ok = false;
+    }
+  if (!ok) {
+    if (c->local) cudaFree(c->local);
+    c->local = nullptr;
+    c->bytes = 0;
+    return -6;
+  }
   c->peer.assign((size_t)c->world, nullptr);
   for (int r = 0; r < c->world; r++) {
     if (r == c->rank) {
       c->peer[(size_t)r] = c->local;
       continue;
     }
-    if (!cuda_ok(cudaIpcOpenMemHandle(&c->peer[(size_t)r], all[(size_t)r], cudaIpcMemLazyEnablePeerAccess),
+    if (!cuda_ok(cudaIpcOpenMemHandle(&c->peer[(size_t)r], all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess),
                  "cudaIpcOpenMemHandle"))
       return -6;
   }

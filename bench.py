@@ -234,10 +234,18 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         from autorust_b200 import multi_gpu
         gather = multi_gpu.Gather(rank, world, local_rank)  # NCCL communicator of libar_gather.so
         if args.gather == "p2p":
-            # copy-engine gather: this rank's outputs land in gathered[rank] and are pushed to the peers piece by piece
-            gathered = gather.p2p_open((world, B * H, S, D), torch.bfloat16)
-            p2p = True
-        else:
+            # copy-engine gather: this rank's outputs land in gathered[rank] and are pushed to the peers piece by piece.
+            # Every rank has to have its peers mapped; if one could not, all of them take the NCCL form.
+            try:
+                gathered = gather.p2p_open((world, B * H, S, D), torch.bfloat16)
+                opened = 1
+            except RuntimeError as exc:
+                print(f"[bench] rank {rank}: copy-engine gather unavailable ({exc}); using NCCL", file=sys.stderr)
+                opened = 0
+            flag = torch.tensor([opened], dtype=torch.int32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            p2p = bool(flag.item())
+        if not p2p:
             gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device)
     # N > 1, copy-engine gather: pieces of the flattened (batch, head) axis, each a whole number of waves of CTAs
     # as far as possible, with a short last piece so that little is left to push when the step's last kernel ends.
