@@ -72,9 +72,11 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self) -> dict:
+    def stop(self, t_begin: float | None = None, t_end: float | None = None) -> dict:
+        """Median SM clock and the throttle reasons seen among the samples taken between t_begin and t_end
+        (time.perf_counter values; None: all samples)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         self.proc.terminate()
@@ -84,20 +86,24 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        power = []
+        for (when, ln) in self.lines:
+            if (t_begin is not None and when < t_begin) or (t_end is not None and when > t_end):
+                continue
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 7:
                 continue
             try:
                 sm.append(float(parts[0]))
                 mx = float(parts[1])
+                power.append(float(parts[2]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None, "sm_max_mhz": mx,
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # --------------------------------------------------------------------------------- CPU baseline
@@ -343,6 +349,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         time.sleep(0.25)
     launches0 = int(L.ar_attn_launch_count())
     barrier()
+    load_t0 = time.perf_counter()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record(stream)
     for _ in range(args.steps):
@@ -350,11 +357,25 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     t1.record(stream)
     barrier()
     launches = int(L.ar_attn_launch_count()) - launches0
+    # nvidia-smi delivers a sample every 100 ms and K steps may last less than that: the same steps keep running,
+    # untimed, until the load has lasted 1.5 s, and the clocks are taken from the samples of that whole window
+    extra = max(1, int(1.5 / max(time.perf_counter() - load_t0, 1e-3) * args.steps) - args.steps)
+    extra = min(extra, 2000)
+    if world > 1:  # the steps contain collectives: every rank must run the same number of them
+        n_extra = torch.tensor([extra], dtype=torch.int32, device=device)
+        dist.broadcast(n_extra, src=0)
+        extra = int(n_extra.item())
+    for _ in range(extra):
+        step()
+    barrier()
+    load_t1 = time.perf_counter()
     ms_total = t0.elapsed_time(t1)
     status = int(L.ar_attn_last_status(None, stream.cuda_stream))
     if status != 0:
         raise SystemExit(f"device status after the timed region: {_abi.strerror(status)}")
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(load_t0 + 0.1, load_t1) if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "the timed steps and the same steps repeated right after them, %.2f s in all" % (load_t1 - load_t0)
     if world > 1:
         t = torch.tensor([ms_total], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
