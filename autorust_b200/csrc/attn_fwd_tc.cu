@@ -58,11 +58,14 @@ using namespace arptx;
 
 // Timeline of one CTA (-DAR_TRACE=3, debug builds only): clock() at fixed points of a few steps.
 #if defined(AR_TRACE) && AR_TRACE >= 3
+#ifndef AR_TL_J0
+#define AR_TL_J0 20  // first of the eight steps that are recorded
+#endif
 __device__ unsigned g_timeline[4 * 8 * 16];
 #define TL(role, j, ev)                                                                   \
   do {                                                                                    \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && ((j) >= 20 && (j) < 28))                      \
-      g_timeline[((role) * 8 + ((j) - 20)) * 16 + (ev)] = (unsigned)clock();              \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && ((j) >= AR_TL_J0 && (j) < AR_TL_J0 + 8))                      \
+      g_timeline[((role) * 8 + ((j) - AR_TL_J0)) * 16 + (ev)] = (unsigned)clock();              \
   } while (0)
 #else
 #define TL(role, j, ev)
@@ -99,14 +102,24 @@ __device__ __forceinline__ void commit_one(uint64_t* bar) {
 
 // One softmax step of one row: scores of 128 keys (sv, raw accumulator bits) -> P in TMEM, running
 // max m and running sum l updated, O rescaled in place when the max grows by more than the threshold.
-// EDGE selects the element-wise path for steps that touch the sequence end, the causal diagonal or
+// EDGE = 1 selects the element-wise path for steps that touch the sequence end, the causal diagonal or
 // an additive mask.
-template <int MODE, int D, bool EDGE>
+template <int MODE, int D, int EDGE>
 __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float& l, float c, int j, int col0, int row,
                                              int N, int causal, const float* __restrict__ mask, uint32_t tS,
                                              uint32_t tO, uint64_t* p_parts) {
   float mc;  // row maximum of this step in the scaled (log2) domain
-  if constexpr (EDGE) {
+  if constexpr (EDGE == 2) {
+    // Bounds only (sequence end and/or causal diagonal, no additive mask), f32 scores: the columns past the
+    // first excluded one get -inf and the step then runs as an interior one.  -inf times a positive scale stays
+    // -inf, 2^(-inf - m) is 0 and every row of such a step keeps at least one column, so the result is that of
+    // the element-wise path with its finite sentinel.
+    const int first_out = min(causal ? row - col0 + 1 : BN, N - col0);
+#pragma unroll
+    for (int i = 0; i < BN; i++)
+      if (i >= first_out) sv[i] = 0xff800000u;
+  }
+  if constexpr (EDGE == 1) {
     // leaves scaled logits in sv and c = 1
     const float* mrow = (mask != nullptr && row < N) ? mask + (size_t)row * N : nullptr;
     float mx = NEG;
@@ -186,7 +199,7 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
 #pragma unroll
     for (int i = 0; i < 16; i++) {
       uint64_t x2;
-      if constexpr (MODE == TC_SAGE && !EDGE) {
+      if constexpr (MODE == TC_SAGE && EDGE != 1) {
         // s32 -> f32 through the bits of 1.5 * 2^23 (exact for |x| < 2^22)
         x2 = add_f32x2(pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
                                   __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u)), magic2);
@@ -528,12 +541,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (C::QUANT) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
-      // Two separate instantiations: the interior step must not carry the merge points of the
-      // boundary path (that alone costs it ~300 cycles of scheduling freedom).
-      if (edge)
-        softmax_step<MODE, D, true>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      else
-        softmax_step<MODE, D, false>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+      // Separate instantiations: the interior step must not carry the merge points of the boundary paths
+      // (that alone costs it ~300 cycles of scheduling freedom).  A boundary step without an additive mask and
+      // with f32 scores masks by -inf and runs the interior code; an additive mask (whose -1e30 must tie with
+      // the initial running max) and the INT8 scores take the element-wise path.
+      if constexpr (MODE == TC_SAGE) {
+        if (edge)
+          softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+        else
+          softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+      } else {
+        if (!edge)
+          softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+        else if (mask == nullptr)
+          softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+        else
+          softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+      }
       TR_T(ts3); TR_ADD(sm_compute, ts2, ts3);
       if (r == 0) TL(t, j, 3);
       tmem_wait_st();
