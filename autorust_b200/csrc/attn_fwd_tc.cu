@@ -109,7 +109,21 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
                                              int N, int causal, const float* __restrict__ mask, uint32_t tS,
                                              uint32_t tO, uint64_t* p_parts) {
   float mc;  // row maximum of this step in the scaled (log2) domain
+  // INT8 scores stay integers through the maximum on interior steps only; a bounds-only boundary step converts
+  // them first (the same exact bit trick as below), so that the excluded columns can be marked with -inf
+  constexpr bool INT_SCORES = MODE == TC_SAGE && EDGE == 0;
   if constexpr (EDGE == 2) {
+    if constexpr (MODE == TC_SAGE) {
+      const uint64_t magic2 = pack_f32x2(-12582912.0f, -12582912.0f);
+#pragma unroll
+      for (int i = 0; i < BN; i += 2) {
+        float a, b;
+        unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(sv[i] + 0x4B400000u), __uint_as_float(sv[i + 1] + 0x4B400000u)),
+                               magic2), a, b);
+        sv[i] = __float_as_uint(a);
+        sv[i + 1] = __float_as_uint(b);
+      }
+    }
     // Bounds only (sequence end and/or causal diagonal, no additive mask), f32 scores: the columns past the
     // first excluded one get -inf and the step then runs as an interior one.  -inf times a positive scale stays
     // -inf, 2^(-inf - m) is 0 and every row of such a step keeps at least one column, so the result is that of
@@ -134,7 +148,7 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
     }
     c = 1.0f;
     mc = mx;
-  } else if constexpr (MODE == TC_SAGE) {
+  } else if constexpr (INT_SCORES) {
     // exact s32 scores: integer maximum first, one conversion for the row
     int m0 = (int)sv[0], m1 = (int)sv[1], m2 = (int)sv[2], m3 = (int)sv[3];
 #pragma unroll
@@ -199,7 +213,7 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
 #pragma unroll
     for (int i = 0; i < 16; i++) {
       uint64_t x2;
-      if constexpr (MODE == TC_SAGE && EDGE != 1) {
+      if constexpr (INT_SCORES) {
         // s32 -> f32 through the bits of 1.5 * 2^23 (exact for |x| < 2^22)
         x2 = add_f32x2(pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
                                   __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u)), magic2);
@@ -543,21 +557,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
       // Separate instantiations: the interior step must not carry the merge points of the boundary paths
       // (that alone costs it ~300 cycles of scheduling freedom).  A boundary step without an additive mask and
-      // with f32 scores masks by -inf and runs the interior code; an additive mask (whose -1e30 must tie with
-      // the initial running max) and the INT8 scores take the element-wise path.
-      if constexpr (MODE == TC_SAGE) {
-        if (edge)
-          softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-        else
-          softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      } else {
-        if (!edge)
-          softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-        else if (mask == nullptr)
-          softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-        else
-          softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      }
+      // masks by -inf and runs the interior code (INT8 scores are converted first); an additive mask, whose -1e30
+      // must tie with the initial running max, takes the element-wise path.
+      if (!edge)
+        softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+      else if (mask == nullptr)
+        softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+      else
+        softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
       TR_T(ts3); TR_ADD(sm_compute, ts2, ts3);
       if (r == 0) TL(t, j, 3);
       tmem_wait_st();
