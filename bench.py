@@ -440,9 +440,11 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
             "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (BASELINE config 3)",
-                       **w, "global_batch": B * world, "partition": ("batch-interleaved over ranks; bf16 outputs gathered per batch "
-                       "element under the next element's kernels, " + ("by peer-to-peer copies on the copy engines "
-                       "(CUDA IPC over NVLink) closed by a 4-byte NCCL all-reduce" if p2p else "by NCCL all-gather"))
+                       **w, "global_batch": B * world, "partition": ("one batch of B per rank (independent (batch, head) pairs, no reduction); bf16 "
+                       "outputs gathered on every rank " + ("piece by piece (37, 37, 37, 9, 8 heads: whole waves of CTAs, "
+                       "short tail) under the next piece's kernel, by peer-to-peer copies on the copy engines (CUDA IPC "
+                       "over NVLink) closed by a 4-byte NCCL all-reduce" if p2p else "per batch element under the next "
+                       "element's kernels, by NCCL all-gather"))
                        if world > 1 else "single GPU",
                        "l2": "inputs (805 MB) exceed L2 (126 MB); no flush needed",
                        "timing": "CUDA events on the launching stream, max over ranks"},
