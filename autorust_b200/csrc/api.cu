@@ -367,17 +367,6 @@ int ar_attn_last_status(void* workspace, void* cu_stream) {
   return host == 0 ? AR_OK : AR_ERR_DEVICE_WAIT;
 }
 
-#ifdef AR_TRACE
-// Debug builds only: copies the 31 cycle accumulators the traced kernel adds behind the status word.
-int ar_debug_read_trace(void* workspace, unsigned long long* out31, int clear) {
-  uint32_t* st = status_ptr(workspace);
-  if (!st) return AR_ERR_CUDA;
-  cudaDeviceSynchronize();
-  if (cudaMemcpy(out31, st + 2, 31 * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return AR_ERR_CUDA;
-  if (clear) cudaMemset(st + 2, 0, 31 * 8);
-  return AR_OK;
-}
-#endif
 
 uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 5) ? g_selected[mode].load() : 0; }
 uint64_t ar_attn_launch_count(void) { return g_launches.load(); }

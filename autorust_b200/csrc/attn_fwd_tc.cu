@@ -42,20 +42,6 @@ namespace ar {
 namespace {
 using namespace arptx;
 
-// Optional cycle accounting (-DAR_TRACE, debug builds only): per-role clock64 deltas accumulated
-// behind the status word.
-#if defined(AR_TRACE) && AR_TRACE < 3
-#define TR_DECL(n) unsigned tr_##n = 0
-#define TR_T(var) const unsigned var = (unsigned)clock()
-#define TR_ADD(n, a, b) tr_##n += (unsigned)(b) - (unsigned)(a)
-#define TR_FLUSH(slot, n) atomicAdd(((unsigned long long*)status) + 1 + (slot), (unsigned long long)tr_##n)
-#else
-#define TR_DECL(n)
-#define TR_T(var)
-#define TR_ADD(n, a, b)
-#define TR_FLUSH(slot, n)
-#endif
-
 // Timeline of one CTA (-DAR_TRACE=3, debug builds only): clock() at fixed points of a few steps.
 #if defined(AR_TRACE) && AR_TRACE >= 3
 #ifndef AR_TL_J0
@@ -267,14 +253,12 @@ struct Cfg {
   static constexpr int V_BOX_BYTES = MODE == TC_TF32 ? D * 128 : BN * 128;
   static constexpr int V_TILE_BYTES = BN * D * V_ESIZE;
   static constexpr int PV_KSTEPS = MODE == TC_TF32 ? BN / 8 : BN / 16;
-  static constexpr int P_COLS = MODE == TC_TF32 ? BN : BN / 2;  // TMEM columns of P
   static constexpr int STAGES = (2 * QK_TILE_BYTES + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2;
   static constexpr int SMEM_TILES = 2 * QK_TILE_BYTES + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
   static constexpr int NUM_BARS = 2 + 4 * STAGES + 4 + 2 * NPART;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
   static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_SAGE_FP8 ? KIND_F8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
-  static constexpr int PV_KIND = MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
   static constexpr uint32_t IDESC_QK = MODE == TC_SAGE       ? make_idesc(2, 1, 1, 0, 0, BM, BN)  // s8 x s8 -> s32
                                        : MODE == TC_SAGE_FP8 ? make_idesc(1, 0, 0, 0, 0, BM, BN)  // e4m3 x e4m3 -> f32
                                        : MODE == TC_TF32     ? make_idesc(1, 2, 2, 0, 0, BM, BN)
@@ -454,7 +438,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             mma_ts_lohi<KIND_F16>(d, a + s * 8, va + s * (2048 >> 4), v_hi, C::IDESC_PV, (acc || s > 0) ? 1u : 0u);
         }
       };
-      TR_DECL(mma_wait_kv); TR_DECL(mma_wait_p); TR_DECL(mma_issue); TR_T(tm_begin);
+
       bool ok = true;
       if (nkv_max > 0) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, abort_flag, status, 0x20));
       for (int t = 0; t < 2 && ok; t++) {
@@ -470,16 +454,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int s = j % ST;
         const int s1 = (j + 1) % ST;
         if (lane == 0) TL(2, j, 0);
-        TR_T(tv0);
+
         ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22));
-        TR_T(tv1); TR_ADD(mma_wait_kv, tv0, tv1);
+
         if (lane == 0) TL(2, j, 1);
         if (!ok) break;
         // K(j+1) is needed right after the last PV of a tile: see it arrive now, off the critical path
         if (j + 1 < nkv_max) {
-          TR_T(tk0);
+
           ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24));
-          TR_T(tk1); TR_ADD(mma_wait_kv, tk0, tk1);
+
           if (!ok) break;
         }
         for (int t = 0; t < 2 && ok; t++) {
@@ -487,23 +471,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           // P arrives in NPART parts: the first PV MMAs run under the exponentials of the later parts
 #pragma unroll
           for (int hf = 0; hf < NPART; hf++) {
-            TR_T(tp0);
+
             ok = __all_sync(0xffffffffu, mbar_wait(&p_part[NPART * t + hf], j & 1, abort_flag, status, 0x23));
-            TR_T(tp1); TR_ADD(mma_wait_p, tp0, tp1);
+
             if (lane == 0 && hf == NPART - 1) TL(2, j, 2 + 4 * t);
             if (!ok) break;
             tc_fence_after();
-            TR_T(ti0);
+
             issue_pv(t, s, j > 0, hf);
-            TR_T(ti1); TR_ADD(mma_issue, ti0, ti1);
+
           }
           if (!ok) break;
           if (lane == 0) TL(2, j, 3 + 4 * t);
           if (j + 1 < nkv[t]) {
             if (lane == 0) TL(2, j, 4 + 4 * t);
-            TR_T(tq0);
+
             issue_qk(t, s1);
-            TR_T(tq1); TR_ADD(mma_issue, tq0, tq1);
+
             if (lane == 0) TL(2, j, 5 + 4 * t);
             commit_one(&s_full[t]);
           } else {
@@ -515,9 +499,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (j + 1 < nkv_max) commit_one(&k_empty[s1]);
         if (lane == 0) TL(2, j, 10);
       }
-#ifdef AR_TRACE
-      if (lane == 0) { TR_T(tm_end); TR_DECL(mma_total); TR_ADD(mma_total, tm_begin, tm_end); TR_FLUSH(5, mma_wait_p); TR_FLUSH(6, mma_wait_kv); TR_FLUSH(7, mma_issue); TR_FLUSH(8, mma_total); }
-#endif
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------ softmax warps
@@ -533,13 +514,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     float qs = 1.f;
     if (C::QUANT && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
     float m = NEG, l = 0.f;
-    TR_DECL(sm_wait_s); TR_DECL(sm_ld); TR_DECL(sm_compute); TR_DECL(sm_st); TR_DECL(sm_steps); TR_T(tsm_begin);
+
     bool ok = true;
     for (int j = 0; j < nkv[t]; j++) {
       if (r == 0) TL(t, j, 0);
-      TR_T(ts0);
+
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, status, 0x30));
-      TR_T(ts1); TR_ADD(sm_wait_s, ts0, ts1);
+
       if (r == 0) TL(t, j, 1);
       if (!ok) break;
       tc_fence_after();
@@ -549,7 +530,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 64, sv + 64);
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
-      TR_T(ts2); TR_ADD(sm_ld, ts1, ts2);
+
       if (r == 0) TL(t, j, 2);
       float c = scale_log2;
       if (C::QUANT) c *= qs * k_scale[(size_t)kvbh * nblk + j];
@@ -565,17 +546,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
       else
         softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      TR_T(ts3); TR_ADD(sm_compute, ts2, ts3);
+
       if (r == 0) TL(t, j, 3);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_part[NPART * t + NPART - 1]);
-      TR_T(ts4); TR_ADD(sm_st, ts3, ts4); TR_ADD(sm_steps, 0, 1);
+
       if (r == 0) TL(t, j, 4);
     }
-#ifdef AR_TRACE
-    if (tid == 0) { TR_T(tsm_end); TR_DECL(sm_total); TR_ADD(sm_total, tsm_begin, tsm_end); TR_FLUSH(0, sm_wait_s); TR_FLUSH(1, sm_ld); TR_FLUSH(2, sm_compute); TR_FLUSH(3, sm_st); TR_FLUSH(4, sm_total); TR_FLUSH(9, sm_steps); }
-#endif
     if (ok && nkv[t] > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], 0, abort_flag, status, 0x31));
       if (ok) {
