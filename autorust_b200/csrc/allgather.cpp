@@ -20,6 +20,13 @@ struct Comm {
   size_t bytes = 0;
   std::vector<void*> peer;
   int* fence_word = nullptr;
+  // pushes to different peers go out on separate streams (separate copy engines); events tie them to the caller's
+  static constexpr int kSide = 4;
+  static constexpr int kEvents = 64;
+  cudaStream_t side[kSide] = {};
+  cudaEvent_t ring[kEvents] = {};
+  int next_event = 0;
+  bool side_dirty = false;
 };
 bool cuda_ok(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return true;
@@ -144,6 +151,10 @@ int ar_gather_p2p_open(void* comm, size_t bytes) {
   }
   if (!cuda_ok(cudaMalloc((void**)&c->fence_word, sizeof(int)), "cudaMalloc")) return -6;
   if (!cuda_ok(cudaMemset(c->fence_word, 0, sizeof(int)), "cudaMemset")) return -6;
+  for (int i = 0; i < Comm::kSide; i++)
+    if (!cuda_ok(cudaStreamCreateWithFlags(&c->side[i], cudaStreamNonBlocking), "cudaStreamCreate")) return -6;
+  for (int i = 0; i < Comm::kEvents; i++)
+    if (!cuda_ok(cudaEventCreateWithFlags(&c->ring[i], cudaEventDisableTiming), "cudaEventCreate")) return -6;
   return 0;
 }
 
@@ -154,14 +165,21 @@ int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream)
   Comm* c = static_cast<Comm*>(comm);
   if (!c->local || offset > c->bytes || bytes > c->bytes - offset) return -5;
   const char* src = static_cast<const char*>(c->local) + offset;
-  // one copy per peer, starting with the next rank so that the ranks do not all write to the same peer at once
+  // The copies start after what the caller's stream holds now ...
+  cudaEvent_t ready = c->ring[c->next_event];
+  c->next_event = (c->next_event + 1) % Comm::kEvents;
+  if (!cuda_ok(cudaEventRecord(ready, (cudaStream_t)cu_stream), "cudaEventRecord")) return -6;
+  // ... one per peer, spread over the side streams so that several copy engines work at once, starting with the
+  // next rank so that the ranks do not all write to the same peer at the same time.
   for (int i = 1; i < c->world; i++) {
     const int r = (c->rank + i) % c->world;
-    if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset, src, bytes, cudaMemcpyDeviceToDevice,
-                                 (cudaStream_t)cu_stream),
+    cudaStream_t s = c->side[(i - 1) % Comm::kSide];
+    if (i - 1 < Comm::kSide && !cuda_ok(cudaStreamWaitEvent(s, ready, 0), "cudaStreamWaitEvent")) return -6;
+    if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset, src, bytes, cudaMemcpyDeviceToDevice, s),
                  "cudaMemcpyAsync(peer)"))
       return -6;
   }
+  c->side_dirty = true;
   return 0;
 }
 
@@ -169,6 +187,16 @@ int ar_gather_p2p_fence(void* comm, void* cu_stream) {
   if (!comm) return -2;
   Comm* c = static_cast<Comm*>(comm);
   if (!c->fence_word) return -5;
+  // the caller's stream first collects the side streams' copies
+  if (c->side_dirty) {
+    for (int i = 0; i < Comm::kSide; i++) {
+      cudaEvent_t done = c->ring[c->next_event];
+      c->next_event = (c->next_event + 1) % Comm::kEvents;
+      if (!cuda_ok(cudaEventRecord(done, c->side[i]), "cudaEventRecord")) return -6;
+      if (!cuda_ok(cudaStreamWaitEvent((cudaStream_t)cu_stream, done, 0), "cudaStreamWaitEvent")) return -6;
+    }
+    c->side_dirty = false;
+  }
   // Stream order on every rank puts its pushes before its part of this all-reduce, and the all-reduce cannot
   // finish anywhere before every rank has started its part.
   return check(ncclAllReduce(c->fence_word, c->fence_word, 1, ncclInt32, ncclMax, c->comm, (cudaStream_t)cu_stream),
@@ -187,6 +215,16 @@ void ar_gather_p2p_close(void* comm) {
   c->peer.clear();
   if (c->fence_word) cudaFree(c->fence_word);
   c->fence_word = nullptr;
+  for (int i = 0; i < Comm::kSide; i++)
+    if (c->side[i]) {
+      cudaStreamDestroy(c->side[i]);
+      c->side[i] = nullptr;
+    }
+  for (int i = 0; i < Comm::kEvents; i++)
+    if (c->ring[i]) {
+      cudaEventDestroy(c->ring[i]);
+      c->ring[i] = nullptr;
+    }
   cudaFree(c->local);
   c->local = nullptr;
   c->bytes = 0;

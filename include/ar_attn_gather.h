@@ -54,8 +54,10 @@ int ar_gather_p2p_open(void* comm, size_t bytes);
 /* This rank's buffer (device memory owned by the library until ar_gather_p2p_close), or NULL. */
 void* ar_gather_p2p_buffer(void* comm);
 
-/* Copies [offset, offset + bytes) of the local buffer to the same range of every peer's buffer, asynchronously on
- * `cu_stream`, after whatever that stream holds (the event of the kernel that produced the range). */
+/* Copies [offset, offset + bytes) of the local buffer to the same range of every peer's buffer, asynchronously,
+ * after whatever `cu_stream` holds at the time of the call (the kernel that produced the range).  The copies run on
+ * streams of the library's own, one peer after the other round-robin over them, so that several copy engines work at
+ * once; ar_gather_p2p_fence joins them back into `cu_stream`. */
 int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream);
 
 /* Queues on `cu_stream` the point after which every push that any rank queued before ITS fence has landed in
