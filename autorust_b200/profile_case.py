@@ -14,7 +14,7 @@ from . import ops
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="sage", choices=["exact", "tf32", "bf16", "sage"])
+    ap.add_argument("--mode", default="sage", choices=["exact", "tf32", "bf16", "sage", "sage_fp8"])
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--Hkv", type=int, default=0)
