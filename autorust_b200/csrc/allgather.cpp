@@ -164,20 +164,35 @@ int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream)
   if (!comm) return -2;
   Comm* c = static_cast<Comm*>(comm);
   if (!c->local || offset > c->bytes || bytes > c->bytes - offset) return -5;
+  if (c->world < 2 || bytes == 0) return 0;
   const char* src = static_cast<const char*>(c->local) + offset;
   // The copies start after what the caller's stream holds now ...
   cudaEvent_t ready = c->ring[c->next_event];
   c->next_event = (c->next_event + 1) % Comm::kEvents;
   if (!cuda_ok(cudaEventRecord(ready, (cudaStream_t)cu_stream), "cudaEventRecord")) return -6;
-  // ... one per peer, spread over the side streams so that several copy engines work at once, starting with the
-  // next rank so that the ranks do not all write to the same peer at the same time.
+  // ... spread over the side streams so that several copy engines work at once: one copy per peer, or with fewer
+  // peers than streams each peer's range cut into pieces, starting with the next rank so that the ranks do not all
+  // write to the same peer at the same time.
+  const int peers = c->world - 1;
+  const int pieces = peers >= Comm::kSide ? 1 : Comm::kSide / peers;
+  const size_t piece = ((bytes + (size_t)pieces - 1) / (size_t)pieces + 255) / 256 * 256;
+  bool waited[Comm::kSide] = {};
+  int turn = 0;
   for (int i = 1; i < c->world; i++) {
     const int r = (c->rank + i) % c->world;
-    cudaStream_t s = c->side[(i - 1) % Comm::kSide];
-    if (i - 1 < Comm::kSide && !cuda_ok(cudaStreamWaitEvent(s, ready, 0), "cudaStreamWaitEvent")) return -6;
-    if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset, src, bytes, cudaMemcpyDeviceToDevice, s),
-                 "cudaMemcpyAsync(peer)"))
-      return -6;
+    for (size_t at = 0; at < bytes; at += piece, turn++) {
+      const int si = turn % Comm::kSide;
+      cudaStream_t s = c->side[si];
+      if (!waited[si]) {
+        if (!cuda_ok(cudaStreamWaitEvent(s, ready, 0), "cudaStreamWaitEvent")) return -6;
+        waited[si] = true;
+      }
+      const size_t n = bytes - at < piece ? bytes - at : piece;
+      if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset + at, src + at, n,
+                                   cudaMemcpyDeviceToDevice, s),
+                   "cudaMemcpyAsync(peer)"))
+        return -6;
+    }
   }
   c->side_dirty = true;
   return 0;
