@@ -327,7 +327,35 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     g_timeline[3 * 8 * 16 + 1] = (unsigned)gt;
   }
 #endif
-  if (tid == 0) {
+  // Q and one K/V pair per ring stage: nothing to wait for, the stages are empty
+  auto issue_q = [&]() {
+    for (int t = 0; t < 2; t++) {
+      if (nkv[t] == 0) continue;
+      mbar_arrive_expect_tx(&q_full[t], C::QK_TILE_BYTES);
+      for (int bx = 0; bx < C::QK_BOXES; bx++)
+        load_tile(sQ + t * C::QK_TILE_BYTES + bx * (BM * 128), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS, q0 + t * BM, h, 0);
+    }
+  };
+  auto issue_k = [&](int j) {
+    const int s = j % ST;
+    mbar_arrive_expect_tx(&k_full[s], C::QK_TILE_BYTES);
+    for (int bx = 0; bx < C::QK_BOXES; bx++)
+      load_tile(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN, kvh, 1);
+  };
+  auto issue_v = [&](int j) {
+    const int s = j % ST;
+    mbar_arrive_expect_tx(&v_full[s], C::V_TILE_BYTES);
+    for (int bx = 0; bx < C::V_BOXES; bx++) {
+      if constexpr (MODE == TC_TF32)  // transposed V: x = key, y = d
+        load_tile(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], j * BN + bx * 32, 0, kvh, 2);
+      else
+        load_tile(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], bx * 64, j * BN, kvh, 2);
+    }
+  };
+  const int preloaded = min(ST, nkv_max);  // K/V pairs issued before the CTA-wide barrier below
+  // The producer thread sets up the barriers and starts the first loads itself, before the CTA meets: the copies
+  // are in flight while the TMEM allocation and the barrier complete (a CTA of a short sequence is mostly latency).
+  if (warp == 8 && lane == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; i++) {
       mbar_init(&q_full[i], 1);
@@ -342,15 +370,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(&v_empty[i], 1);
     }
     fence_mbar_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    issue_q();
+    for (int j = 0; j < preloaded; j++) {
+      issue_k(j);
+      issue_v(j);
+    }
   }
   if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
-  }
-  if (warp == 8 && lane == 0) {
-    prefetch_tmap(&tm_q);
-    prefetch_tmap(&tm_k);
-    prefetch_tmap(&tm_v);
   }
   tc_fence_before();
   __syncthreads();
@@ -361,28 +392,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int t = 0; t < 2; t++) {
-        if (nkv[t] == 0) continue;
-        mbar_arrive_expect_tx(&q_full[t], C::QK_TILE_BYTES);
-        for (int bx = 0; bx < C::QK_BOXES; bx++)
-          load_tile(sQ + t * C::QK_TILE_BYTES + bx * (BM * 128), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS, q0 + t * BM, h, 0);
-      }
-      int issued = 0;
-      for (int j = 0; j < nkv_max; j++) {
+      int issued = preloaded;
+      for (int j = preloaded; j < nkv_max; j++) {
         const int s = j % ST;
         const int n = j / ST;
-        if (n > 0 && !mbar_wait(&k_empty[s], (n - 1) & 1, abort_flag, status, 0x10)) break;
-        mbar_arrive_expect_tx(&k_full[s], C::QK_TILE_BYTES);
-        for (int bx = 0; bx < C::QK_BOXES; bx++)
-          load_tile(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN, kvh, 1);
-        if (n > 0 && !mbar_wait(&v_empty[s], (n - 1) & 1, abort_flag, status, 0x11)) break;
-        mbar_arrive_expect_tx(&v_full[s], C::V_TILE_BYTES);
-        for (int bx = 0; bx < C::V_BOXES; bx++) {
-          if constexpr (MODE == TC_TF32)  // transposed V: x = key, y = d
-            load_tile(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], j * BN + bx * 32, 0, kvh, 2);
-          else
-            load_tile(sV + s * C::V_TILE_BYTES + bx * C::V_BOX_BYTES, &tm_v, &v_full[s], bx * 64, j * BN, kvh, 2);
+        // a stage is free once the MMAs that read pair j - ST from it have completed; K's comes free a step earlier
+        if (!mbar_wait(&k_empty[s], (n - 1) & 1, abort_flag, status, 0x10)) break;
+        issue_k(j);
+        if (!mbar_wait(&v_empty[s], (n - 1) & 1, abort_flag, status, 0x11)) {
+          mbar_wait_quiet(&k_full[s], n & 1);  // the K tile just started
+          break;
         }
+        issue_v(j);
         issued = j + 1;
       }
       if (*abort_flag) {
