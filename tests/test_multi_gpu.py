@@ -94,6 +94,7 @@ def _gpu_rank(rank, world, port, seed, result):
     import torch.distributed as dist
     from autorust_b200 import ops
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["AR_GATHER_STREAMS"] = "3"  # the copy-engine gather cut over several streams (its default is one)
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             timeout=datetime.timedelta(seconds=120))
