@@ -31,6 +31,9 @@ SYMBOLS = (
     "ar_attn_workspace_bytes",
     "ar_attn_forward",
     "ar_attn_forward_strided",
+    "ar_attn_train_forward",
+    "ar_attn_train_workspace_bytes",
+    "ar_attn_train_backward",
     "ar_sage_quantize",
     "ar_sage_quantize_fp8",
     "ar_sage_attention_prequantized",
@@ -71,6 +74,12 @@ def load() -> ctypes.CDLL:
     L.ar_attn_forward.restype = ci
     L.ar_attn_forward_strided.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, p, p, p, p, ctypes.c_size_t, p]
     L.ar_attn_forward_strided.restype = ci
+    L.ar_attn_train_forward.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p]
+    L.ar_attn_train_forward.restype = ci
+    L.ar_attn_train_workspace_bytes.argtypes = [i64, i64, i64]
+    L.ar_attn_train_workspace_bytes.restype = ctypes.c_size_t
+    L.ar_attn_train_backward.argtypes = [p] * 10 + [i64] * 5 + [ci, p, ctypes.c_size_t, p]
+    L.ar_attn_train_backward.restype = ci
     L.ar_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, ci, p]
     L.ar_sage_quantize.restype = ci
     L.ar_sage_attention_prequantized.argtypes = [p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]

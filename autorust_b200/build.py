@@ -31,7 +31,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
-KERNEL_SOURCES = ["attn_fwd_tc.cu", "attn_fwd_exact.cu", "sage_prologue.cu", "api.cu", "sage_static.cu"]
+KERNEL_SOURCES = ["attn_fwd_tc.cu", "attn_fwd_exact.cu", "attn_train.cu", "sage_prologue.cu", "api.cu", "sage_static.cu"]
 
 
 def _nvcc() -> str:

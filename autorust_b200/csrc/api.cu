@@ -302,6 +302,47 @@ int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, c
   return AR_OK;
 }
 
+int ar_attn_train_forward(const float* q, const float* k, const float* v, float* o, float* lse, const float* mask,
+                          int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* cu_stream) {
+  if (!q || !k || !v || !o || !lse) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if (!mode_has_kernel(AR_MODE_EXACT_F32, AR_DTYPE_F32, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  ar::ExactArgs e{q, k, v, o, mask, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, causal ? 1 : 0};
+  e.lse = lse;
+  if (ar::launch_attn_exact(e, (cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;
+  g_launches++;
+  return AR_OK;
+}
+
+size_t ar_attn_train_workspace_bytes(int64_t B, int64_t Hq, int64_t S) {
+  if (B <= 0 || Hq <= 0 || S <= 0) return 0;
+  return align_up(sizeof(float) * (size_t)(B * Hq * S), 256);
+}
+
+int ar_attn_train_backward(const float* q, const float* k, const float* v, const float* o, const float* d_o,
+                           const float* lse, const float* mask, float* dq, float* dk, float* dv, int64_t B,
+                           int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                           size_t workspace_bytes, void* cu_stream) {
+  if (!q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv || !workspace) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if (!mode_has_kernel(AR_MODE_EXACT_F32, AR_DTYPE_F32, B, Hq, S, D) || B * Hkv > 65535) return AR_ERR_UNSUPPORTED;
+  if (workspace_bytes < ar_attn_train_workspace_bytes(B, Hq, S)) return AR_ERR_WORKSPACE;
+  for (const void* p : {(const void*)q, (const void*)k, (const void*)v, (const void*)o, (const void*)d_o, (const void*)dq,
+                        (const void*)dk, (const void*)dv, (const void*)workspace})
+    if (!aligned16(p)) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  ar::TrainBwdArgs a{q, k, v, o, d_o, lse, mask, dq, dk, dv, (float*)workspace, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D,
+                     causal ? 1 : 0};
+  int launches = 0;
+  const cudaError_t e = ar::launch_attn_train_backward(a, (cudaStream_t)cu_stream, &launches);
+  g_launches += (uint64_t)launches;
+  return e == cudaSuccess ? AR_OK : AR_ERR_CUDA;
+}
+
 namespace {
 int sage_prequantized_any(int mode, const void* q8, const void* k8, const float* q_scale, const float* k_scale,
                           const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B, int64_t Hq,

@@ -47,8 +47,20 @@ struct ExactArgs {
   const float* mask;
   int B, Hq, Hkv, S, D;
   int causal;
+  float* lse = nullptr;  // [B*Hq, S]: when set, the rows' log-sum-exp is written as well (training forward)
 };
 cudaError_t launch_attn_exact(const ExactArgs& a, cudaStream_t stream);
+
+// Training path (attn_train.cu): gradients of the exact f32 forward, from its saved log-sum-exp.
+struct TrainBwdArgs {
+  const float *q, *k, *v, *o, *d_o, *lse, *mask;
+  float *dq, *dk, *dv;
+  float* delta;  // [B*Hq, S] scratch: D_i = O_i . dO_i
+  int B, Hq, Hkv, S, D;
+  int causal;
+};
+// Launches prep, dQ and dK/dV; *launches returns the number of kernels.
+cudaError_t launch_attn_train_backward(const TrainBwdArgs& a, cudaStream_t stream, int* launches);
 
 // Sage prologue (sage_prologue.cu).
 struct PrologueArgs {

@@ -27,8 +27,8 @@ struct ExactCfg {
 template <int D>
 __global__ void __launch_bounds__(256) attn_fwd_exact_kernel(const float* __restrict__ Q, const float* __restrict__ K,
                                                              const float* __restrict__ V, float* __restrict__ O,
-                                                             const float* __restrict__ M, int N, int Hq, int Hkv,
-                                                             int causal) {
+                                                             const float* __restrict__ M, float* __restrict__ LSE,
+                                                             int N, int Hq, int Hkv, int causal) {
   using C = ExactCfg<D>;
   extern __shared__ __align__(16) float smem_f[];
   float* sQ = smem_f;
@@ -166,6 +166,8 @@ __global__ void __launch_bounds__(256) attn_fwd_exact_kernel(const float* __rest
     const int row = q0 + ty * 4 + i;
     if (row >= N) continue;
     const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    // training forward: the row's log-sum-exp, LSE = m + log(l) (src/runtime/cuda_flash_train.rs:8-11)
+    if (LSE != nullptr && tx == 0) LSE[(size_t)bh * N + row] = m[i] + logf(l[i]);
     float* dst = O + ((size_t)bh * N + row) * D;
 #pragma unroll
     for (int dd = 0; dd < OD; dd++)
@@ -188,7 +190,7 @@ cudaError_t launch_exact(const ExactArgs& a, cudaStream_t stream) {
     configured[dev] = true;
   }
   dim3 grid((a.S + BQ - 1) / BQ, a.B * a.Hq, 1);
-  kern<<<grid, 256, C::SMEM_BYTES, stream>>>(a.q, a.k, a.v, a.out, a.mask, a.S, a.Hq, a.Hkv, a.causal);
+  kern<<<grid, 256, C::SMEM_BYTES, stream>>>(a.q, a.k, a.v, a.out, a.mask, a.lse, a.S, a.Hq, a.Hkv, a.causal);
   return cudaGetLastError();
 }
 

@@ -323,6 +323,73 @@ std::optional<Tensor> fused_attention_ex(const Tensor& q, const Tensor& k, const
   return out;
 }
 
+// ------------------------------------------------------------------------------ training path
+namespace {
+// train_shape of the reference (src/models/flash_attention.rs:760-773): rank 4, equal lengths and head sizes, GQA by
+// head counts.
+bool train_shape(const Tensor& q, const Tensor& k, const Tensor& v, int64_t* b, int64_t* h, int64_t* n, int64_t* d,
+                 int64_t* hk) {
+  if (q.shape().size() != 4 || k.shape().size() != 4 || v.shape().size() != 4) return false;
+  *b = q.shape()[0]; *h = q.shape()[1]; *n = q.shape()[2]; *d = q.shape()[3];
+  *hk = k.shape()[1];
+  if (k.shape() != v.shape() || k.shape()[0] != *b || k.shape()[2] != *n || k.shape()[3] != *d) return false;
+  return *hk > 0 && *h % *hk == 0;
+}
+bool train_gates(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* mask, int64_t b, int64_t h, int64_t hk,
+                 int64_t n, int64_t d) {
+  if (q.dtype() != DType::Float32 || k.dtype() != DType::Float32 || v.dtype() != DType::Float32) return false;
+  if (k.device() != q.device() || v.device() != q.device()) return false;
+  if (mask) {
+    const auto& ms = mask->shape();
+    if (mask->dtype() != DType::Float32 || ms.size() != 2 || ms[0] != n || ms[1] != n) return false;
+  }
+  return ar_attn_supported(AR_MODE_EXACT_F32, AR_DTYPE_F32, b, h, hk, n, d, 0, mask ? 1 : 0) == 1;
+}
+}  // namespace
+
+std::optional<std::pair<Tensor, Tensor>> fused_attention_train(const Tensor& q, const Tensor& k, const Tensor& v,
+                                                               const Tensor* attn_mask, bool is_causal, Session& sess) {
+  (void)sess;  // the reference runs these launches directly, outside the captured list (flash_attention.rs:836-866)
+  int64_t b, h, n, d, hk;
+  if (!train_shape(q, k, v, &b, &h, &n, &d, &hk)) return std::nullopt;
+  DeviceGuard guard(q.device());
+  if (!train_gates(q, k, v, attn_mask, b, h, hk, n, d)) return std::nullopt;
+  Tensor out = Tensor::empty(DType::Float32, q.shape(), q.device());
+  Tensor lse = Tensor::empty(DType::Float32, {b, h, n}, q.device());
+  const int rc = ar_attn_train_forward((const float*)q.data_ptr(), (const float*)k.data_ptr(), (const float*)v.data_ptr(),
+                                       (float*)out.data_ptr(), (float*)lse.data_ptr(),
+                                       attn_mask ? (const float*)attn_mask->data_ptr() : nullptr, b, h, hk, n, d,
+                                       is_causal ? 1 : 0, dev_state(q.device()).stream);
+  if (rc != AR_OK) throw Error(std::string("ar_fl_fwd: ") + ar_attn_strerror(rc));
+  return std::make_pair(out, lse);
+}
+
+std::optional<AttentionGrads> fused_attention_backward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                                       const Tensor& lse, const Tensor& dout, const Tensor* attn_mask,
+                                                       bool is_causal, Session& sess) {
+  (void)sess;
+  int64_t b, h, n, d, hk;
+  if (!train_shape(q, k, v, &b, &h, &n, &d, &hk)) return std::nullopt;
+  DeviceGuard guard(q.device());
+  if (!train_gates(q, k, v, attn_mask, b, h, hk, n, d)) return std::nullopt;
+  if (o.shape() != q.shape() || dout.shape() != q.shape() || o.dtype() != DType::Float32 ||
+      dout.dtype() != DType::Float32 || lse.dtype() != DType::Float32 || lse.numel() != b * h * n)
+    return std::nullopt;
+  AttentionGrads g;
+  g.dq = Tensor::empty(DType::Float32, q.shape(), q.device());
+  g.dk = Tensor::empty(DType::Float32, k.shape(), q.device());
+  g.dv = Tensor::empty(DType::Float32, v.shape(), q.device());
+  const size_t ws_bytes = ar_attn_train_workspace_bytes(b, h, n);
+  Buffer ws(q.device(), ws_bytes);
+  const int rc = ar_attn_train_backward(
+      (const float*)q.data_ptr(), (const float*)k.data_ptr(), (const float*)v.data_ptr(), (const float*)o.data_ptr(),
+      (const float*)dout.data_ptr(), (const float*)lse.data_ptr(), attn_mask ? (const float*)attn_mask->data_ptr() : nullptr,
+      (float*)g.dq.data_ptr(), (float*)g.dk.data_ptr(), (float*)g.dv.data_ptr(), b, h, hk, n, d, is_causal ? 1 : 0, ws.ptr(),
+      ws.nbytes(), dev_state(q.device()).stream);
+  if (rc != AR_OK) throw Error(std::string("ar_fl_bwd: ") + ar_attn_strerror(rc));
+  return g;  // the scratch goes back to the cache; reuse is ordered on the device's one launch stream
+}
+
 // ------------------------------------------------------------------- streamed host-to-host form
 namespace {
 // Kernel choice of fused_attention_ex for a problem of `b` batches: sage > bf16 > tf32 > scalar.

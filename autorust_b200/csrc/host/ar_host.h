@@ -20,6 +20,7 @@
 #include <optional>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace arh {
@@ -160,6 +161,19 @@ class Session {
 // (rank, shape, dtype or mask form not covered).
 std::optional<Tensor> fused_attention_ex(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* attn_mask,
                                          bool is_causal, bool enable_gqa, bool quantized, Session& sess);
+
+// src/models/flash_attention.rs:775-870: the forward for training, (O, LSE) with LSE [B, Hq, S] f32.  nullopt where the
+// reference returns None: not f32, ranks or shapes that do not match, a mask that is not dense f32 [S, S], a head size
+// without a kernel (the reference: D = 64 only; here 64 and 128).  Not wired into an autograd here either.
+std::optional<std::pair<Tensor, Tensor>> fused_attention_train(const Tensor& q, const Tensor& k, const Tensor& v,
+                                                               const Tensor* attn_mask, bool is_causal, Session& sess);
+// src/models/flash_attention.rs:873-977: (dQ, dK, dV) from the forward's O and LSE and the output gradient.
+struct AttentionGrads {
+  Tensor dq, dk, dv;
+};
+std::optional<AttentionGrads> fused_attention_backward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                                       const Tensor& lse, const Tensor& dout, const Tensor* attn_mask,
+                                                       bool is_causal, Session& sess);
 
 // Host-to-host form of the operator, for callers whose q, k, v live in host memory (pinned, for the
 // copies to overlap) and whose result goes back to host memory.  The (batch, kv head) groups of the

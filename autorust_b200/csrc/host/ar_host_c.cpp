@@ -83,6 +83,30 @@ int arh_fused_attention_ex(void* q, void* k, void* v, void* mask, int is_causal,
   });
 }
 
+// fused_attention_train: *out / *lse = NULL where the reference returns None.
+int arh_fused_attention_train(void* q, void* k, void* v, void* mask, int is_causal, void* sess, void** out, void** lse) {
+  return guarded([&] {
+    auto r = arh::fused_attention_train(*static_cast<arh::Tensor*>(q), *static_cast<arh::Tensor*>(k),
+                                        *static_cast<arh::Tensor*>(v), static_cast<arh::Tensor*>(mask), is_causal != 0,
+                                        *static_cast<arh::Session*>(sess));
+    *out = r ? new arh::Tensor(r->first) : nullptr;
+    *lse = r ? new arh::Tensor(r->second) : nullptr;
+  });
+}
+// fused_attention_backward: the three outputs are NULL where the reference returns None.
+int arh_fused_attention_backward(void* q, void* k, void* v, void* o, void* lse, void* dout, void* mask, int is_causal,
+                                 void* sess, void** dq, void** dk, void** dv) {
+  return guarded([&] {
+    auto r = arh::fused_attention_backward(*static_cast<arh::Tensor*>(q), *static_cast<arh::Tensor*>(k),
+                                           *static_cast<arh::Tensor*>(v), *static_cast<arh::Tensor*>(o),
+                                           *static_cast<arh::Tensor*>(lse), *static_cast<arh::Tensor*>(dout),
+                                           static_cast<arh::Tensor*>(mask), is_causal != 0, *static_cast<arh::Session*>(sess));
+    *dq = r ? new arh::Tensor(r->dq) : nullptr;
+    *dk = r ? new arh::Tensor(r->dk) : nullptr;
+    *dv = r ? new arh::Tensor(r->dv) : nullptr;
+  });
+}
+
 // Streamed host-to-host form (arh::attention_host): kind 1 = flash, 2 = sage; host pointers throughout.
 int arh_attention_host(int kind, const void* q, const void* k, const void* v, void* out, int dtype, int64_t B, int64_t Hq,
                        int64_t Hkv, int64_t S, int64_t D, const float* mask_host, int is_causal, int64_t groups_per_chunk,

@@ -60,6 +60,8 @@ def load() -> ctypes.CDLL:
     L.arh_session_clear.restype = None
     L.arh_attention.argtypes = [p, p, p, p, ctypes.c_double, ci, ci, p, pp]
     L.arh_fused_attention_ex.argtypes = [p, p, p, p, ci, ci, ci, p, pp]
+    L.arh_fused_attention_train.argtypes = [p, p, p, p, ci, p, pp, pp]
+    L.arh_fused_attention_backward.argtypes = [p, p, p, p, p, p, p, ci, p, pp, pp, pp]
     L.arh_attention_host.argtypes = [ci, p, p, p, p, ci, i64, i64, i64, i64, i64, p, ci, i64, ci]
     L.arh_settings_set.argtypes = [ci, ci, ci, ci]
     L.arh_settings_set.restype = None
@@ -245,6 +247,24 @@ def fused_attention_ex(q: Tensor, k: Tensor, v: Tensor, attn_mask, is_causal: bo
     _check(load().arh_fused_attention_ex(q._h, k._h, v._h, attn_mask._h if attn_mask is not None else None,
                                          int(is_causal), int(enable_gqa), int(quantized), sess._h, ctypes.byref(out)))
     return Tensor(out) if out.value else None
+
+
+def fused_attention_train(q: Tensor, k: Tensor, v: Tensor, attn_mask, is_causal: bool, sess: Session):
+    """src/models/flash_attention.rs:789: (O, LSE), or None where the reference returns None."""
+    out, lse = ctypes.c_void_p(), ctypes.c_void_p()
+    _check(load().arh_fused_attention_train(q._h, k._h, v._h, attn_mask._h if attn_mask is not None else None,
+                                            int(is_causal), sess._h, ctypes.byref(out), ctypes.byref(lse)))
+    return (Tensor(out), Tensor(lse)) if out.value else None
+
+
+def fused_attention_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, dout: Tensor, attn_mask,
+                             is_causal: bool, sess: Session):
+    """src/models/flash_attention.rs:873: (dQ, dK, dV), or None where the reference returns None."""
+    dq, dk, dv = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+    _check(load().arh_fused_attention_backward(q._h, k._h, v._h, o._h, lse._h, dout._h,
+                                               attn_mask._h if attn_mask is not None else None, int(is_causal), sess._h,
+                                               ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv)))
+    return (Tensor(dq), Tensor(dk), Tensor(dv)) if dq.value else None
 
 
 def selections(mode: int) -> int:

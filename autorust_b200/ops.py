@@ -120,6 +120,43 @@ def attn_forward_views(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
     return out
 
 
+def train_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None = None,
+                  causal: bool = False, stream=None):
+    """Exact f32 forward that also returns the rows' log-sum-exp: (o [B,Hq,S,D], lse [B,Hq,S])."""
+    L = _abi.load()
+    _check_qkv(q, k, v)
+    if q.dtype != torch.float32:
+        raise TypeError("the training path is float32")
+    B, Hq, S, D = q.shape
+    o = torch.empty_like(q)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_attn_train_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                     mask.data_ptr() if mask is not None else None, B, Hq, k.shape[1], S, D, int(causal),
+                                     s.cuda_stream)
+    _abi.check(rc, "ar_attn_train_forward")
+    return o, lse
+
+
+def train_backward(q, k, v, o, d_o, lse, mask=None, causal: bool = False, stream=None):
+    """(dq, dk, dv) from the forward's o and lse and the output gradient d_o (all float32, contiguous)."""
+    L = _abi.load()
+    _check_qkv(q, k, v)
+    B, Hq, S, D = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    need = int(L.ar_attn_train_workspace_bytes(B, Hq, S))
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_attn_train_backward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                                      mask.data_ptr() if mask is not None else None, dq.data_ptr(), dk.data_ptr(),
+                                      dv.data_ptr(), B, Hq, k.shape[1], S, D, int(causal), ws.data_ptr(), need, s.cuda_stream)
+    _abi.check(rc, "ar_attn_train_backward")
+    ws.record_stream(s)
+    return dq, dk, dv
+
+
 def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=None, fp8: bool = False):
     """The Sage prologue on its own: returns (q8, k8, q_scale, k_scale, k_mean).  fp8: E4M3 bit patterns in
     uint8 tensors and scales amax / 448 instead of INT8 and amax / 127."""

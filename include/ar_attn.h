@@ -106,6 +106,26 @@ int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, c
                             const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
                             void* workspace, size_t workspace_bytes, void* cu_stream);
 
+/* ---- Training path (f32, D = 64 or 128): the exact forward that also saves the rows' log-sum-exp, and the
+ * gradients computed from it.  Replaces `cuda_flash_train::run_fwd / run_prep / run_dq / run_dkv`
+ * (src/runtime/cuda_flash_train.rs:336-560; kernels :49-309), which `fused_attention_train` and
+ * `fused_attention_backward` call (src/models/flash_attention.rs:789-977).  Causal, additive [S, S] f32 mask and GQA
+ * as in the forward; no atomics, one fixed summation order. */
+
+/* o [B,Hq,S,D] and lse [B,Hq,S] (LSE = m + log l of the scaled, masked logits). */
+int ar_attn_train_forward(const float* q, const float* k, const float* v, float* o, float* lse, const float* mask,
+                          int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* cu_stream);
+
+/* Scratch of ar_attn_train_backward: D_i = O_i . dO_i per row. */
+size_t ar_attn_train_workspace_bytes(int64_t B, int64_t Hq, int64_t S);
+
+/* dq [B,Hq,S,D], dk and dv [B,Hkv,S,D] from q, k, v, the forward's o and lse, and the output gradient d_o.
+ * Under GQA dk and dv are summed over the query heads of a group. */
+int ar_attn_train_backward(const float* q, const float* k, const float* v, const float* o, const float* d_o,
+                           const float* lse, const float* mask, float* dq, float* dk, float* dv, int64_t B,
+                           int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                           size_t workspace_bytes, void* cu_stream);
+
 /* The Sage prologue on its own: optional K mean-smoothing, then symmetric INT8 quantisation of
  * Q and K with one f32 scale per `block` consecutive tokens
  * (scale = amax > 0 ? amax / 127 : 1; q8 = clamp(rn(x * (1 / scale)), -127, 127): the scalar

@@ -156,6 +156,26 @@ def sage_quantize(q, k, block=128, smooth=True, fp8=False):
     return q8, k8, qs, ks, km
 
 
+def attn_train(q, k, v, d_o, mask=None, causal=False):
+    """Training path: (o, lse, dq, dk, dv) for f32 q [B,Hq,N,D], k, v [B,Hkv,N,D] and the output gradient d_o."""
+    q, k, v, d_o = (np.ascontiguousarray(x, np.float32) for x in (q, k, v, d_o))
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, np.float32)
+    o, dq = np.empty_like(q), np.empty_like(q)
+    dk, dv = np.empty_like(k), np.empty_like(v)
+    lse = np.empty((B, Hq, N), np.float32)
+    L = lib()
+    L.ar_oracle_attn_train.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int64] * 5 + [ctypes.c_int]
+    L.ar_oracle_attn_train.restype = ctypes.c_int
+    rc = L.ar_oracle_attn_train(_ptr(q), _ptr(k), _ptr(v), _ptr(d_o), _ptr(mask), _ptr(o), _ptr(lse), _ptr(dq), _ptr(dk),
+                                _ptr(dv), B, Hq, Hkv, N, D, int(causal))
+    if rc != 0:
+        raise ValueError("ar_oracle_attn_train rejected the arguments")
+    return o, lse, dq, dk, dv
+
+
 def rows_f32(q_rows, row_idx, k, v, causal=False):
     """Exact f32 attention for selected query rows of one head (sampled check at full sizes)."""
     in_bf16 = q_rows.dtype == np.uint16

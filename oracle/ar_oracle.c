@@ -425,4 +425,92 @@ int ar_oracle_rows_f32(int in_dtype, const void* q_rows, const int64_t* row_idx,
   return 0;
 }
 
+/* ------------------------------------------------------------------------
+ * Training path: forward with the per-row log-sum-exp and the three gradients,
+ * as the reference's fused training kernels define them
+ * (src/runtime/cuda_flash_train.rs:1-21,49-309): with s = scale * q.k (+ mask),
+ * masked entries -1e30, LSE = m + log(l), p = exp(s - LSE), D_i = O_i . dO_i,
+ *   dV_j = sum_i p_ij dO_i     dS_ij = p_ij (dO_i . v_j - D_i)
+ *   dQ_i = scale sum_j dS_ij k_j     dK_j = scale sum_i dS_ij q_i
+ * and under GQA dK, dV sum over the query heads of a group.  f32 tensors,
+ * double accumulation (this is the checker, not a model of a kernel's rounding).
+ * o, dq: [B,Hq,N,D]; lse: [B,Hq,N]; dk, dv: [B,Hkv,N,D]; d_o like o.
+ * ------------------------------------------------------------------------ */
+int ar_oracle_attn_train(const float* q, const float* k, const float* v, const float* d_o, const float* mask, float* o,
+                         float* lse, float* dq, float* dk, float* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t N,
+                         int64_t D, int causal) {
+  if (Hkv <= 0 || Hq % Hkv != 0) return -1;
+  const int64_t group = Hq / Hkv;
+  const double scale = 1.0 / sqrt((double)D);
+  double* dk_acc = (double*)calloc((size_t)(B * Hkv * N * D), sizeof(double));
+  double* dv_acc = (double*)calloc((size_t)(B * Hkv * N * D), sizeof(double));
+  if (!dk_acc || !dv_acc) return -2;
+  /* one kv head at a time so that its accumulators have a single writer */
+#pragma omp parallel for schedule(dynamic)
+  for (int64_t kvh = 0; kvh < B * Hkv; kvh++) {
+    const int64_t b = kvh / Hkv, hk = kvh % Hkv;
+    double* s = (double*)malloc(sizeof(double) * (size_t)N);
+    double* p = (double*)malloc(sizeof(double) * (size_t)N);
+    for (int64_t g = 0; g < group; g++) {
+      const int64_t bh = b * Hq + hk * group + g;
+      for (int64_t i = 0; i < N; i++) {
+        const float* qi = q + (bh * N + i) * D;
+        const float* doi = d_o + (bh * N + i) * D;
+        double mx = -1e30;
+        for (int64_t j = 0; j < N; j++) {
+          const float* kj = k + (kvh * N + j) * D;
+          double acc = 0.0;
+          for (int64_t t = 0; t < D; t++) acc += (double)qi[t] * (double)kj[t];
+          double x = acc * scale;
+          if (mask) x += (double)mask[i * N + j];
+          if (causal && j > i) x = -1e30;
+          s[j] = x;
+          if (x > mx) mx = x;
+        }
+        double l = 0.0;
+        for (int64_t j = 0; j < N; j++) {
+          p[j] = exp(s[j] - mx);
+          l += p[j];
+        }
+        const double L = mx + log(l);
+        lse[bh * N + i] = (float)L;
+        double Di = 0.0;
+        for (int64_t t = 0; t < D; t++) {
+          double acc = 0.0;
+          for (int64_t j = 0; j < N; j++) acc += p[j] * (double)v[(kvh * N + j) * D + t];
+          const double ot = acc / l;
+          o[(bh * N + i) * D + t] = (float)ot;
+          Di += ot * (double)doi[t];
+        }
+        double* dqi = (double*)calloc((size_t)D, sizeof(double));
+        for (int64_t j = 0; j < N; j++) {
+          const double pj = p[j] / l;
+          if (pj == 0.0) continue;
+          const float* vj = v + (kvh * N + j) * D;
+          const float* kj = k + (kvh * N + j) * D;
+          double dp = 0.0;
+          for (int64_t t = 0; t < D; t++) dp += (double)doi[t] * (double)vj[t];
+          const double ds = pj * (dp - Di);
+          for (int64_t t = 0; t < D; t++) {
+            dqi[t] += ds * (double)kj[t];
+            dk_acc[(kvh * N + j) * D + t] += ds * (double)qi[t];
+            dv_acc[(kvh * N + j) * D + t] += pj * (double)doi[t];
+          }
+        }
+        for (int64_t t = 0; t < D; t++) dq[(bh * N + i) * D + t] = (float)(dqi[t] * scale);
+        free(dqi);
+      }
+    }
+    free(s);
+    free(p);
+  }
+  for (int64_t i = 0; i < B * Hkv * N * D; i++) {
+    dk[i] = (float)(dk_acc[i] * scale);
+    dv[i] = (float)dv_acc[i];
+  }
+  free(dk_acc);
+  free(dv_acc);
+  return 0;
+}
+
 int ar_oracle_version(void) { return 1; }
