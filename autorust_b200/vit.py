@@ -124,7 +124,7 @@ class ViT:
 
 
 def images_per_second(batch=64, iters=10, warmup=3, attention="fused", seed=3, copies=False) -> dict:
-    """BASELINE config 4: ViT-B/16, batch 64, 224x224x3 inputs ~ U(0,1) (seed 3), bf16 GEMMs."""
+    """benchmark configuration 4: ViT-B/16, batch 64, 224x224x3 inputs ~ U(0,1) (seed 3), bf16 GEMMs."""
     model = ViT(seed=seed)
     g = torch.Generator(device="cuda").manual_seed(seed)
     x = torch.rand(batch, 3, 224, 224, device="cuda", generator=g)

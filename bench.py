@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (per GPU): the Sage INT8 forward BASELINE.json's metric is quoted on -- B=4, H=32,
+Workload (per GPU): the Sage INT8 forward the headline metric is quoted on -- B=4, H=32,
 S=8192, D=128, non-causal, bf16 q/k/v ~ N(0,1) with a per-(head, channel) offset ~ N(0,4) on K,
 seed 2 -- as seeded synthetic tensors.  One step = the quantise prologue + the attention kernel
 over that batch.  With N > 1 every rank owns one such batch (weak scaling; global batch element
@@ -166,7 +166,7 @@ def run_reference_arm(args, rank: int) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal (BASELINE config 3)", **WORKLOAD,
+        "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal (benchmark configuration 3)", **WORKLOAD,
                    "timing": "wall clock around each bounded CPU sample"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -426,7 +426,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg()
-    # the other half of BASELINE's metric: ViT-B/16 images/s around the operator (config 4), rank 0 at N=1 only
+    # the other half of the headline metric: ViT-B/16 images/s around the operator (config 4), rank 0 at N=1 only
     vit_line = None
     if rank == 0 and world == 1 and not args.no_vit:
         from autorust_b200 import vit
@@ -439,7 +439,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
-            "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (BASELINE config 3)",
+            "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (benchmark configuration 3)",
                        **w, "global_batch": B * world, "partition": ("one batch of B per rank (independent (batch, head) pairs, no reduction); bf16 "
                        "outputs gathered on every rank " + ("piece by piece (37, 37, 37, 9, 8 heads: whole waves of CTAs, "
                        "short tail) under the next piece's kernel, by peer-to-peer copies on the copy engines (CUDA IPC "

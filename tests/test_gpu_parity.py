@@ -77,7 +77,7 @@ def test_exact_f32_masks_causal_gqa(ops, oracle_lib, label, b, hq, hkv, n, causa
 
 
 def test_exact_f32_config1_vit_shape(ops, oracle_lib):
-    """BASELINE config 1: B=1, H=12, S=197, D=64, N(0,1) seed 0, non-causal."""
+    """benchmark configuration 1: B=1, H=12, S=197, D=64, N(0,1) seed 0, non-causal."""
     q, k, v = normal_qkv(0, 1, 12, 12, 197, 64)
     got = run_f32(ops, "exact", q, k, v)
     assert rel_close(got, oracle_lib.sdpa_f32(q, k, v), 1e-5)
@@ -367,7 +367,7 @@ def _sample_check(oracle_lib, q, k, v, out, causal, pairs, rows, Hq, Hkv):
 
 
 def test_bf16_config2_full_size_sampled_and_properties(ops, oracle_lib):
-    """BASELINE config 2: bf16 causal, B=8, H=32, S=4096, D=128, N(0,1) seed 1."""
+    """benchmark configuration 2: bf16 causal, B=8, H=32, S=4096, D=128, N(0,1) seed 1."""
     import torch
     B, H, S, D = 8, 32, 4096, 128
     g = torch.Generator(device="cuda").manual_seed(1)
@@ -392,7 +392,7 @@ def test_bf16_config2_full_size_sampled_and_properties(ops, oracle_lib):
 
 
 def test_sage_config3_full_size_sampled_and_properties(ops, oracle_lib):
-    """BASELINE config 3: Sage INT8, B=4, H=32, S=8192, D=128, non-causal, K with a per-channel
+    """benchmark configuration 3: Sage INT8, B=4, H=32, S=8192, D=128, non-causal, K with a per-channel
     offset ~ N(0, 4), seed 2."""
     import torch
     B, H, S, D = 4, 32, 8192, 128
