@@ -43,6 +43,7 @@ bool make_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+inline bool aligned4(const void* p) { return ((uintptr_t)p & 3u) == 0; }  // f32 arrays read element-wise (NULL passes)
 
 constexpr size_t STATUS_BYTES = 256;
 
@@ -130,6 +131,7 @@ int sage_quantize_any(const void* q, const void* k, int dtype, int8_t* q8, int8_
   if (block != 128 || (D != 64 && D != 128) || (dtype != AR_DTYPE_F32 && dtype != AR_DTYPE_BF16)) return AR_ERR_UNSUPPORTED;
   if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(q_scale) || !aligned4(k_scale) || !aligned4(k_mean)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   ar::PrologueArgs a{q, k, dtype, q8, k8, q_scale, k_scale, k_mean, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, smooth};
   a.fp8 = fp8;
@@ -163,7 +165,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   if (rc != AR_OK) return rc;
   if (!mode_has_kernel(mode, dtype, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(workspace)) return AR_ERR_ALIGNMENT;
-  if (mask && ((uintptr_t)mask & 3u)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(mask)) return AR_ERR_ALIGNMENT;
   const size_t need = ar_attn_workspace_bytes(mode, dtype, B, Hq, Hkv, S, D);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AR_ERR_WORKSPACE;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
@@ -269,6 +271,7 @@ int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, c
   if (mode != AR_MODE_BF16) return AR_ERR_UNSUPPORTED;
   if (!mode_has_kernel(mode, dtype, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(workspace)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(mask)) return AR_ERR_ALIGNMENT;
   for (int i = 0; i < 3; i++)
     if (o_strides[i] <= 0 || (o_strides[i] * 2) % 16 != 0) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
@@ -308,7 +311,8 @@ int ar_attn_train_forward(const float* q, const float* k, const float* v, float*
   int rc = check_shape(B, Hq, Hkv, S, D);
   if (rc != AR_OK) return rc;
   if (!mode_has_kernel(AR_MODE_EXACT_F32, AR_DTYPE_F32, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return AR_ERR_ALIGNMENT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned4(lse) || !aligned4(mask))
+    return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   ar::ExactArgs e{q, k, v, o, mask, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, causal ? 1 : 0};
   e.lse = lse;
@@ -334,6 +338,7 @@ int ar_attn_train_backward(const float* q, const float* k, const float* v, const
   for (const void* p : {(const void*)q, (const void*)k, (const void*)v, (const void*)o, (const void*)d_o, (const void*)dq,
                         (const void*)dk, (const void*)dv, (const void*)workspace})
     if (!aligned16(p)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(lse) || !aligned4(mask)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   ar::TrainBwdArgs a{q, k, v, o, d_o, lse, mask, dq, dk, dv, (float*)workspace, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D,
                      causal ? 1 : 0};
@@ -353,6 +358,7 @@ int sage_prequantized_any(int mode, const void* q8, const void* k8, const float*
   if (!mode_has_kernel(mode, AR_DTYPE_BF16, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
   if (out_dtype != AR_DTYPE_F32 && out_dtype != AR_DTYPE_BF16) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q8) || !aligned16(k8) || !aligned16(v_bf16) || !aligned16(o)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(q_scale) || !aligned4(k_scale) || !aligned4(mask) || !aligned4(status_word)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   cudaStream_t stream = (cudaStream_t)cu_stream;
   uint32_t* status = status_ptr(status_word);

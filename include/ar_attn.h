@@ -18,7 +18,9 @@
  *     kernels, `Q,K,V,O,M,N,head_dim,causal,has_mask,hq,hkv`
  *     (src/runtime/cuda_flash_bf16.rs:226-230);
  *   - q, k, v, o (and the workspace) must be 16-byte aligned: the kernels stage tiles
- *     with TMA.  A misaligned pointer is reported as AR_ERR_ALIGNMENT, never a fault;
+ *     with TMA; the f32 arrays read element by element (mask, scales, K mean,
+ *     log-sum-exp, a status word) must be 4-byte aligned.  A misaligned pointer is
+ *     reported as AR_ERR_ALIGNMENT, never a fault;
  *   - calls are asynchronous on `cu_stream` (a CUstream / cudaStream_t as void*, NULL =
  *     the default stream) and never synchronise: the caller decides when to wait, as
  *     `run_host_kernel(.., wait)` does;
@@ -54,7 +56,7 @@ enum ar_attn_status {
   AR_OK = 0,
   AR_ERR_UNSUPPORTED = -1, /* shape / dtype / mode combination has no kernel: caller falls back */
   AR_ERR_NULL = -2,        /* a required pointer is NULL */
-  AR_ERR_ALIGNMENT = -3,   /* q/k/v/o/workspace not 16-byte aligned */
+  AR_ERR_ALIGNMENT = -3,   /* q/k/v/o/workspace not 16-byte aligned, or an f32 array not 4-byte aligned */
   AR_ERR_WORKSPACE = -4,   /* workspace missing or smaller than ar_attn_workspace_bytes() */
   AR_ERR_SHAPE = -5,       /* non-positive extent, Hq % Hkv != 0, ... */
   AR_ERR_CUDA = -6,        /* a CUDA runtime / driver call failed (launch, tensor map) */

@@ -80,6 +80,18 @@ def test_bad_calls_return_codes_without_touching_a_device(attn_lib):
     rc = L.ar_sage_quantize(0x1000, 0x2000, _abi.DTYPE_BF16, 0x3000, 0x4000, 0x5000, 0x6000, 0x7000, 1, 2, 2, 128, 128,
                             64, 1, None)
     assert rc == _abi.AR_ERR_UNSUPPORTED  # only 128-token blocks
+    # f32 arrays that the kernels read element-wise (mask, scales, log-sum-exp) must sit on 4-byte boundaries
+    assert _fwd(L, _abi.MODE_BF16, _abi.DTYPE_BF16, mask=0x5002) == _abi.AR_ERR_ALIGNMENT
+    rc = L.ar_sage_quantize(0x1000, 0x2000, _abi.DTYPE_BF16, 0x3000, 0x4000, 0x5001, 0x6000, 0x7000, 1, 2, 2, 128, 128,
+                            128, 1, None)
+    assert rc == _abi.AR_ERR_ALIGNMENT
+    rc = L.ar_attn_train_forward(0x1000, 0x2000, 0x3000, 0x4000, 0x5002, None, 1, 2, 2, 128, 64, 0, None)
+    assert rc == _abi.AR_ERR_ALIGNMENT
+    rc = L.ar_attn_train_forward(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 0x6001, 1, 2, 2, 128, 64, 0, None)
+    assert rc == _abi.AR_ERR_ALIGNMENT
+    rc = L.ar_sage_attention_prequantized(0x1000, 0x2000, 0x3002, 0x4000, 0x5000, 0x6000, _abi.DTYPE_BF16, None, 1, 2, 2,
+                                          128, 128, 0, None, None)
+    assert rc == _abi.AR_ERR_ALIGNMENT
 
 
 def test_no_device_is_an_error_not_a_fallback(attn_lib):
