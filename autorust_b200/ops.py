@@ -35,6 +35,19 @@ def _check_qkv(q, k, v):
         raise TypeError("q, k, v must share one dtype")
 
 
+def _check_mask(mask, S, device):
+    if mask is None:
+        return
+    if (mask.dtype != torch.float32 or tuple(mask.shape) != (S, S) or not mask.is_cuda or mask.device != device
+            or not mask.is_contiguous()):
+        raise ValueError("mask must be a contiguous float32 CUDA tensor of shape [S, S] on the tensors' device")
+
+
+def _check_dense(name, t, shape, dtype, device):
+    if tuple(t.shape) != tuple(shape) or t.dtype != dtype or t.device != device or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous {dtype} tensor of shape {tuple(shape)} on {device}")
+
+
 def mode_code(mode) -> int:
     return _MODE_NAMES[mode] if isinstance(mode, str) else int(mode)
 
@@ -62,11 +75,11 @@ def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
     m = mode_code(mode)
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
-    if mask is not None:
-        if mask.dtype != torch.float32 or tuple(mask.shape) != (S, S) or not mask.is_cuda or not mask.is_contiguous():
-            raise ValueError("mask must be a contiguous float32 CUDA tensor of shape [S, S]")
+    _check_mask(mask, S, q.device)
     if out is None:
         out = torch.empty_like(q)
+    else:
+        _check_dense("out", out, q.shape, q.dtype, q.device)
     need = int(L.ar_attn_workspace_bytes(m, _dtype_code(q), B, Hq, Hkv, S, D))
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
@@ -99,6 +112,7 @@ def attn_forward_views(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
         raise ValueError("shape or dtype mismatch between q, k, v")
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
+    _check_mask(mask, S, q.device)
     if out is None:
         out = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device).transpose(1, 2)
     if tuple(out.shape) != (B, Hq, S, D) or out.stride(3) != 1 or out.dtype != q.dtype:
@@ -128,6 +142,7 @@ def train_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch
     if q.dtype != torch.float32:
         raise TypeError("the training path is float32")
     B, Hq, S, D = q.shape
+    _check_mask(mask, S, q.device)
     o = torch.empty_like(q)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
@@ -143,7 +158,13 @@ def train_backward(q, k, v, o, d_o, lse, mask=None, causal: bool = False, stream
     """(dq, dk, dv) from the forward's o and lse and the output gradient d_o (all float32, contiguous)."""
     L = _abi.load()
     _check_qkv(q, k, v)
+    if q.dtype != torch.float32:
+        raise TypeError("the training path is float32")
     B, Hq, S, D = q.shape
+    _check_mask(mask, S, q.device)
+    _check_dense("o", o, q.shape, torch.float32, q.device)
+    _check_dense("d_o", d_o, q.shape, torch.float32, q.device)
+    _check_dense("lse", lse, (B, Hq, S), torch.float32, q.device)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     need = int(L.ar_attn_train_workspace_bytes(B, Hq, S))
     ws = torch.empty(need, dtype=torch.uint8, device=q.device)
@@ -161,6 +182,10 @@ def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=
     """The Sage prologue on its own: returns (q8, k8, q_scale, k_scale, k_mean).  fp8: E4M3 bit patterns in
     uint8 tensors and scales amax / 448 instead of INT8 and amax / 127."""
     L = _abi.load()
+    if q.dim() != 4 or k.dim() != 4 or not (q.is_cuda and k.is_cuda) or not (q.is_contiguous() and k.is_contiguous()):
+        raise ValueError("q and k must be contiguous CUDA tensors [B, H, S, D]: there is no CPU path")
+    if k.dtype != q.dtype or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
+        raise ValueError("shape or dtype mismatch between q and k")
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
     nblk = (S + 127) // 128
@@ -188,8 +213,18 @@ def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None
     Hkv = k8.shape[1]
     if v.dtype != torch.bfloat16:
         raise TypeError("v must be bfloat16")
+    nblk = (S + 127) // 128
+    dev = q8.device
+    _check_dense("q8", q8, (B, Hq, S, D), q8.dtype, dev)
+    _check_dense("k8", k8, (B, Hkv, S, D), q8.dtype, dev)
+    _check_dense("v", v, (B, Hkv, S, D), torch.bfloat16, dev)
+    _check_dense("q_scale", q_scale, (B, Hq, nblk), torch.float32, dev)
+    _check_dense("k_scale", k_scale, (B, Hkv, nblk), torch.float32, dev)
+    _check_mask(mask, S, dev)
     if out is None:
-        out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=q8.device)
+        out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
+    else:
+        _check_dense("out", out, (B, Hq, S, D), out.dtype, dev)
     with torch.cuda.device(q8.device):
         s = stream if stream is not None else torch.cuda.current_stream()
         fn = L.ar_sage_attention_prequantized_fp8 if q8.dtype == torch.uint8 else L.ar_sage_attention_prequantized
