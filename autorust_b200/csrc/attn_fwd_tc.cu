@@ -86,6 +86,9 @@ __device__ __forceinline__ void commit_one(uint64_t* bar) {
   if (elect_one()) tc_commit(bar);
 }
 
+// Largest scale c of an INT8 step that may fold its conversion: (12582912 + 127 * 127 * 128) * c < 2^14.
+constexpr float FOLD_MAX_C = 1.0e-3f;
+
 // One softmax step of one row: scores of 128 keys (sv, raw accumulator bits) -> P in TMEM, running
 // max m and running sum l updated, O rescaled in place when the max grows by more than the threshold.
 // EDGE = 1 selects the element-wise path for steps that touch the sequence end, the causal diagonal or
@@ -189,9 +192,14 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
     }
   }
   // p = 2^(x * c - m), two lanes per instruction; the row sum keeps the unrounded values
+  // INT8 interior steps fold the s32 -> f32 conversion into the same multiply-add: the bits of 1.5 * 2^23 + s are
+  // the float 12582912 + s (exact for |s| < 2^22), the product with c is exact inside the fused operation, and
+  // the constant 12582912 * c + m is subtracted in its place.  That constant is rounded once, to half an ulp of a
+  // value below 2^14 (the caller sends steps with c >= FOLD_MAX_C down the converting path): at most 2^-11 in
+  // the exponent, the same for every column of the row in this step.
   const uint64_t c2 = pack_f32x2(c, c);
-  const uint64_t negm2 = pack_f32x2(-m, -m);
-  const uint64_t magic2 = pack_f32x2(-12582912.0f, -12582912.0f);
+  const float sub = INT_SCORES ? fmaf(12582912.0f, c, m) : m;
+  const uint64_t negm2 = pack_f32x2(-sub, -sub);
   uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
   for (int qd = 0; qd < 4; qd++) {
@@ -200,9 +208,8 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
     for (int i = 0; i < 16; i++) {
       uint64_t x2;
       if constexpr (INT_SCORES) {
-        // s32 -> f32 through the bits of 1.5 * 2^23 (exact for |x| < 2^22)
-        x2 = add_f32x2(pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
-                                  __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u)), magic2);
+        x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i] + 0x4B400000u),
+                        __uint_as_float(sv[qd * 32 + 2 * i + 1] + 0x4B400000u));
       } else {
         x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i]), __uint_as_float(sv[qd * 32 + 2 * i + 1]));
       }
@@ -556,7 +563,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       float c = scale_log2;
       if (C::QUANT) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
-      const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr);
+      // INT8 steps whose scale is too large for the folded conversion (see softmax_step) convert first, as the
+      // boundary paths do; |s| <= 127 * 127 * 128 and m <= |s| * c keep 12582912 * c + m below 2^14 otherwise
+      const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr) ||
+                        (MODE == TC_SAGE && c >= FOLD_MAX_C);
       // Separate instantiations: the interior step must not carry the merge points of the boundary paths
       // (that alone costs it ~300 cycles of scheduling freedom).  A boundary step without an additive mask and
       // masks by -inf and runs the interior code (INT8 scores are converted first); an additive mask, whose -1e30

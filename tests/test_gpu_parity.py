@@ -222,6 +222,19 @@ def test_sage_normal_inputs_with_k_offset(ops, oracle_lib, n, causal, hq, hkv):
         assert max_abs(got, exact) <= 2e-2
 
 
+@pytest.mark.parametrize("gain,n,causal", [(1.0, 640, False), (6.0, 640, False), (6.0, 700, True), (40.0, 384, False)])
+def test_sage_large_scales_take_the_converting_path(ops, oracle_lib, gain, n, causal):
+    """Interior INT8 steps fold the s32 -> f32 conversion into the exponent's multiply-add while the step's scale
+    q_scale * k_scale * log2(e) / sqrt(D) stays below 1e-3 and convert first above it; both sides of that line
+    (gain 1: about 2e-4; gain 6 and 40: far above) must match the quantised model."""
+    q, k, v = normal_qkv(5, 1, 2, 2, n, 128, k_offset_sigma=0.0)
+    q, k = q * np.float32(gain), k * np.float32(gain)
+    qb, kb, vb = (oracle_lib.f32_to_bf16(x) for x in (q, k, v))
+    got = oracle_lib.bf16_to_f32(run_bf16(ops, "sage", qb, kb, vb, None, causal))
+    model = oracle_lib.bf16_to_f32(oracle_lib.flash(3, qb, kb, vb, None, causal, block=128, smooth=True))
+    assert max_abs(got, model) < 2e-2 and cosine(got, model) > 0.9999
+
+
 def test_sage_with_mask(ops, oracle_lib):
     q, k, v = sawtooth_qkv(1, 2, 2, 200, 128)
     mask = sawtooth_mask(200)
