@@ -394,9 +394,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     roofline = {
         "bound": "tensor", "kernel": "attn_fwd_tc_kernel<SAGE,128>", "achieved": achieved, "peak": bf16_peak,
         "unit": "TFLOP/s", "frac": achieved / bf16_peak,
-        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at B=1 (179.4 MB,
+        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at B=1 (173.8 MB,
         # profiles/attn_fwd_tc_sage_S8192_D128.md), scaled by the batch: traffic grows with the number of heads
-        "traffic": 179.4e6 * B if (H, S, D) == (32, 8192, 128) else None,
+        "traffic": 173.8e6 * B if (H, S, D) == (32, 8192, 128) else None,
         "traffic_source": "ncu capture at B=1 scaled by B; algorithmic bytes 201 MB per batch element",
         "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst), {peaks['source']}",
         "kernel_ms": kern_ms_avg,
