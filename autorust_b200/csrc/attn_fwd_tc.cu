@@ -89,6 +89,41 @@ __device__ __forceinline__ void commit_one(uint64_t* bar) {
 // Largest scale c of an INT8 step that may fold its conversion: (12582912 + 127 * 127 * 128) * c < 2^14.
 constexpr float FOLD_MAX_C = 1.0e-3f;
 
+// Which of the 16 column pairs of each 32-column group take their exponential on the FMA pipe (bit i = pair i):
+// the MUFU unit delivers 16 ex2 per clock and SM, which alone would bound a step of two tiles at 2048 cycles.
+#ifndef AR_POLY_MASK
+#define AR_POLY_MASK 0x0000u
+#endif
+constexpr uint32_t POLY_MASK = AR_POLY_MASK;
+
+// 2^x for two lanes on the MUFU unit.
+__device__ __forceinline__ void exp2_mufu_x2(uint64_t x2, float& p0, float& p1) {
+  float a, b;
+  unpack_f32x2(x2, a, b);
+  p0 = ex2f(a);
+  p1 = ex2f(b);
+}
+// 2^x for two lanes without the MUFU unit: x = n + f with n the nearest integer (read from the low mantissa bits of
+// x + 1.5 * 2^23) and f in [-0.5, 0.5], 2^f by a cubic whose relative error stays below 1.1e-4 (P is rounded to
+// bf16, 2^-9, afterwards), n added to the exponent field.  x is clamped at -126 so that the exponent cannot wrap;
+// 2^0 is exactly 1.
+__device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& p0, float& p1) {
+  float a, b;
+  unpack_f32x2(x2, a, b);
+  const uint64_t xc = pack_f32x2(fmaxf(a, -126.0f), fmaxf(b, -126.0f));
+  const uint64_t t2 = add_f32x2(xc, pack_f32x2(12582912.0f, 12582912.0f));
+  const uint64_t n2 = add_f32x2(t2, pack_f32x2(-12582912.0f, -12582912.0f));
+  const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.0f, -1.0f), xc);
+  uint64_t y2 = fma_f32x2(pack_f32x2(0.055008914f, 0.055008914f), f2, pack_f32x2(0.242211f, 0.242211f));
+  y2 = fma_f32x2(y2, f2, pack_f32x2(0.69328296f, 0.69328296f));
+  y2 = fma_f32x2(y2, f2, pack_f32x2(1.0f, 1.0f));
+  float ya, yb, ta, tb;
+  unpack_f32x2(y2, ya, yb);
+  unpack_f32x2(t2, ta, tb);
+  p0 = __uint_as_float(__float_as_uint(ya) + (__float_as_uint(ta) << 23));
+  p1 = __uint_as_float(__float_as_uint(yb) + (__float_as_uint(tb) << 23));
+}
+
 // One softmax step of one row: scores of 128 keys (sv, raw accumulator bits) -> P in TMEM, running
 // max m and running sum l updated, O rescaled in place when the max grows by more than the threshold.
 // EDGE = 1 selects the element-wise path for steps that touch the sequence end, the causal diagonal or
@@ -213,9 +248,11 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
       } else {
         x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i]), __uint_as_float(sv[qd * 32 + 2 * i + 1]));
       }
-      float a, b;
-      unpack_f32x2(fma_f32x2(x2, c2, negm2), a, b);
-      const float p0 = ex2f(a), p1 = ex2f(b);
+      float p0, p1;
+      if (((POLY_MASK >> i) & 1u) != 0)  // i is a constant of the unrolled loop
+        exp2_poly_x2(fma_f32x2(x2, c2, negm2), p0, p1);
+      else
+        exp2_mufu_x2(fma_f32x2(x2, c2, negm2), p0, p1);
       const uint64_t p2 = pack_f32x2(p0, p1);
       if (i & 1) sum_b = add_f32x2(sum_b, p2); else sum_a = add_f32x2(sum_a, p2);
       if constexpr (MODE == TC_TF32) {  // P stays f32 in TMEM; the MMA reads its tf32 part

@@ -169,6 +169,12 @@ class Gather:
         if load().ar_gather_p2p_fence(self._h, s.cuda_stream) != 0:
             raise RuntimeError("ar_gather_p2p_fence: " + load().ar_gather_last_error().decode())
 
+    def p2p_close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (every rank calls it; the tensor p2p_open returned must not
+        be used afterwards).  p2p_open may be called again."""
+        self._p2p = None
+        load().ar_gather_p2p_close(self._h)
+
     def close(self) -> None:
         if self._h:
             self._p2p = None

@@ -4,18 +4,20 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (per GPU): the Sage INT8 forward the headline metric is quoted on -- B=4, H=32,
-S=8192, D=128, non-causal, bf16 q/k/v ~ N(0,1) with a per-(head, channel) offset ~ N(0,4) on K,
-seed 2 -- as seeded synthetic tensors.  One step = the quantise prologue + the attention kernel
-over that batch.  With N > 1 every rank owns one such batch (weak scaling; global batch element
-g = c*N + r lives on rank r) and the bf16 outputs are all-gathered over NCCL, chunk by chunk on a
-side stream while the next chunk computes (libar_gather.so, include/ar_attn_gather.h).
+Headline workload (per GPU): the Sage INT8 forward the metric is quoted on -- B=4, H=32, S=8192, D=128,
+non-causal, bf16 q/k/v ~ N(0,1) with a per-(head, channel) offset ~ N(0,4) on K, seed 2 -- as seeded
+synthetic tensors.  One step = the quantise prologue + the attention kernel over that batch.  With N > 1
+every rank owns one such batch (weak scaling) and the bf16 outputs are gathered on every rank; after the
+timed region every rank checks every slab of its gathered buffer against the owner's checksum.
 
-Prints ONE JSON line (rank 0).  `value` is device-resident throughput (inputs already in HBM);
-`e2e` goes through the host-facing call with pinned host buffers, H2D and D2H copies inside the
-timed region; `roofline` is the attention kernel timed with CUDA events inside the timed region;
-`cpu_baseline` is the CPU port of the reference's SDPA path timed on this box's host cores on a
-bounded sample.  `--impl reference` times only that CPU path.
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput (inputs already in HBM); `e2e` goes
+through the host-facing call with pinned host buffers, H2D and D2H copies inside the timed region;
+`roofline` is the attention kernel timed with CUDA events inside the timed region, against the mixed
+INT8/bf16 tensor peak; `cpu_baseline` is the CPU port of the reference's SDPA path timed on this box's host
+cores on a bounded sample.  Further keys: `bf16_fwd` (the bf16 kernel at the headline shape) and `config2`
+(bf16 causal, B=8 H=32 S=4096) at N=1; `long_context` (B=16 H=64 S=16384 causal Sage, ONE global tensor cut
+over the N ranks, strong scaling, with and without the output gather) at every N.
+`--impl reference` times only the CPU path.
 """
 from __future__ import annotations
 
@@ -33,8 +35,13 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 WORKLOAD = {"B": 4, "H": 32, "S": 8192, "D": 128, "causal": False, "seed": 2, "k_offset_sigma": 2.0}
+LONG_CONTEXT = {"B": 16, "H": 64, "S": 16384, "D": 128, "causal": True, "seed": 2, "k_offset_sigma": 2.0}
 METRIC = "sage_int8_attention_fwd_throughput"
 UNIT = "TOPS"  # INT8 ops of QK^T + bf16 flops of PV, 4*B*H*S^2*D per batch
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the Sage attention kernel per (batch, head) pair at S=8192, D=128:
+# one ncu capture of a 32-head launch (173.8 MB), divided by its heads.  Traffic grows in proportion to the heads.
+NCU_TRAFFIC_BYTES_PER_HEAD_S8192 = 173.8e6 / 32
 
 
 def work_ops(B, H, S, D, causal=False):
@@ -126,9 +133,16 @@ def cpu_step(q, k, v):
     return time.perf_counter() - t0, threads
 
 
-def cpu_baseline_leg(budget_s: float = 12.0) -> dict:
+def cpu_prepare():
+    """Builds the CPU port and gives it every core this process may run on (a launcher such as
+    torch.distributed.run exports OMP_NUM_THREADS=1 to its children, which is not what is being measured)."""
     import oracle
     oracle.build()
+    return oracle.set_cpu_threads()
+
+
+def cpu_baseline_leg(budget_s: float = 12.0) -> dict:
+    cpu_prepare()
     w = WORKLOAD
     q, k, v = cpu_inputs(1)
     cpu_step(q, k, v)  # warm-up (page faults, thread pool)
@@ -147,8 +161,7 @@ def run_reference_arm(args, rank: int) -> None:
     in oracle/ar_cpu_baseline.c).  Each step is a bounded sample: `heads` (batch, head) pairs."""
     if rank != 0:
         return
-    import oracle
-    oracle.build()
+    cores = cpu_prepare()
     w = WORKLOAD
     heads = 4
     q, k, v = cpu_inputs(heads)
@@ -161,7 +174,8 @@ def run_reference_arm(args, rank: int) -> None:
     total = sum(times)
     ops = work_ops(1, heads, w["S"], w["D"], w["causal"]) * args.steps
     value = ops / total / 1e12
-    sample = f"{heads} of {w['B'] * w['H']} (batch, head) pairs per step, f32 SDPA port, all host threads"
+    sample = (f"{heads} of {w['B'] * w['H']} (batch, head) pairs per step, f32 SDPA port, {threads} OpenMP threads "
+              f"({cores} cores usable by this process)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -208,6 +222,211 @@ def int8_peak_tops(torch, device) -> float | None:
         return 2.0 * n ** 3 / (best * 1e-3) / 1e12
     except Exception:
         return None
+
+
+def slab_checksums(torch, slabs) -> "torch.Tensor":
+    """Two position-sensitive 64-bit checksums per slab (bf16 bits read as int32 words; sums wrap modulo 2^64):
+    sum(w) and sum(w * (1 + i mod 8191)).  A slab that arrived incomplete, shifted or permuted changes them."""
+    out = []
+    for s in slabs:
+        words = s.reshape(-1).view(torch.int32)
+        a = torch.zeros((), dtype=torch.int64, device=s.device)
+        b = torch.zeros((), dtype=torch.int64, device=s.device)
+        step = 1 << 26
+        for at in range(0, words.numel(), step):
+            w = words[at:at + step].to(torch.int64)
+            idx = torch.arange(at, at + w.numel(), device=s.device, dtype=torch.int64) % 8191 + 1
+            a += w.sum()
+            b += (w * idx).sum()
+        out.append(torch.stack([a, b]))
+    return torch.stack(out)  # [slabs, 2]
+
+
+def verify_gather(torch, dist, slabs, rank, world) -> tuple[bool, int]:
+    """Every rank checksums every slab of ITS gathered buffer; the tables go round; slab s must read the same on
+    every rank as on its owner s.  Returns (all equal, the sum of the owners' first checksums)."""
+    mine = slab_checksums(torch, slabs)  # [world, 2]: this rank's view of every slab
+    table = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(table, mine)
+    table = torch.stack(table).cpu()  # [viewer, slab, 2]
+    ok = True
+    for s in range(world):
+        for r in range(world):
+            ok = ok and bool(torch.equal(table[r, s], table[s, s]))
+    total = int(sum(int(table[s, s, 0]) for s in range(world)) % (1 << 63))
+    return ok, total
+
+
+def time_kernel(torch, fn, iters=10, warm=3, reps=4) -> float:
+    """Median CUDA-event time of fn() in ms; each sample brackets `reps` back-to-back calls, so that the host's
+    time to issue a call does not sit between the events of a short kernel."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / reps)
+    return statistics.median(ts)
+
+
+def bf16_legs(torch, device, bf16_peak) -> dict:
+    """The bf16 kernel at the headline shape (non-causal) and benchmark configuration 2 (causal, B=8 H=32 S=4096,
+    N(0,1) seed 1): kernel time with CUDA events, TFLOP/s and the fraction of the measured bf16 burst peak."""
+    from autorust_b200 import ops
+    res = {}
+    for key, (B, H, S, D, causal, seed) in {"bf16_fwd": (4, 32, 8192, 128, False, 2),
+                                            "config2": (8, 32, 4096, 128, True, 1)}.items():
+        g = torch.Generator(device=device).manual_seed(seed)
+        q, k, v = (torch.randn(B, H, S, D, device=device, generator=g).to(torch.bfloat16) for _ in range(3))
+        out = torch.empty_like(q)
+        ms = time_kernel(torch, lambda: ops.attn_forward("bf16", q, k, v, None, causal, out=out))
+        tf = work_ops(B, H, S, D, causal) / (ms * 1e-3) / 1e12
+        res[key] = {"workload": f"bf16 fwd B={B} H={H} S={S} D={D} {'causal' if causal else 'non-causal'}, N(0,1) seed {seed}",
+                    "kernel_ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / bf16_peak,
+                    "flops": "4*B*H*S^2*D" + ("/2" if causal else ""), "timing": "CUDA events around 4 back-to-back launches, median of 10 samples"}
+        del q, k, v, out
+    return res
+
+
+def long_context_slab(torch, device, pair_begin: int, pair_end: int):
+    """q, k, v [pairs, S, D] bf16 of the (batch, head) pairs [pair_begin, pair_end) of benchmark configuration 5's
+    global tensor (pair = b * H + h): N(0,1), K with an offset ~ N(0, 4) per (head, channel) that is the same for
+    every batch element and token.  The values of a pair depend on the pair alone -- one generator per group of 8
+    pairs, seeded by the group's index -- so any cut of the pair axis produces the same global tensor."""
+    lc = LONG_CONTEXT
+    H, S, D = lc["H"], lc["S"], lc["D"]
+    grp = 8
+    if pair_begin % grp or pair_end % grp:
+        raise ValueError("long_context_slab: the range must start and end on a multiple of 8 pairs")
+    n = pair_end - pair_begin
+    g0 = torch.Generator(device=device).manual_seed(lc["seed"])
+    k_offset = lc["k_offset_sigma"] * torch.randn((H, 1, D), device=device, generator=g0)
+    q = torch.empty((n, S, D), dtype=torch.bfloat16, device=device)
+    k = torch.empty_like(q)
+    v = torch.empty_like(q)
+    for c in range(n // grp):
+        p0 = pair_begin + c * grp
+        g = torch.Generator(device=device).manual_seed(lc["seed"] * 1_000_003 + p0 // grp)
+        heads = torch.arange(p0, p0 + grp, device=device) % H
+        q[c * grp:(c + 1) * grp] = torch.randn((grp, S, D), device=device, generator=g).to(torch.bfloat16)
+        k[c * grp:(c + 1) * grp] = (torch.randn((grp, S, D), device=device, generator=g) + k_offset[heads]).to(torch.bfloat16)
+        v[c * grp:(c + 1) * grp] = torch.randn((grp, S, D), device=device, generator=g).to(torch.bfloat16)
+    return q, k, v
+
+
+def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=True, steps=3) -> dict:
+    """Benchmark configuration 5: ONE global tensor B=16, H=64, S=16384, D=128, causal Sage, cut over the ranks
+    along the flattened (batch, head) axis (1024 pairs -> 1024 / N per rank, strong scaling); every rank ends up
+    with the whole bf16 output.  The inputs of pair p depend on p alone (a generator seeded per group of 8 pairs),
+    so every N computes the same global tensor and the checksum of the output must not depend on N."""
+    from autorust_b200 import multi_gpu
+    lc = LONG_CONTEXT
+    B, H, S, D = lc["B"], lc["H"], lc["S"], lc["D"]
+    shard = multi_gpu.equal_partition(B, H, H, world)[rank]
+    n_local = shard.q_end - shard.q_begin
+    q, k, v = long_context_slab(torch, device, shard.q_begin, shard.q_end)
+    nblk = (S + 127) // 128
+    q8 = torch.empty((n_local, S, D), dtype=torch.int8, device=device)
+    k8 = torch.empty_like(q8)
+    qs = torch.empty((n_local, nblk), dtype=torch.float32, device=device)
+    ks = torch.empty_like(qs)
+    km = torch.empty((n_local, D), dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream()
+    comm_stream = torch.cuda.Stream() if world > 1 else None
+    p2p = False
+    full = None
+    if world > 1 and use_p2p:
+        try:
+            full = gather.p2p_open((world, n_local, S, D), torch.bfloat16)
+            opened = 1
+        except RuntimeError:
+            opened = 0
+        flag = torch.tensor([opened], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        p2p = bool(flag.item())
+        if not p2p and opened:
+            gather.p2p_close()
+    if not p2p:
+        full = torch.empty((world, n_local, S, D), dtype=torch.bfloat16, device=device)
+    npieces = 8 if p2p else 1
+    per = n_local // npieces
+
+    def compute(h0, h1):
+        rc = L.ar_sage_attention_prequantized(q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(),
+                                              ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(), full[rank, h0:h1].data_ptr(),
+                                              _abi.DTYPE_BF16, None, 1, h1 - h0, h1 - h0, S, D, 1, None, stream.cuda_stream)
+        _abi.check(rc, "ar_sage_attention_prequantized")
+
+    def step(with_gather: bool):
+        rc = L.ar_sage_quantize(q.data_ptr(), k.data_ptr(), _abi.DTYPE_BF16, q8.data_ptr(), k8.data_ptr(), qs.data_ptr(),
+                                ks.data_ptr(), km.data_ptr(), 1, n_local, n_local, S, D, 128, 1, stream.cuda_stream)
+        _abi.check(rc, "ar_sage_quantize")
+        for i in range(npieces):
+            h0, h1 = i * per, (i + 1) * per if i + 1 < npieces else n_local
+            compute(h0, h1)
+            if with_gather and p2p:
+                done = torch.cuda.Event()
+                done.record(stream)
+                comm_stream.wait_event(done)
+                gather.p2p_push(full[rank, h0:h1], comm_stream)
+        if with_gather and p2p:
+            gather.p2p_fence(comm_stream)
+            stream.wait_stream(comm_stream)
+        elif with_gather and world > 1:
+            gather.allgather_in_place(full, stream)
+
+    def timed(with_gather: bool) -> float:
+        step(with_gather)  # warm-up
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(steps):
+            step(with_gather)
+        t1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / steps
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    ms_compute = timed(False)
+    ms_total = timed(True) if world > 1 else ms_compute
+    status = int(L.ar_attn_last_status(None, stream.cuda_stream))
+    if status != 0:
+        raise SystemExit(f"device status after the long-context steps: {_abi.strerror(status)}")
+    if world > 1:
+        ok, checksum = verify_gather(torch, dist, [full[r] for r in range(world)], rank, world)
+    else:
+        ok, checksum = True, int(slab_checksums(torch, [full[0]])[0, 0].item() % (1 << 63))
+    ops = work_ops(B, H, S, D, True)
+    res = {"workload": "sage_int8_fwd B=16 H=64 S=16384 D=128 causal (benchmark configuration 5), one global tensor cut "
+                       f"into {world} contiguous ranges of {n_local} (batch, head) pairs",
+           "scaling": "strong", "steps": steps, "pairs_per_rank": n_local,
+           "ms_per_step_excluding_gather": ms_compute, "tops_excluding_gather": ops / (ms_compute * 1e-3) / 1e12,
+           "ms_per_step_including_gather": ms_total, "tops_including_gather": ops / (ms_total * 1e-3) / 1e12,
+           "gather_bytes_received_per_rank": (world - 1) * n_local * S * D * 2,
+           "gather": ("peer-to-peer copies on the copy engines, 8 pieces under the following pieces' kernels" if p2p
+                      else "NCCL all-gather in place after the kernel") if world > 1 else None,
+           "gather_verified": bool(ok) if world > 1 else None, "output_checksum": checksum,
+           "timing": "CUDA events on the launching stream, max over ranks; flops 4*B*H*S^2*D/2"}
+    if world > 1 and not ok:
+        raise SystemExit("long_context: a gathered slab differs from its owner's copy")
+    if p2p:
+        del full
+        gather.p2p_close()
+    return res
 
 
 def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
@@ -384,6 +603,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     ops_per_step_rank = work_ops(B, H, S, D, w["causal"])
     value = ops_per_step_rank * world / (ms_per_step * 1e-3) / 1e12
 
+    # the gathered buffers after the last step: every slab on every rank against its owner's copy
+    gather_verified = None
+    if world > 1:
+        slabs = [gathered[r] for r in range(world)] if p2p else [gathered[:, r] for r in range(world)]
+        gather_verified, _ = verify_gather(torch, dist, slabs, rank, world)
+        if not gather_verified:
+            raise SystemExit("a gathered slab differs from its owner's copy")
+
     # roofline of the dominant kernel: its launches inside the timed region, bracketed by events
     # every event pair covers `nb` batch elements' worth of the kernel; scaled to a full-batch launch
     kern_ms_avg = sum(e0.elapsed_time(e1) for (e0, e1, _) in kernel_events) / sum(nb for (_, _, nb) in kernel_events) * B
@@ -391,37 +618,37 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     i8_peak = int8_peak_tops(torch, device) if rank == 0 else None
     achieved = ops_per_step_rank / (kern_ms_avg * 1e-3) / 1e12
     bf16_peak = peaks["bf16_tflops"]
+    # Half of the work (QK^T) runs at the INT8 rate and half (PV) at the bf16 rate: the time the tensor pipe needs at
+    # least is ops_i8 / peak_i8 + flop_bf16 / peak_bf16, i.e. the peak for this mix is the harmonic mean of the two.
+    i8_used = i8_peak if i8_peak else 2.0 * bf16_peak
+    mixed = 2.0 / (1.0 / i8_used + 1.0 / bf16_peak)
     roofline = {
-        "bound": "tensor", "kernel": "attn_fwd_tc_kernel<SAGE,128>", "achieved": achieved, "peak": bf16_peak,
-        "unit": "TFLOP/s", "frac": achieved / bf16_peak,
-        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at B=1 (173.8 MB,
-        # profiles/attn_fwd_tc_sage_S8192_D128.md), scaled by the batch: traffic grows with the number of heads
-        "traffic": 173.8e6 * B if (H, S, D) == (32, 8192, 128) else None,
-        "traffic_source": "ncu capture at B=1 scaled by B; algorithmic bytes 201 MB per batch element",
-        "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst), {peaks['source']}",
+        "bound": "tensor", "kernel": "attn_fwd_tc_kernel<SAGE,128>", "achieved": achieved, "peak": mixed,
+        "unit": "TOPS (INT8 QK^T ops + bf16 PV flops)", "frac": achieved / mixed,
+        "peak_source": ("mixed peak = 2 / (1/int8 + 1/bf16): int8 = " +
+                        ("torch._int_mm 8192^3 measured live in this run, best of 10"
+                         if i8_peak else "2 x the bf16 figure (the live INT8 measurement failed)") +
+                        f"; bf16 = MEASURED_PEAKS.json bf16_tflops (burst), {peaks['source']}"),
+        "int8_peak_tops": i8_used, "bf16_peak_tflops": bf16_peak,
+        "frac_of_int8_peak": achieved / i8_used, "frac_of_bf16_peak": achieved / bf16_peak,
+        "traffic": NCU_TRAFFIC_BYTES_PER_HEAD_S8192 * B * H if (S, D) == (8192, 128) else None,
+        "traffic_source": "one ncu capture of a 32-head launch, scaled by the heads; algorithmic bytes 201 MB per 32 heads",
         "kernel_ms": kern_ms_avg,
-        "note": "achieved = (INT8 QK^T ops + bf16 PV flops) / kernel time; half of the work runs at the INT8 rate",
     }
-    if i8_peak:
-        mixed = 2.0 / (1.0 / i8_peak + 1.0 / bf16_peak)
-        roofline.update({"int8_peak_tops_live": i8_peak, "frac_of_int8_peak": achieved / i8_peak,
-                         "mixed_peak": mixed, "frac_of_mixed_peak": achieved / mixed})
 
     # end to end through the host-facing call: pinned host buffers, H2D + D2H inside the timed region
-    e2e = None
-    if True:
-        from autorust_b200 import host
-        e2e = host.bench_e2e(q, k, v, causal=w["causal"], steps=max(3, min(args.steps, 10)), warmup=2, world=world)
-        e2e_value = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
-        e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d_bytes"] * world,
-               "d2h_bytes_per_step": e2e["d2h_bytes"] * world, "ms_per_step": e2e["ms_per_step"],
-               "api": e2e["api"], "ms_per_step_tensor_api": e2e["ms_per_step_tensor_api"],
-               "tensor_api": e2e["tensor_api"], "streamed_equals_tensor_api": e2e["streamed_equals_tensor_api"]}
-        if world > 1:
-            t = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e["ms_per_step"] = float(t.item())
-            e2e["value"] = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
+    from autorust_b200 import host
+    e2e = host.bench_e2e(q, k, v, causal=w["causal"], steps=max(3, min(args.steps, 10)), warmup=2, world=world)
+    e2e_value = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
+    e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d_bytes"] * world,
+           "d2h_bytes_per_step": e2e["d2h_bytes"] * world, "ms_per_step": e2e["ms_per_step"],
+           "api": e2e["api"], "ms_per_step_tensor_api": e2e["ms_per_step_tensor_api"],
+           "tensor_api": e2e["tensor_api"], "streamed_equals_tensor_api": e2e["streamed_equals_tensor_api"]}
+    if world > 1:
+        t = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e["ms_per_step"] = float(t.item())
+        e2e["value"] = ops_per_step_rank * world / (e2e["ms_per_step"] * 1e-3) / 1e12
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -433,6 +660,18 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         vit_line = vit.images_per_second(batch=64, iters=10, warmup=3, attention="fused")
         vit_line["img_per_s_copy_form"] = vit.images_per_second(batch=64, iters=10, warmup=3, attention="fused",
                                                                   copies=True)["img_per_s"]
+        vit_line["img_per_s_torch_sdpa"] = vit.images_per_second(batch=64, iters=10, warmup=3,
+                                                                   attention="torch")["img_per_s"]
+    bf16 = bf16_legs(torch, device, bf16_peak) if (rank == 0 and world == 1 and not args.no_extra) else {}
+
+    # free the headline tensors before the long-context leg allocates its own
+    del q, k, v, out, q8, k8, qs, ks, km, q8f, k8f, qsf, ksf, vf
+    if world > 1 and p2p:
+        gathered = None
+        gather.p2p_close()
+    long_context = None
+    if not args.no_long_context:
+        long_context = long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=p2p)
 
     if rank == 0:
         line = {
@@ -449,9 +688,12 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
                        "l2": "inputs (805 MB) exceed L2 (126 MB); no flush needed",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "per_gpu_tops": value / world, "vit_b16_bs64": vit_line,
+            "per_gpu_tops": value / world, "gather_verified": gather_verified, "vit_b16_bs64": vit_line,
+            "long_context": long_context, **bf16,
         }
         print(json.dumps(line), flush=True)
+    if gather is not None:
+        gather.close()
 
 
 def main() -> None:
@@ -462,6 +704,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-vit", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the bf16_fwd and config2 legs")
+    ap.add_argument("--no-long-context", action="store_true", help="skip the B=16 H=64 S=16384 causal leg")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: how the output slabs reach the other ranks (copy engines, or NCCL's all-gather kernels)")
     args = ap.parse_args()

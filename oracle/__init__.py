@@ -48,8 +48,12 @@ def lib() -> ctypes.CDLL:
         L.ar_oracle_e4m3_to_f32.restype = None
         L.ar_oracle_rows_f32.argtypes = [ci, p, p, i64, p, p, p, i64, i64, ci]
         L.ar_oracle_rows_f32.restype = ci
+        L.ar_oracle_rows_sage.argtypes = [p, p, p, i64, p, p, p, p, i64, i64, i64, ci]
+        L.ar_oracle_rows_sage.restype = ci
         L.ar_cpu_sdpa_f32.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, ci, i64, i64]
         L.ar_cpu_sdpa_f32.restype = ci
+        L.ar_cpu_set_threads.argtypes = [ci]
+        L.ar_cpu_set_threads.restype = None
         L.ar_oracle_f32_to_bf16.argtypes = [p, p, i64]
         L.ar_oracle_bf16_to_f32.argtypes = [p, p, i64]
         _lib = L
@@ -189,6 +193,35 @@ def rows_f32(q_rows, row_idx, k, v, causal=False):
     lib().ar_oracle_rows_f32(BF16 if in_bf16 else F32, _ptr(q_rows), _ptr(row_idx), len(row_idx), _ptr(k), _ptr(v),
                              _ptr(out), N, D, int(causal))
     return out
+
+
+def rows_sage(q8_rows, q_scale_rows, row_idx, k8, k_scale, v_bf16, causal=False, block=128):
+    """The Sage model (flash mode 3) for selected query rows of one head, on tensors sage_quantize produced:
+    q8_rows [n, D] int8, q_scale_rows [n] (the scale of each row's block), k8 [N, D], k_scale [ceil(N/block)],
+    v_bf16 [N, D] uint16.  Returns [n, D] f32."""
+    q8_rows = np.ascontiguousarray(q8_rows, np.int8)
+    q_scale_rows = np.ascontiguousarray(q_scale_rows, np.float32)
+    row_idx = np.ascontiguousarray(row_idx, np.int64)
+    k8 = np.ascontiguousarray(k8, np.int8)
+    k_scale = np.ascontiguousarray(k_scale, np.float32)
+    v_bf16 = np.ascontiguousarray(v_bf16, np.uint16)
+    N, D = k8.shape
+    out = np.empty((len(row_idx), D), np.float32)
+    rc = lib().ar_oracle_rows_sage(_ptr(q8_rows), _ptr(q_scale_rows), _ptr(row_idx), len(row_idx), _ptr(k8), _ptr(k_scale),
+                                   _ptr(v_bf16), _ptr(out), N, D, block, int(causal))
+    if rc != 0:
+        raise ValueError("ar_oracle_rows_sage rejected the arguments")
+    return out
+
+
+def set_cpu_threads(n: int | None = None) -> int:
+    """Sets the thread count of the timed CPU baseline: n, or every core this process may run on.  Explicit, because
+    a process launcher may have exported OMP_NUM_THREADS=1 to its children."""
+    import os
+    if n is None:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().ar_cpu_set_threads(int(n))
+    return int(n)
 
 
 def cpu_sdpa_f32(q, k, v, causal=False, bh_begin=0, bh_end=None):

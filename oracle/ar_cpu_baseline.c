@@ -59,6 +59,16 @@ static inline __m256 exp8(__m256 x) {
   return _mm256_mul_ps(p, _mm256_castsi256_ps(e));
 }
 
+/* Number of OpenMP threads the timed baseline uses from now on.  The caller states it instead of leaving it to
+ * OMP_NUM_THREADS, which process launchers set to 1 for their children. */
+void ar_cpu_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* q: [B,Hq,N,D]  k,v: [B,Hkv,N,D]  out: [B,Hq,N,D]; D a multiple of 16.
  * Only heads [bh_begin, bh_end) of the flattened (b, hq) axis are computed, so that a caller can
  * time a bounded sample of a large workload.  Returns the number of threads used. */

@@ -402,10 +402,12 @@ int ar_oracle_rows_f32(int in_dtype, const void* q_rows, const int64_t* row_idx,
     float* s = (float*)malloc(sizeof(float) * (size_t)N);
     float mx = AR_NEG;
     for (int64_t j = 0; j < N; j++) {
-      float dot = 0.f;
-      for (int64_t t = 0; t < D; t++) dot += load_elem(q_rows, in_dtype, r * D + t) * load_elem(k, in_dtype, j * D + t);
-      float sc = dot * scale;
-      if (causal && j > i) sc = AR_NEG;
+      float sc = AR_NEG; /* a key past the diagonal: its weight exp(-1e30 - mx) is exactly 0, the dot product is not needed */
+      if (!(causal && j > i)) {
+        float dot = 0.f;
+        for (int64_t t = 0; t < D; t++) dot += load_elem(q_rows, in_dtype, r * D + t) * load_elem(k, in_dtype, j * D + t);
+        sc = dot * scale;
+      }
       s[j] = sc;
       if (sc > mx) mx = sc;
     }
@@ -418,6 +420,49 @@ int ar_oracle_rows_f32(int in_dtype, const void* q_rows, const int64_t* row_idx,
     for (int64_t t = 0; t < D; t++) {
       float acc = 0.f;
       for (int64_t j = 0; j < N; j++) acc += s[j] * load_elem(v, in_dtype, j * D + t);
+      out[r * D + t] = acc * inv;
+    }
+    free(s);
+  }
+  return 0;
+}
+
+/* The Sage model of ar_oracle_flash (mode 3) for the listed query rows of one (b, h) pair, on tensors that are
+ * already quantised (ar_oracle_sage_quantize): the sampled check at sequence lengths where the whole head would
+ * take minutes.  q8_rows: [nrows, D] gathered INT8 rows; q_scale_rows: [nrows] the scale of each row's block;
+ * k8: [N, D]; k_scale: [ceil(N / block)]; v: [N, D] bf16; out: [nrows, D] f32 (acc * inv, not rounded).
+ * Same arithmetic and rounding points as mode 3: exact s32 dot, s = (float)acc * (sq * sk * scale), P -> bf16 rn,
+ * l over the unrounded p (src/runtime/cuda_flash_sage.rs:261,315-322). */
+int ar_oracle_rows_sage(const int8_t* q8_rows, const float* q_scale_rows, const int64_t* row_idx, int64_t nrows,
+                        const int8_t* k8, const float* k_scale, const uint16_t* v, float* out, int64_t N, int64_t D,
+                        int64_t block, int causal) {
+  if (block <= 0) return -1;
+  const float scale = 1.0f / sqrtf((float)D);
+#pragma omp parallel for schedule(dynamic)
+  for (int64_t r = 0; r < nrows; r++) {
+    const int64_t i = row_idx[r];
+    float* s = (float*)malloc(sizeof(float) * (size_t)N);
+    float mx = AR_NEG;
+    for (int64_t j = 0; j < N; j++) {
+      float sc = AR_NEG; /* past the diagonal: weight exactly 0 */
+      if (!(causal && j > i)) {
+        int32_t acc = 0;
+        for (int64_t t = 0; t < D; t++) acc += (int32_t)q8_rows[r * D + t] * (int32_t)k8[j * D + t];
+        sc = (float)acc * (q_scale_rows[r] * k_scale[j / block] * scale);
+      }
+      s[j] = sc;
+      if (sc > mx) mx = sc;
+    }
+    float l = 0.f;
+    for (int64_t j = 0; j < N; j++) {
+      const float p = expf(s[j] - mx);
+      l += p;
+      s[j] = round_bf16(p);
+    }
+    const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+    for (int64_t t = 0; t < D; t++) {
+      float acc = 0.f;
+      for (int64_t j = 0; j < N; j++) acc += s[j] * bf16_to_f32(v[j * D + t]);
       out[r * D + t] = acc * inv;
     }
     free(s);

@@ -1,0 +1,110 @@
+"""Benchmark configuration 5 on one GPU: the slab rank 0 owns when B=16, H=64, S=16384, D=128 (causal Sage) is cut
+over eight ranks -- 128 (batch, head) pairs -- on the inputs bench.py generates for it.
+
+Causal rows attend to row + 1 keys, so the INT8 rounding of single logits is averaged over few keys on the first
+rows.  The test therefore separates two questions:
+  * is the kernel faithful to the specified algorithm?  Every sampled row, the first ones included, against the
+    oracle's Sage model (same quantised tensors, same rounding points): max-abs <= 2e-2;
+  * how far is the specified algorithm from exact attention?  Rows >= 256 against the exact f32 oracle: max-abs
+    <= 2e-2 and cosine >= 0.999.  Rows < 256 against exact: reported per 16-row bucket (printed; run with -s),
+    bounded at 1e-1, cosine over all of them >= 0.999.
+INT8 tensors, scales and the K mean of two pairs are bit-exact against the oracle's prologue.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from helpers import cosine, from_dev_bf16, max_abs
+
+pytestmark = pytest.mark.gpu
+
+PAIRS = 128  # 1024 pairs / 8 ranks
+S, D = 16384, 128
+
+
+@pytest.fixture(scope="module")
+def slab(attn_lib):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no fallback path to test")
+    import bench
+    from autorust_b200 import ops
+    dev = torch.device("cuda", 0)
+    q, k, v = bench.long_context_slab(torch, dev, 0, PAIRS)
+    q4, k4, v4 = (t.view(1, PAIRS, S, D) for t in (q, k, v))
+    ws = torch.empty(ops.workspace_bytes("sage", q4, k4), dtype=torch.uint8, device=dev)
+    out = ops.attn_forward("sage", q4, k4, v4, None, True, workspace=ws)
+    torch.cuda.synchronize()
+    assert ops.last_status(ws) == 0
+    return ops, q, k, v, out[0], ws
+
+
+def _head_oracles(oracle_lib, q, k, v, pair, rows):
+    qb, kb, vb = from_dev_bf16(q[pair]), from_dev_bf16(k[pair]), from_dev_bf16(v[pair])
+    rows = np.asarray(rows, np.int64)
+    exact = oracle_lib.rows_f32(qb[rows], rows, kb, vb, True)
+    q8, k8, qs, ks, km = oracle_lib.sage_quantize(qb[None, None], kb[None, None], 128, True)
+    model = oracle_lib.rows_sage(q8[0, 0][rows], qs[0, 0][rows // 128], rows, k8[0, 0], ks[0, 0], vb, True)
+    return exact, model, (q8[0, 0], k8[0, 0], qs[0, 0], ks[0, 0], km[0, 0])
+
+
+def test_config5_first_rows_every_pair(slab, oracle_lib):
+    """Rows 0..255 of all 128 pairs: the kernel against the Sage model, and the per-row distance from exact."""
+    ops, q, k, v, out, _ = slab
+    rows = np.arange(256)
+    worst_exact = np.zeros(256)
+    worst_model = 0.0
+    dots, n_got, n_ex = 0.0, 0.0, 0.0
+    for pair in range(PAIRS):
+        exact, model, _ = _head_oracles(oracle_lib, q, k, v, pair, rows)
+        got = oracle_lib.bf16_to_f32(from_dev_bf16(out[pair, :256]))
+        worst_exact = np.maximum(worst_exact, np.abs(got - exact).max(axis=1))
+        worst_model = max(worst_model, max_abs(got, model))
+        dots += float((got.astype(np.float64) * exact).sum())
+        n_got += float((got.astype(np.float64) ** 2).sum())
+        n_ex += float((exact.astype(np.float64) ** 2).sum())
+    print("\nmax-abs against exact f32 attention, worst over 128 pairs, per bucket of 16 rows:")
+    for r0 in range(0, 256, 16):
+        print(f"  rows {r0:3d}-{r0 + 15:3d}: {worst_exact[r0:r0 + 16].max():.4f}")
+    above = np.nonzero(worst_exact > 2e-2)[0]
+    print(f"  rows above 2e-2: {above.tolist()}")
+    print(f"  against the Sage model: {worst_model:.4f}")
+    assert worst_model <= 2e-2
+    assert worst_exact.max() <= 1e-1
+    assert dots / np.sqrt(n_got * n_ex) >= 0.999
+
+
+def test_config5_later_rows_hold_the_exact_bound(slab, oracle_lib):
+    """Rows from 256 to the last tile on three pairs: 2e-2 and cosine 0.999 against exact, 2e-2 against the model."""
+    ops, q, k, v, out, _ = slab
+    rows = [256, 257, 383, 384, 511, 1000, 4095, 4096, 8191, 8192, 12345] + list(range(S - 128, S, 9)) + [S - 1]
+    for pair in (0, 77, PAIRS - 1):
+        exact, model, _ = _head_oracles(oracle_lib, q, k, v, pair, rows)
+        got = oracle_lib.bf16_to_f32(from_dev_bf16(out[pair][rows]))
+        assert max_abs(got, exact) <= 2e-2, (pair, max_abs(got, exact))
+        assert cosine(got, exact) >= 0.999
+        assert max_abs(got, model) <= 2e-2, (pair, max_abs(got, model))
+
+
+def test_config5_prologue_bits_and_relaunch(slab, oracle_lib):
+    import torch
+    ops, q, k, v, out, ws = slab
+    q8, k8, qs, ks, km = ops.sage_quantize(q.view(1, PAIRS, S, D), k.view(1, PAIRS, S, D), True)
+    torch.cuda.synchronize()
+    for pair in (5, 100):
+        _, _, (wq8, wk8, wqs, wks, wkm) = _head_oracles(oracle_lib, q, k, v, pair, [0])
+        assert np.array_equal(q8[0, pair].cpu().numpy(), wq8)
+        assert np.array_equal(k8[0, pair].cpu().numpy(), wk8)
+        assert np.array_equal(qs[0, pair].cpu().numpy().view(np.uint32), wqs.view(np.uint32))
+        assert np.array_equal(ks[0, pair].cpu().numpy().view(np.uint32), wks.view(np.uint32))
+        assert np.array_equal(km[0, pair].cpu().numpy().view(np.uint32), wkm.view(np.uint32))
+    # a second launch gives the same bits; every output lies inside the per-channel range of its pair's V
+    out2 = ops.attn_forward("sage", q.view(1, PAIRS, S, D), k.view(1, PAIRS, S, D), v.view(1, PAIRS, S, D), None, True,
+                            workspace=ws)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), out2[0].view(torch.int16))
+    vmax = v.float().amax(dim=1, keepdim=True)
+    vmin = v.float().amin(dim=1, keepdim=True)
+    o = out.float()
+    assert bool(((o <= vmax + 2e-2) & (o >= vmin - 2e-2)).all()) and not bool(torch.isnan(o).any())

@@ -295,3 +295,23 @@ def test_rows_helper_matches_full_oracle(oracle_lib):
     full = oracle_lib.flash(0, q, k, v, None, True)
     got = oracle_lib.rows_f32(q[0, 0, rows], rows, k[0, 0], v[0, 0], True)
     assert np.array_equal(got, full[0, 0, rows])
+
+
+def test_sage_rows_helper_matches_full_model(oracle_lib):
+    """rows_sage restates flash mode 3 for selected rows: with f32 output the two must agree bit for bit."""
+    q, k, v = normal_qkv(6, 1, 1, 1, 300, 128, k_offset_sigma=2.0)
+    qb, kb, vb = (oracle_lib.f32_to_bf16(x) for x in (q, k, v))
+    rows = np.array([0, 1, 5, 127, 128, 299])
+    for causal in (True, False):
+        full = oracle_lib.flash(3, qb, kb, vb, None, causal, block=128, smooth=True, out_bf16=False)
+        q8, k8, qs, ks, _ = oracle_lib.sage_quantize(qb, kb, 128, True)
+        got = oracle_lib.rows_sage(q8[0, 0][rows], qs[0, 0][rows // 128], rows, k8[0, 0], ks[0, 0], vb[0, 0], causal)
+        assert np.array_equal(got, full[0, 0, rows])
+
+
+def test_cpu_baseline_thread_count_is_explicit(oracle_lib):
+    q, k, v = normal_qkv(3, 1, 2, 2, 64, 64)
+    assert oracle_lib.set_cpu_threads(2) == 2
+    assert oracle_lib.cpu_sdpa_f32(q, k, v)[1] == 2
+    n = oracle_lib.set_cpu_threads()
+    assert n >= 1 and oracle_lib.cpu_sdpa_f32(q, k, v)[1] == n
