@@ -30,6 +30,7 @@ SYMBOLS = (
     "ar_attn_supported",
     "ar_attn_workspace_bytes",
     "ar_attn_forward",
+    "ar_attn_forward_replicated",
     "ar_attn_forward_strided",
     "ar_attn_train_forward",
     "ar_attn_train_workspace_bytes",
@@ -37,6 +38,7 @@ SYMBOLS = (
     "ar_sage_quantize",
     "ar_sage_quantize_fp8",
     "ar_sage_attention_prequantized",
+    "ar_sage_attention_prequantized_replicated",
     "ar_sage_attention_prequantized_fp8",
     "ar_sage_forward_static",
     "ar_attn_last_status",
@@ -72,6 +74,10 @@ def load() -> ctypes.CDLL:
     L.ar_attn_workspace_bytes.restype = sz
     L.ar_attn_forward.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, sz, p]
     L.ar_attn_forward.restype = ci
+    L.ar_attn_forward_replicated.argtypes = [ci, ci, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, sz, p]
+    L.ar_attn_forward_replicated.restype = ci
+    L.ar_sage_attention_prequantized_replicated.argtypes = [p, p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]
+    L.ar_sage_attention_prequantized_replicated.restype = ci
     L.ar_attn_forward_strided.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, p, p, p, p, ctypes.c_size_t, p]
     L.ar_attn_forward_strided.restype = ci
     L.ar_attn_train_forward.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p]

@@ -5,8 +5,12 @@
   autorust_b200/lib/libar_attn.so    the CUDA kernels + the C ABI of include/ar_attn.h
   autorust_b200/lib/libar_host.so    the C++ host layer that mirrors autorust's Tensor / Session /
                                      Settings / fused_attention_ex surface on top of that ABI
-  autorust_b200/lib/libar_gather.so  the NCCL output gather (kept apart so that single-GPU users
+  autorust_b200/lib/libar_gather.so  the output gather for N > 1 (kept apart so that single-GPU users
                                      need no NCCL at load time)
+  autorust_b200/lib/waittest/libar_attn.so
+                                     the same kernels with a wait budget of about a millisecond and a hook
+                                     that leaves one K tile unrequested: what tests/test_gpu_wait_expiry.py
+                                     loads to see a bounded wait run out and the kernel leave in order
 
 nvcc cross-compiles without a GPU; nothing here needs one.  Objects are rebuilt only when a
 source or header is newer than the library.
@@ -76,6 +80,32 @@ def build_kernels(force: bool = False) -> Path:
     return out
 
 
+# Sources whose device code contains bounded waits: rebuilt with the short budget for the wait-expiry test library.
+WAIT_SOURCES = ["attn_fwd_tc.cu", "sage_prologue.cu"]
+WAIT_TEST_FLAGS = ["-DAR_WAIT_TEST", "-DAR_WAIT_BUDGET_CYCLES=2000000ll"]
+
+
+def build_wait_test(force: bool = False) -> Path:
+    """The test-only variant of libar_attn.so (never loaded by the package itself)."""
+    build_kernels(force)
+    out_dir = LIB / "waittest"
+    out_dir.mkdir(exist_ok=True)
+    out = out_dir / "libar_attn.so"
+    srcs = [CSRC / s for s in KERNEL_SOURCES]
+    if not force and not _newer(out, srcs + _headers()):
+        return out
+    objs = []
+    for s in srcs:
+        if s.name in WAIT_SOURCES:
+            o = out_dir / (s.stem + ".o")
+            _run([_nvcc(), *NVCC_FLAGS, *WAIT_TEST_FLAGS, "-c", str(s), "-o", str(o)])
+        else:
+            o = LIB / (s.stem + ".o")
+        objs.append(str(o))
+    _run([_nvcc(), "-shared", "-o", str(out), *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+    return out
+
+
 def build_host(force: bool = False) -> Path | None:
     host_dir = CSRC / "host"
     srcs = sorted(host_dir.glob("*.cpp"))
@@ -126,6 +156,7 @@ def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_host(force)
     build_gather(force)
+    build_wait_test(force)
 
 
 if __name__ == "__main__":

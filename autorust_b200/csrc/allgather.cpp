@@ -1,5 +1,6 @@
-// libar_gather.so: NCCL all-gather of the attention output slabs (include/ar_attn_gather.h).
-// The only collective on the path: head-parallel attention shards without any reduction.
+// libar_gather.so: the gather of the attention output slabs (include/ar_attn_gather.h) -- NCCL's all-gather, or
+// buffers mapped between the ranks that the attention kernel (fused form) or the copy engines fill.
+// The only cross-GPU step on the path: head-parallel attention shards without any reduction.
 #include "../../include/ar_attn_gather.h"
 
 #include <cuda_runtime.h>
@@ -20,14 +21,12 @@ struct Comm {
   size_t bytes = 0;
   std::vector<void*> peer;
   int* fence_word = nullptr;
-  // pushes to different peers go out on separate streams (separate copy engines); events tie them to the caller's
-  static constexpr int kSide = 4;
+  // the pushes go out on a stream of the library's own; events tie it to the caller's
   static constexpr int kEvents = 64;
-  cudaStream_t side[kSide] = {};
+  cudaStream_t side = nullptr;
   cudaEvent_t ring[kEvents] = {};
   int next_event = 0;
   bool side_dirty = false;
-  int streams = 1;  // side streams in use (AR_GATHER_STREAMS, 1..kSide)
 };
 bool cuda_ok(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return true;
@@ -61,17 +60,10 @@ void* ar_gather_init(const void* id, int rank, int world) {
   ncclUniqueId u;
   std::memcpy(&u, id, sizeof(u));
   // The gather runs beside the attention kernel, whose CTAs fill an SM each: every CTA NCCL takes is an SM the
-  // attention kernel loses for the length of the gather.  Capping them (AR_GATHER_MAX_CTAS) was measured on two
-  // GPUs and loses more than it wins -- 32: 4.15 ms per step, 8: 4.76, 4: 6.13, 2: 10.2 -- so the default stays
-  // NCCL's own choice; the copy-engine path below takes no SM at all.
+  // attention kernel loses for the length of the gather.  Capping NCCL's CTAs was measured on two GPUs and loses
+  // more than it wins (32: 4.15 ms per step, 8: 4.76, 4: 6.13, 2: 10.2), so NCCL keeps its own choice; the mapped-
+  // buffer forms below take no SM from the attention kernel.
   ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
-  if (const char* e = std::getenv("AR_GATHER_MAX_CTAS")) {
-    const int v = std::atoi(e);
-    if (v > 0) {
-      cfg.minCTAs = 1;
-      cfg.maxCTAs = v;
-    }
-  }
   ncclComm_t c;
   if (!check(ncclCommInitRankConfig(&c, world, u, rank, &cfg), "ncclCommInitRankConfig")) return nullptr;
   Comm* out = new Comm();
@@ -141,32 +133,49 @@ int ar_gather_p2p_open(void* comm, size_t bytes) {
     return -6;
   }
   c->peer.assign((size_t)c->world, nullptr);
-  for (int r = 0; r < c->world; r++) {
+  bool mapped = true;
+  for (int r = 0; r < c->world && mapped; r++) {
     if (r == c->rank) {
       c->peer[(size_t)r] = c->local;
       continue;
     }
-    if (!cuda_ok(cudaIpcOpenMemHandle(&c->peer[(size_t)r], all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess),
-                 "cudaIpcOpenMemHandle"))
-      return -6;
+    mapped = cuda_ok(cudaIpcOpenMemHandle(&c->peer[(size_t)r], all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess),
+                     "cudaIpcOpenMemHandle");
+    if (!mapped) c->peer[(size_t)r] = nullptr;
   }
-  if (!cuda_ok(cudaMalloc((void**)&c->fence_word, sizeof(int)), "cudaMalloc")) return -6;
-  if (!cuda_ok(cudaMemset(c->fence_word, 0, sizeof(int)), "cudaMemset")) return -6;
-  // One stream of copies, one peer after the other, measured best on eight GPUs (4.79 ms per step of the benchmark
-  // against 6.55 ms with four streams: concurrent copies to several peers get in each other's way); the variable
-  // is there to measure it again on another machine.
-  if (const char* e = std::getenv("AR_GATHER_STREAMS")) {
-    const int v = std::atoi(e);
-    if (v >= 1 && v <= Comm::kSide) c->streams = v;
+  if (mapped) mapped = cuda_ok(cudaMalloc((void**)&c->fence_word, sizeof(int)), "cudaMalloc") &&
+                       cuda_ok(cudaMemset(c->fence_word, 0, sizeof(int)), "cudaMemset") &&
+                       cuda_ok(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking), "cudaStreamCreate");
+  for (int i = 0; mapped && i < Comm::kEvents; i++)
+    mapped = cuda_ok(cudaEventCreateWithFlags(&c->ring[i], cudaEventDisableTiming), "cudaEventCreate");
+  // All ranks leave with one verdict: a rank that could not map a peer must not leave the others believing that
+  // the gather is open.  (A second small collective; MIN over "mapped everything".)
+  const std::string first_error = g_err;
+  int* verdict = nullptr;
+  int mine_ok = mapped ? 1 : 0, all_ok = 0;
+  const bool agreed = cuda_ok(cudaMalloc((void**)&verdict, sizeof(int)), "cudaMalloc") &&
+                      cuda_ok(cudaMemcpy(verdict, &mine_ok, sizeof(int), cudaMemcpyHostToDevice), "cudaMemcpy") &&
+                      check(ncclAllReduce(verdict, verdict, 1, ncclInt32, ncclMin, c->comm, nullptr), "ncclAllReduce(open)") &&
+                      cuda_ok(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize") &&
+                      cuda_ok(cudaMemcpy(&all_ok, verdict, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
+  if (verdict) cudaFree(verdict);
+  if (!agreed || !all_ok) {
+    if (!mapped) g_err = first_error;
+    else if (agreed) g_err = "ar_gather_p2p_open: another rank could not map its peers";
+    ar_gather_p2p_close(comm);  // unmaps what was opened, frees the local buffer: a later open starts clean
+    return -6;
   }
-  for (int i = 0; i < Comm::kSide; i++)
-    if (!cuda_ok(cudaStreamCreateWithFlags(&c->side[i], cudaStreamNonBlocking), "cudaStreamCreate")) return -6;
-  for (int i = 0; i < Comm::kEvents; i++)
-    if (!cuda_ok(cudaEventCreateWithFlags(&c->ring[i], cudaEventDisableTiming), "cudaEventCreate")) return -6;
   return 0;
 }
 
 void* ar_gather_p2p_buffer(void* comm) { return comm ? static_cast<Comm*>(comm)->local : nullptr; }
+
+void* ar_gather_p2p_peer(void* comm, int rank) {
+  if (!comm) return nullptr;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->local || rank < 0 || rank >= c->world || c->peer.size() != (size_t)c->world) return nullptr;
+  return c->peer[(size_t)rank];
+}
 
 int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream) {
   if (!comm) return -2;
@@ -178,30 +187,15 @@ int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream)
   cudaEvent_t ready = c->ring[c->next_event];
   c->next_event = (c->next_event + 1) % Comm::kEvents;
   if (!cuda_ok(cudaEventRecord(ready, (cudaStream_t)cu_stream), "cudaEventRecord")) return -6;
-  // ... spread over the side streams so that several copy engines work at once: one copy per peer, or with fewer
-  // peers than streams each peer's range cut into pieces, starting with the next rank so that the ranks do not all
-  // write to the same peer at the same time.
-  const int peers = c->world - 1;
-  const int ns = c->streams;
-  const int pieces = peers >= ns ? 1 : ns / peers;
-  const size_t piece = ((bytes + (size_t)pieces - 1) / (size_t)pieces + 255) / 256 * 256;
-  bool waited[Comm::kSide] = {};
-  int turn = 0;
+  // ... one peer after the other, starting with the next rank so that the ranks do not all write to the same
+  // peer at the same time
+  if (!cuda_ok(cudaStreamWaitEvent(c->side, ready, 0), "cudaStreamWaitEvent")) return -6;
   for (int i = 1; i < c->world; i++) {
     const int r = (c->rank + i) % c->world;
-    for (size_t at = 0; at < bytes; at += piece, turn++) {
-      const int si = turn % ns;
-      cudaStream_t s = c->side[si];
-      if (!waited[si]) {
-        if (!cuda_ok(cudaStreamWaitEvent(s, ready, 0), "cudaStreamWaitEvent")) return -6;
-        waited[si] = true;
-      }
-      const size_t n = bytes - at < piece ? bytes - at : piece;
-      if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset + at, src + at, n,
-                                   cudaMemcpyDeviceToDevice, s),
-                   "cudaMemcpyAsync(peer)"))
-        return -6;
-    }
+    if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + offset, src, bytes, cudaMemcpyDeviceToDevice,
+                                 c->side),
+                 "cudaMemcpyAsync(peer)"))
+      return -6;
   }
   c->side_dirty = true;
   return 0;
@@ -213,37 +207,34 @@ int ar_gather_p2p_fence(void* comm, void* cu_stream) {
   if (!c->fence_word) return -5;
   // the caller's stream first collects the side streams' copies
   if (c->side_dirty) {
-    for (int i = 0; i < Comm::kSide; i++) {
-      cudaEvent_t done = c->ring[c->next_event];
-      c->next_event = (c->next_event + 1) % Comm::kEvents;
-      if (!cuda_ok(cudaEventRecord(done, c->side[i]), "cudaEventRecord")) return -6;
-      if (!cuda_ok(cudaStreamWaitEvent((cudaStream_t)cu_stream, done, 0), "cudaStreamWaitEvent")) return -6;
-    }
+    cudaEvent_t done = c->ring[c->next_event];
+    c->next_event = (c->next_event + 1) % Comm::kEvents;
+    if (!cuda_ok(cudaEventRecord(done, c->side), "cudaEventRecord")) return -6;
+    if (!cuda_ok(cudaStreamWaitEvent((cudaStream_t)cu_stream, done, 0), "cudaStreamWaitEvent")) return -6;
     c->side_dirty = false;
   }
-  // Stream order on every rank puts its pushes before its part of this all-reduce, and the all-reduce cannot
-  // finish anywhere before every rank has started its part.
+  // Stream order on every rank puts its pushes (and the kernels that stored into the peers) before its part of
+  // this all-reduce, and the all-reduce cannot finish anywhere before every rank has started its part.
   return check(ncclAllReduce(c->fence_word, c->fence_word, 1, ncclInt32, ncclMax, c->comm, (cudaStream_t)cu_stream),
                "ncclAllReduce(fence)")
              ? 0
              : -6;
 }
 
-void ar_gather_p2p_close(void* comm) {
+void ar_gather_p2p_close(void* comm) {  // (also the way out of a failed open: every member may be half set up)
   if (!comm) return;
   Comm* c = static_cast<Comm*>(comm);
   if (!c->local) return;
   cudaDeviceSynchronize();
-  for (int r = 0; r < c->world; r++)
+  for (int r = 0; r < (int)c->peer.size(); r++)
     if (r != c->rank && c->peer[(size_t)r]) cudaIpcCloseMemHandle(c->peer[(size_t)r]);
   c->peer.clear();
   if (c->fence_word) cudaFree(c->fence_word);
   c->fence_word = nullptr;
-  for (int i = 0; i < Comm::kSide; i++)
-    if (c->side[i]) {
-      cudaStreamDestroy(c->side[i]);
-      c->side[i] = nullptr;
-    }
+  if (c->side) {
+    cudaStreamDestroy(c->side);
+    c->side = nullptr;
+  }
   for (int i = 0; i < Comm::kEvents; i++)
     if (c->ring[i]) {
       cudaEventDestroy(c->ring[i]);

@@ -14,7 +14,9 @@ namespace {
 std::atomic<uint64_t> g_selected[5];
 std::atomic<uint64_t> g_launches;
 
-// Device status block used when the caller passes no workspace (word 0 is the status word).
+// The library's status block on each device.  Word 0: launch status of calls that bring no workspace (cleared before
+// every such launch).  Word 1: every expiry of a bounded wait in any kernel of the library is OR-ed in here as well,
+// and only ar_attn_last_status(NULL, ..) clears it -- a launch cannot erase what an earlier one reported.
 __device__ __align__(256) uint32_t g_status_word[64];
 
 // 1 when the current device is compute capability 10.x.
@@ -46,24 +48,8 @@ inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 inline bool aligned4(const void* p) { return ((uintptr_t)p & 3u) == 0; }  // f32 arrays read element-wise (NULL passes)
 
 constexpr size_t STATUS_BYTES = 256;
-
-struct SageLayout {
-  size_t q8, k8, q_scale, k_scale, k_mean, v16, total;
-};
-SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
-  const int64_t nblk = (S + 127) / 128;
-  SageLayout L;
-  size_t off = STATUS_BYTES;
-  L.q8 = off; off = align_up(off + (size_t)(B * Hq * S * D), 256);
-  L.k8 = off; off = align_up(off + (size_t)(B * Hkv * S * D), 256);
-  L.q_scale = off; off = align_up(off + sizeof(float) * (size_t)(B * Hq * nblk), 256);
-  L.k_scale = off; off = align_up(off + sizeof(float) * (size_t)(B * Hkv * nblk), 256);
-  L.k_mean = off; off = align_up(off + sizeof(float) * (size_t)(B * Hkv * D), 256);
-  L.v16 = off;
-  if (dtype == AR_DTYPE_F32) off = align_up(off + 2 * (size_t)(B * Hkv * S * D), 256);
-  L.total = off;
-  return L;
-}
+using ar::SageLayout;
+using ar::sage_layout;
 
 int check_shape(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0) return AR_ERR_SHAPE;
@@ -83,16 +69,62 @@ bool mode_has_kernel(int mode, int dtype, int64_t B, int64_t Hq, int64_t S, int6
   }
 }
 
+uint32_t* library_words() {
+  uint32_t* p = nullptr;
+  if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+// The launch status word of a call: the caller's (first word of its workspace, or the word it named), else the
+// library's word 0.
 uint32_t* status_ptr(void* workspace) {
   if (workspace) return (uint32_t*)workspace;
-  uint32_t* p = nullptr;
-  if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) return nullptr;
-  return p;
+  return library_words();
+}
+uint32_t* sticky_ptr() {
+  uint32_t* p = library_words();
+  return p ? p + 1 : nullptr;
+}
+
+bool replicas_ok(void* const* replicas, int n, ar::OutReplicas* out) {
+  out->n = 0;
+  if (n < 0 || n > 7 || (n > 0 && !replicas)) return false;
+  for (int i = 0; i < n; i++) {
+    if (!replicas[i] || ((uintptr_t)replicas[i] & 15u) != 0) return false;
+    out->p[i] = replicas[i];
+  }
+  out->n = n;
+  return true;
 }
 
 }  // namespace
 
 namespace ar {
+bool library_status_words(uint32_t** launch_word, uint32_t** sticky_word) {
+  uint32_t* p = library_words();
+  if (!p) return false;
+  *launch_word = p;
+  *sticky_word = p + 1;
+  return true;
+}
+
+SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  const int64_t nblk = (S + 127) / 128;
+  SageLayout L;
+  size_t off = STATUS_BYTES;
+  L.q8 = off; off = align_up(off + (size_t)(B * Hq * S * D), 256);
+  L.k8 = off; off = align_up(off + (size_t)(B * Hkv * S * D), 256);
+  L.q_scale = off; off = align_up(off + sizeof(float) * (size_t)(B * Hq * nblk), 256);
+  L.k_scale = off; off = align_up(off + sizeof(float) * (size_t)(B * Hkv * nblk), 256);
+  L.k_mean = off; off = align_up(off + sizeof(float) * (size_t)(B * Hkv * D), 256);
+  L.v16 = off;
+  if (dtype == AR_DTYPE_F32) off = align_up(off + 2 * (size_t)(B * Hkv * S * D), 256);
+  L.total = off;
+  return L;
+}
+
 // Lets other translation units of the library feed the launch counters.
 void count_launches(int mode, int kernels) {
   g_launches += (uint64_t)kernels;
@@ -137,6 +169,7 @@ int sage_quantize_any(const void* q, const void* k, int dtype, int8_t* q8, int8_
   a.fp8 = fp8;
   // this entry point has no workspace: its status goes to the library's own word (ar_attn_last_status(NULL, ...))
   a.status = status_ptr(nullptr);
+  a.sticky = sticky_ptr();
   if (!a.status || cudaMemsetAsync(a.status, 0, sizeof(uint32_t), (cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;
   int launches = 0;
   cudaError_t e = ar::launch_sage_prologue(a, (cudaStream_t)cu_stream, &launches);
@@ -157,9 +190,10 @@ int ar_sage_quantize_fp8(const void* q, const void* k, int dtype, uint8_t* q8, u
                            1, cu_stream);
 }
 
-int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
-                    int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
-                    size_t workspace_bytes, void* cu_stream) {
+namespace {
+int forward_impl(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const ar::OutReplicas& reps,
+                 const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal,
+                 void* workspace, size_t workspace_bytes, void* cu_stream) {
   if (!q || !k || !v || !o) return AR_ERR_NULL;
   int rc = check_shape(B, Hq, Hkv, S, D);
   if (rc != AR_OK) return rc;
@@ -171,6 +205,8 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   cudaStream_t stream = (cudaStream_t)cu_stream;
 
+  if (reps.n > 0 && (mode == AR_MODE_EXACT_F32 || mode == AR_MODE_TF32 || dtype != AR_DTYPE_BF16))
+    return AR_ERR_UNSUPPORTED;  // replicas receive bf16 rows of the tensor-core kernels
   if (mode == AR_MODE_EXACT_F32) {
     ar::ExactArgs a{(const float*)q, (const float*)k, (const float*)v, (float*)o, mask,
                     (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, causal};
@@ -194,6 +230,8 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
   a.status = status;
+  a.sticky = sticky_ptr();
+  a.replicas = reps;
   if (mode == AR_MODE_BF16) {
     a.mode = ar::TC_BF16;
     a.out_f32 = 0;
@@ -225,6 +263,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
     ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
     p.fp8 = mode == AR_MODE_SAGE_FP8;
     p.status = status;  // shared with the attention kernel: cleared once, before the first launch
+    p.sticky = sticky_ptr();
     int launches = 0;
     if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
     if (cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
@@ -254,6 +293,24 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
   g_launches++;
   g_selected[mode]++;
   return AR_OK;
+}
+}  // namespace
+
+int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
+                    int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                    size_t workspace_bytes, void* cu_stream) {
+  ar::OutReplicas none;
+  none.n = 0;
+  return forward_impl(mode, dtype, q, k, v, o, none, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes, cu_stream);
+}
+
+int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
+                               void* const* replicas, int n_replicas, const float* mask, int64_t B, int64_t Hq,
+                               int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace, size_t workspace_bytes,
+                               void* cu_stream) {
+  ar::OutReplicas reps;
+  if (!replicas_ok(replicas, n_replicas, &reps)) return n_replicas > 7 ? AR_ERR_UNSUPPORTED : AR_ERR_ALIGNMENT;
+  return forward_impl(mode, dtype, q, k, v, o, reps, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes, cu_stream);
 }
 
 int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
@@ -291,6 +348,7 @@ int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, c
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
   a.status = status;
+  a.sticky = sticky_ptr();
   int tq = 0, tk = 0, tv = 0;
   const int bf16 = (int)CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (!ar::make_tile_map(&a.tm_q, q, bf16, 2, B, Hq, S, D, q_strides[0], q_strides[1], q_strides[2], 64, 128, &tq) ||
@@ -350,13 +408,15 @@ int ar_attn_train_backward(const float* q, const float* k, const float* v, const
 
 namespace {
 int sage_prequantized_any(int mode, const void* q8, const void* k8, const float* q_scale, const float* k_scale,
-                          const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B, int64_t Hq,
-                          int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word, void* cu_stream) {
+                          const void* v_bf16, void* o, const ar::OutReplicas& reps, int out_dtype, const float* mask,
+                          int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
+                          void* cu_stream) {
   if (!q8 || !k8 || !q_scale || !k_scale || !v_bf16 || !o) return AR_ERR_NULL;
   int rc = check_shape(B, Hq, Hkv, S, D);
   if (rc != AR_OK) return rc;
   if (!mode_has_kernel(mode, AR_DTYPE_BF16, B, Hq, S, D)) return AR_ERR_UNSUPPORTED;
   if (out_dtype != AR_DTYPE_F32 && out_dtype != AR_DTYPE_BF16) return AR_ERR_UNSUPPORTED;
+  if (reps.n > 0 && out_dtype != AR_DTYPE_BF16) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q8) || !aligned16(k8) || !aligned16(v_bf16) || !aligned16(o)) return AR_ERR_ALIGNMENT;
   if (!aligned4(q_scale) || !aligned4(k_scale) || !aligned4(mask) || !aligned4(status_word)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
@@ -378,6 +438,8 @@ int sage_prequantized_any(int mode, const void* q8, const void* k8, const float*
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
   a.status = status;
+  a.sticky = sticky_ptr();
+  a.replicas = reps;
   if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
       !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
       !make_map(&a.tm_v, v_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
@@ -394,23 +456,39 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
                                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
                                    void* cu_stream) {
-  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, out_dtype, mask, B, Hq, Hkv, S, D,
-                               causal, status_word, cu_stream);
+  ar::OutReplicas none;
+  none.n = 0;
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, none, out_dtype, mask, B, Hq, Hkv, S,
+                               D, causal, status_word, cu_stream);
+}
+int ar_sage_attention_prequantized_replicated(const int8_t* q8, const int8_t* k8, const float* q_scale,
+                                              const float* k_scale, const void* v_bf16, void* o, void* const* replicas,
+                                              int n_replicas, const float* mask, int64_t B, int64_t Hq, int64_t Hkv,
+                                              int64_t S, int64_t D, int causal, void* status_word, void* cu_stream) {
+  ar::OutReplicas reps;
+  if (!replicas_ok(replicas, n_replicas, &reps)) return n_replicas > 7 ? AR_ERR_UNSUPPORTED : AR_ERR_ALIGNMENT;
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, reps, AR_DTYPE_BF16, mask, B, Hq, Hkv,
+                               S, D, causal, status_word, cu_stream);
 }
 int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, const float* q_scale,
                                        const float* k_scale, const void* v_bf16, void* o, int out_dtype,
                                        const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
                                        int causal, void* status_word, void* cu_stream) {
-  return sage_prequantized_any(AR_MODE_SAGE_FP8, q8, k8, q_scale, k_scale, v_bf16, o, out_dtype, mask, B, Hq, Hkv, S, D,
-                               causal, status_word, cu_stream);
+  ar::OutReplicas none;
+  none.n = 0;
+  return sage_prequantized_any(AR_MODE_SAGE_FP8, q8, k8, q_scale, k_scale, v_bf16, o, none, out_dtype, mask, B, Hq, Hkv, S,
+                               D, causal, status_word, cu_stream);
 }
 
 int ar_attn_last_status(void* workspace, void* cu_stream) {
-  uint32_t* status = status_ptr(workspace);
+  // a workspace (or a named status word): the status of the last launch that used it.  NULL: the library's
+  // accumulator of every launch since it was last read, which this call clears.
+  uint32_t* status = workspace ? (uint32_t*)workspace : sticky_ptr();
   if (!status) return AR_ERR_CUDA;
   uint32_t host = 0;
   if (cudaStreamSynchronize((cudaStream_t)cu_stream) != cudaSuccess) return AR_ERR_CUDA;
   if (cudaMemcpy(&host, status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return AR_ERR_CUDA;
+  if (host != 0 && !workspace && cudaMemset(status, 0, sizeof(uint32_t)) != cudaSuccess) return AR_ERR_CUDA;
   return host == 0 ? AR_OK : AR_ERR_DEVICE_WAIT;
 }
 

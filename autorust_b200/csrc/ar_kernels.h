@@ -9,6 +9,13 @@ namespace ar {
 // Tensor-core forward (attn_fwd_tc.cu): bf16 or Sage INT8 QK^T, bf16 PV.
 enum TcMode { TC_BF16 = 0, TC_SAGE = 1, TC_TF32 = 2, TC_SAGE_FP8 = 3 };  // TC_SAGE: INT8 operands; TC_SAGE_FP8: E4M3
 
+// Further buffers that receive the same bf16 output rows as `out`, at the same offsets: buffers of other GPUs
+// mapped into this process (the fused output gather).  Plain stores only; nothing is ever read from them.
+struct OutReplicas {
+  void* p[7];
+  int n;
+};
+
 struct TcArgs {
   int mode;             // TcMode
   int D;                // 64 or 128
@@ -27,7 +34,9 @@ struct TcArgs {
   const float* k_scale; // TC_SAGE: [B*Hkv, nblk]
   int B, Hq, Hkv, S;
   int causal;
-  uint32_t* status;     // device status word
+  OutReplicas replicas; // bf16 output only
+  uint32_t* status;     // the launch's device status word: zero at launch, set when a bounded wait ran out
+  uint32_t* sticky;     // the library's accumulator of the same bits (nullable)
 };
 cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream);
 // Rank-4 tile map (128-byte swizzle) of a tensor indexed (batch, head, row, inner) whose element lies at
@@ -39,6 +48,19 @@ bool make_tile_map(CUtensorMap* m, const void* ptr, int cu_dtype, int esize, lon
                    long long inner, long long sb, long long sh, long long sr, int box_inner, int box_rows,
                    int* token_major_bit);
 bool attn_tc_has(int mode, int D);
+
+// The library's own status block on the current device (api.cu): word 0 is the launch status of calls that bring
+// no workspace, word 1 accumulates every expiry of a bounded wait until the host reads and clears it.
+// False when the address cannot be resolved.
+bool library_status_words(uint32_t** launch_word, uint32_t** sticky_word);
+
+// Layout of the Sage workspace (offsets in bytes from its start; every section 256-byte aligned, the first 256 bytes
+// are the status block): INT8 or FP8 copies of Q and K, their per-block scales, the K mean, and for f32 tensors
+// the bf16 copy of V.
+struct SageLayout {
+  size_t q8, k8, q_scale, k_scale, k_mean, v16, total;
+};
+SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D);
 
 // Exact f32 forward on FFMA (attn_fwd_exact.cu).
 struct ExactArgs {
@@ -72,6 +94,7 @@ struct PrologueArgs {
   int smooth;
   int fp8 = 0;                 // 0: INT8, scale amax/127 (the default); 1: FP8 E4M3, scale amax/448
   uint32_t* status = nullptr;  // device word a bounded wait that ran out is recorded in; cleared by the caller
+  uint32_t* sticky = nullptr;  // the library's accumulator of the same bits
 };
 // Returns the number of kernels launched through *launches.
 cudaError_t launch_sage_prologue(const PrologueArgs& a, cudaStream_t stream, int* launches);

@@ -16,12 +16,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -51,56 +45,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// try_wait that lets the hardware suspend the thread for up to `hint_ns` while the phase is pending.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0;
-}
-
 // Wait budget in SM clock cycles (clock64): about 0.4 s at 2 GHz -- far longer than any launch of these
 // kernels, short enough that a broken pipeline ends by itself.  The SM-local cycle counter is used
 // because reading it costs a few cycles, whereas %globaltimer is a slow system register.
-#ifndef AR_WAIT_MODE
-#define AR_WAIT_MODE 0
-#endif
 #ifndef AR_WAIT_BUDGET_CYCLES
 #define AR_WAIT_BUDGET_CYCLES 800000000ll
 #endif
 
-// Bounded wait on `bar` for phase `parity`. `abort_flag` is a CTA-shared word: once
-// any wait in the CTA has run out, every later wait returns false at once.
-// On expiry the site id is OR-ed into *status (global memory; may be null).
+// Where a wait that ran out is recorded.  `abort_flag` is a CTA-shared word: once any wait in the CTA has run out,
+// every later wait returns false at once.  `status` is the launch's device word (cleared by the host before the
+// launch; a CTA that finds it set on entry leaves without working), `sticky` the library's accumulator, which only
+// the host clears when it reads it.  Either may be null.
+struct WaitCtx {
+  volatile uint32_t* abort_flag;
+  uint32_t* status;
+  uint32_t* sticky;
+};
+
+// Bounded wait on `bar` for phase `parity`.  On expiry the site id is OR-ed into the status words.
 // mbarrier.try_wait suspends the thread in hardware for a bounded time, so the loop is not a hot spin.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t site) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
-  if (*abort_flag) return false;
+  if (*w.abort_flag) return false;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-#if AR_WAIT_MODE == 1
-    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
-#elif AR_WAIT_MODE == 2
     if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(40);
-#elif AR_WAIT_MODE == 3
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(200);
-#else
-    if (mbar_try_wait(bar, parity)) return true;
-#endif
     if ((++spins & 0x3f) == 0) {
-      if (*abort_flag) return false;
+      if (*w.abort_flag) return false;
       if (clock64() - t0 > AR_WAIT_BUDGET_CYCLES) {
-        *abort_flag = 1u;
-        if (status) atomicOr(status, 0x80000000u | site);
+        *w.abort_flag = 1u;
+        if (w.status) atomicOr(w.status, 0x80000000u | site);
+        if (w.sticky) atomicOr(w.sticky, 0x80000000u | site);
         return false;
       }
     }
@@ -124,13 +100,6 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
 // Tiled load of one box into shared memory; completion is signalled on `bar` as
 // transaction bytes. Coordinates are innermost first. The innermost coordinate
 // times the element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y,
-                                            int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z,
                                             int w) {
   asm volatile(
@@ -146,17 +115,6 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
                "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int x, int y, int z) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(m),
-               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
-
 // ----------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -182,50 +140,8 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 
 enum MmaKind { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2, KIND_F8 = 3 };
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-template <int KIND>
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  if constexpr (KIND == KIND_F16) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else if constexpr (KIND == KIND_TF32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-// D[tmem] (+)= A[tmem] * B[smem desc]
-template <int KIND>
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  if constexpr (KIND == KIND_F16) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-
-// The same two instructions with the 64-bit shared-memory descriptors passed as (low, high) words.
+// D[tmem] (+)= A[smem desc] * B[smem desc] and D[tmem] (+)= A[tmem] * B[smem desc], with the 64-bit shared-memory
+// descriptors passed as (low, high) words.
 // The issuing thread keeps the high words (layout, strides) and per-tile low words (address >> 4)
 // in registers and only adds a small constant to a low word per instruction, which keeps the
 // single-threaded issue loop short.
@@ -306,17 +222,8 @@ __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint
   return base + (lane << 16) + col;
 }
 
-// Each thread of a warp reads 16 consecutive 32-bit columns of "its" lane
+// Each thread of a warp reads 32 consecutive 32-bit columns of "its" lane
 // (lane = 32 * (warp % 4) + laneid).
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "

@@ -42,27 +42,13 @@ namespace ar {
 namespace {
 using namespace arptx;
 
-// Timeline of one CTA (-DAR_TRACE=3, debug builds only): clock() at fixed points of a few steps.
-#if defined(AR_TRACE) && AR_TRACE >= 3
-#ifndef AR_TL_J0
-#define AR_TL_J0 20  // first of the eight steps that are recorded
-#endif
-__device__ unsigned g_timeline[4 * 8 * 16];
-#define TL(role, j, ev)                                                                   \
-  do {                                                                                    \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && ((j) >= AR_TL_J0 && (j) < AR_TL_J0 + 8))                      \
-      g_timeline[((role) * 8 + ((j) - AR_TL_J0)) * 16 + (ev)] = (unsigned)clock();              \
-  } while (0)
-#else
-#define TL(role, j, ev)
+#ifdef AR_WAIT_TEST
+__device__ int g_test_skip_k_tile = -1;
 #endif
 
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per step
-#ifndef AR_NPART
-#define AR_NPART 2
-#endif
-constexpr int NPART = AR_NPART;  // P of a step is handed to the MMA warp in this many parts (1, 2 or 4)
+constexpr int NPART = 2;  // P of a step is handed to the MMA warp in two halves of 64 keys
 constexpr float LOG2E = 1.4426950408889634f;
 // The reference's finite sentinel (-1e30), expressed in the log2 domain the softmax works in, so that
 // a logit masked by an additive -1e30 still ties with the initial running max (p = 1 for a fully
@@ -91,10 +77,7 @@ constexpr float FOLD_MAX_C = 1.0e-3f;
 
 // Which of the 16 column pairs of each 32-column group take their exponential on the FMA pipe (bit i = pair i):
 // the MUFU unit delivers 16 ex2 per clock and SM, which alone would bound a step of two tiles at 2048 cycles.
-#ifndef AR_POLY_MASK
-#define AR_POLY_MASK 0x0000u
-#endif
-constexpr uint32_t POLY_MASK = AR_POLY_MASK;
+constexpr uint32_t POLY_MASK = 0x8888u;  // one pair in four
 
 // 2^x for two lanes on the MUFU unit.
 __device__ __forceinline__ void exp2_mufu_x2(uint64_t x2, float& p0, float& p1) {
@@ -249,7 +232,8 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
         x2 = pack_f32x2(__uint_as_float(sv[qd * 32 + 2 * i]), __uint_as_float(sv[qd * 32 + 2 * i + 1]));
       }
       float p0, p1;
-      if (((POLY_MASK >> i) & 1u) != 0)  // i is a constant of the unrolled loop
+      // (i is a constant of the unrolled loop; boundary steps keep the MUFU path, whose 2^-inf is exactly 0)
+      if (EDGE == 0 && ((POLY_MASK >> i) & 1u) != 0)
         exp2_poly_x2(fma_f32x2(x2, c2, negm2), p0, p1);
       else
         exp2_mufu_x2(fma_f32x2(x2, c2, negm2), p0, p1);
@@ -262,12 +246,12 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
         pk[i] = pack_bf16x2(p0, p1);
       }
     }
-    if (qd > 0 && qd % (4 / NPART) == 0) {
-      // The stores of the previous part were issued a quarter ago and have landed by now: hand that part
+    if (qd == 2) {
+      // The stores of the first half were issued a quarter ago and have landed by now: hand that half
       // of P to the MMA warp, whose first PV instructions then run under the rest of this loop.
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_parts + qd / (4 / NPART) - 1);
+      mbar_arrive(p_parts);
     }
     if constexpr (MODE == TC_TF32)
       tmem_st32(tS + qd * 32, pk);
@@ -316,7 +300,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
                    int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
-                   uint32_t* status) {
+                   const OutReplicas reps, uint32_t* status, uint32_t* sticky) {
   using C = Cfg<MODE, D>;
   constexpr int ST = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -335,6 +319,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* o_full = p_part + 2 * NPART;  // [2]
   uint32_t* tmem_slot = (uint32_t*)(o_full + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  const WaitCtx wctx{abort_flag, status, sticky};
 
   const int tid = threadIdx.x;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler as well
@@ -363,14 +348,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
   const int nkv_max = max(nkv[0], nkv[1]);
 
-#if defined(AR_TRACE) && AR_TRACE >= 3
-  if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    g_timeline[3 * 8 * 16 + 0] = (unsigned)clock();
-    g_timeline[3 * 8 * 16 + 1] = (unsigned)gt;
-  }
-#endif
   // Q and one K/V pair per ring stage: nothing to wait for, the stages are empty
   auto issue_q = [&]() {
     for (int t = 0; t < 2; t++) {
@@ -382,6 +359,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   };
   auto issue_k = [&](int j) {
     const int s = j % ST;
+#ifdef AR_WAIT_TEST
+    // Test build only: the K tile whose index the test set is never requested, so that the wait for it runs out
+    // (after the short budget that build is compiled with) and the CTA leaves through its bounded-wait path.
+    if (j == g_test_skip_k_tile) return;
+#endif
     mbar_arrive_expect_tx(&k_full[s], C::QK_TILE_BYTES);
     for (int bx = 0; bx < C::QK_BOXES; bx++)
       load_tile(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN, kvh, 1);
@@ -399,8 +381,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int preloaded = min(ST, nkv_max);  // K/V pairs issued before the CTA-wide barrier below
   // The producer thread sets up the barriers and starts the first loads itself, before the CTA meets: the copies
   // are in flight while the TMEM allocation and the barrier complete (a CTA of a short sequence is mostly latency).
+  bool lost = false;  // (meaningful in the producer thread only)
   if (warp == 8 && lane == 0) {
-    *abort_flag = 0;
+    // A launch whose status word is already set (a wait ran out in an earlier CTA) is lost: this CTA only allocates
+    // and frees its TMEM, so that the rest of the grid drains in microseconds instead of one wait budget per wave.
+    lost = status != nullptr && (*(volatile uint32_t*)status & 0x80000000u) != 0;
+    *abort_flag = lost ? 1u : 0u;
     for (int i = 0; i < 2; i++) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
@@ -417,10 +403,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     prefetch_tmap(&tm_q);
     prefetch_tmap(&tm_k);
     prefetch_tmap(&tm_v);
-    issue_q();
-    for (int j = 0; j < preloaded; j++) {
-      issue_k(j);
-      issue_v(j);
+    if (!lost) {
+      issue_q();
+      for (int j = 0; j < preloaded; j++) {
+        issue_k(j);
+        issue_v(j);
+      }
     }
   }
   if (warp == 9) {
@@ -436,21 +424,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int issued = preloaded;
-      for (int j = preloaded; j < nkv_max; j++) {
+      int issued = lost ? 0 : preloaded;
+      for (int j = preloaded; j < nkv_max && !lost; j++) {
         const int s = j % ST;
         const int n = j / ST;
         // a stage is free once the MMAs that read pair j - ST from it have completed; K's comes free a step earlier
-        if (!mbar_wait(&k_empty[s], (n - 1) & 1, abort_flag, status, 0x10)) break;
+        if (!mbar_wait(&k_empty[s], (n - 1) & 1, wctx, 0x10)) break;
         issue_k(j);
-        if (!mbar_wait(&v_empty[s], (n - 1) & 1, abort_flag, status, 0x11)) {
+        if (!mbar_wait(&v_empty[s], (n - 1) & 1, wctx, 0x11)) {
           mbar_wait_quiet(&k_full[s], n & 1);  // the K tile just started
           break;
         }
         issue_v(j);
         issued = j + 1;
       }
-      if (*abort_flag) {
+      if (*abort_flag && !lost) {
         // A wait ran out somewhere in this CTA.  Let the loads this thread started land (bounded)
         // before the CTA's shared memory is handed back.
         for (int t = 0; t < 2; t++)
@@ -505,10 +493,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       };
 
       bool ok = true;
-      if (nkv_max > 0) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, abort_flag, status, 0x20));
+      if (nkv_max > 0) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, wctx, 0x20));
       for (int t = 0; t < 2 && ok; t++) {
         if (nkv[t] == 0) continue;
-        ok = __all_sync(0xffffffffu, mbar_wait(&q_full[t], 0, abort_flag, status, 0x21));
+        ok = __all_sync(0xffffffffu, mbar_wait(&q_full[t], 0, wctx, 0x21));
         if (!ok) break;
         tc_fence_after();
         issue_qk(t, 0);
@@ -518,17 +506,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int j = 0; j < nkv_max && ok; j++) {
         const int s = j % ST;
         const int s1 = (j + 1) % ST;
-        if (lane == 0) TL(2, j, 0);
-
-        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, status, 0x22));
-
-        if (lane == 0) TL(2, j, 1);
+        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], (j / ST) & 1, wctx, 0x22));
         if (!ok) break;
         // K(j+1) is needed right after the last PV of a tile: see it arrive now, off the critical path
         if (j + 1 < nkv_max) {
-
-          ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, abort_flag, status, 0x24));
-
+          ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, wctx, 0x24));
           if (!ok) break;
         }
         for (int t = 0; t < 2 && ok; t++) {
@@ -536,24 +518,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           // P arrives in NPART parts: the first PV MMAs run under the exponentials of the later parts
 #pragma unroll
           for (int hf = 0; hf < NPART; hf++) {
-
-            ok = __all_sync(0xffffffffu, mbar_wait(&p_part[NPART * t + hf], j & 1, abort_flag, status, 0x23));
-
-            if (lane == 0 && hf == NPART - 1) TL(2, j, 2 + 4 * t);
+            ok = __all_sync(0xffffffffu, mbar_wait(&p_part[NPART * t + hf], j & 1, wctx, 0x23));
             if (!ok) break;
             tc_fence_after();
-
             issue_pv(t, s, j > 0, hf);
-
           }
           if (!ok) break;
-          if (lane == 0) TL(2, j, 3 + 4 * t);
           if (j + 1 < nkv[t]) {
-            if (lane == 0) TL(2, j, 4 + 4 * t);
-
             issue_qk(t, s1);
-
-            if (lane == 0) TL(2, j, 5 + 4 * t);
             commit_one(&s_full[t]);
           } else {
             commit_one(&o_full[t]);
@@ -562,7 +534,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!ok) break;
         commit_one(&v_empty[s]);
         if (j + 1 < nkv_max) commit_one(&k_empty[s1]);
-        if (lane == 0) TL(2, j, 10);
       }
     }
   } else if (warp < 8) {
@@ -582,11 +553,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     bool ok = true;
     for (int j = 0; j < nkv[t]; j++) {
-      if (r == 0) TL(t, j, 0);
-
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, status, 0x30));
-
-      if (r == 0) TL(t, j, 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, wctx, 0x30));
       if (!ok) break;
       tc_fence_after();
       uint32_t sv[BN];
@@ -595,8 +562,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 64, sv + 64);
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
-
-      if (r == 0) TL(t, j, 2);
       float c = scale_log2;
       if (C::QUANT) c *= qs * k_scale[(size_t)kvbh * nblk + j];
       const int col0 = j * BN;
@@ -614,33 +579,39 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
       else
         softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-
-      if (r == 0) TL(t, j, 3);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_part[NPART * t + NPART - 1]);
-
-      if (r == 0) TL(t, j, 4);
     }
     if (ok && nkv[t] > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], 0, abort_flag, status, 0x31));
+      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], 0, wctx, 0x31));
       if (ok) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        const size_t obase = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)row * o_ss);
+        if (out_f32) {
+          const size_t obase = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)row * o_ss);
 #pragma unroll
-        for (int cch = 0; cch < D / 32; cch++) {
-          uint32_t ov[32];
-          tmem_ld32(tO + cch * 32, ov);
-          tmem_wait_ld();
-          if (row < N) {
-            if (out_f32) {
+          for (int cch = 0; cch < D / 32; cch++) {
+            uint32_t ov[32];
+            tmem_ld32(tO + cch * 32, ov);
+            tmem_wait_ld();
+            if (row < N) {
               float4* dst = (float4*)((float*)out + obase + cch * 32);
 #pragma unroll
               for (int i = 0; i < 8; i++)
                 dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv, __uint_as_float(ov[4 * i + 1]) * inv,
                                      __uint_as_float(ov[4 * i + 2]) * inv, __uint_as_float(ov[4 * i + 3]) * inv);
-            } else {
+            }
+          }
+        } else if (reps.n == 0) {
+          // one output buffer, in this GPU's memory: every thread stores its own row, L2 merges the pieces
+          const size_t obase = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)row * o_ss);
+#pragma unroll
+          for (int cch = 0; cch < D / 32; cch++) {
+            uint32_t ov[32];
+            tmem_ld32(tO + cch * 32, ov);
+            tmem_wait_ld();
+            if (row < N) {
               uint4* dst = (uint4*)((uint16_t*)out + obase + cch * 32);
 #pragma unroll
               for (int i = 0; i < 4; i++) {
@@ -653,6 +624,48 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               }
             }
           }
+        } else {
+          // Replicas are other GPUs' buffers: what crosses NVLink should be whole 128-byte runs, not one 16-byte
+          // piece per row and instruction.  The rows leave through shared memory: the tile's Q buffer is free (every
+          // QK^T of the tile has completed), 128 rows x 128 bytes per pass of 64 columns, the 16-byte chunk c of row
+          // r kept at c ^ (r & 7); each warp reads back only the 32 rows it wrote and stores every run to the local
+          // buffer and to each replica (plain stores; nothing is read from a replica).
+          uint8_t* stage = sQ + t * C::QK_TILE_BYTES;
+          static_assert(C::QK_TILE_BYTES >= BM * 128, "staging area of the epilogue");
+          const int wrow0 = (warp & 3) * 32;
+#pragma unroll 1
+          for (int pass = 0; pass < D / 64; pass++) {
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+              uint32_t ov[32];
+              tmem_ld32(tO + pass * 64 + half * 32, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                uint4 w;
+                w.x = pack_bf16x2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+                w.y = pack_bf16x2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+                w.z = pack_bf16x2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+                w.w = pack_bf16x2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+                *(uint4*)(stage + r * 128 + (((half * 4 + i) ^ (r & 7)) * 16)) = w;
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const int rr = wrow0 + 4 * i + (lane >> 3);
+              const int ch = lane & 7;
+              const uint4 w = *(const uint4*)(stage + rr * 128 + ((ch ^ (rr & 7)) * 16));
+              const int grow = q0 + t * BM + rr;
+              if (grow < N) {
+                const size_t off = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)grow * o_ss) * 2 +
+                                   (size_t)(pass * 128 + ch * 16);
+                *(uint4*)((uint8_t*)out + off) = w;
+                for (int e = 0; e < reps.n; e++) *(uint4*)((uint8_t*)reps.p[e] + off) = w;
+              }
+            }
+            __syncwarp();
+          }
         }
       }
     }
@@ -661,14 +674,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tb, 512);
-#if defined(AR_TRACE) && AR_TRACE >= 3
-  if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    g_timeline[3 * 8 * 16 + 2] = (unsigned)clock();
-    g_timeline[3 * 8 * 16 + 3] = (unsigned)gt;
-  }
-#endif
 }
 
 template <int MODE, int D>
@@ -687,7 +692,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   dim3 grid((a.S + 2 * BM - 1) / (2 * BM), a.B * a.Hq, 1);
   kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale, a.k_scale, a.S,
                                                      a.Hq, a.Hkv, a.causal, a.out_f32, a.token_major, a.o_sb, a.o_sh,
-                                                     a.o_ss, a.status);
+                                                     a.o_ss, a.replicas, a.status, a.sticky);
   return cudaGetLastError();
 }
 
@@ -742,9 +747,10 @@ cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
 
 }  // namespace ar
 
-#if defined(AR_TRACE) && AR_TRACE >= 3
-extern "C" int ar_debug_read_timeline(unsigned* out, int n) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, ar::g_timeline, (size_t)n * 4);
+#ifdef AR_WAIT_TEST
+// Test build only (compiled with a wait budget of about a millisecond): which staged K tile the producer leaves out,
+// -1 for none.
+extern "C" int ar_test_skip_k_tile(int j) {
+  return (int)cudaMemcpyToSymbol(ar::g_test_skip_k_tile, &j, sizeof(int));
 }
 #endif

@@ -166,7 +166,18 @@ void empty_cache(int device) {
   for (auto& kv : victims) cudaFree(kv.second);
 }
 void* device_stream(int device) { return dev_state(resolve_device(device)).stream; }
-void set_device_stream(int device, void* cu_stream) { dev_state(resolve_device(device)).stream = (cudaStream_t)cu_stream; }
+void set_device_stream(int device, void* cu_stream) {
+  device = resolve_device(device);
+  DeviceState& st = dev_state(device);
+  if (st.stream == (cudaStream_t)cu_stream) return;
+  // Cached allocations are reused in the order of the launch stream: work queued on the old stream must be over
+  // before buffers it still uses can be handed to work on the new one.
+  {
+    DeviceGuard guard(device);
+    cuda_check(cudaStreamSynchronize(st.stream), "cudaStreamSynchronize");
+  }
+  st.stream = (cudaStream_t)cu_stream;
+}
 void synchronize(int device) {
   device = resolve_device(device);
   DeviceGuard guard(device);
@@ -465,6 +476,15 @@ void attention_host(AttentionKind kind, const void* q, const void* k, const void
     slot[i].ws = std::make_shared<Buffer>(dev, ws_bytes ? ws_bytes : 256);
   }
   StreamSet st;
+  {
+    // The slots come from the allocation cache, whose reuse is ordered by the device's launch stream: a kernel of an
+    // earlier operator call may still be reading or writing this memory.  The three private streams start behind it.
+    cudaEvent_t prior = st.event();
+    cuda_check(cudaEventRecord(prior, dev_state(dev).stream), "cudaEventRecord");
+    cuda_check(cudaStreamWaitEvent(st.in, prior, 0), "cudaStreamWaitEvent");
+    cuda_check(cudaStreamWaitEvent(st.run, prior, 0), "cudaStreamWaitEvent");
+    cuda_check(cudaStreamWaitEvent(st.out, prior, 0), "cudaStreamWaitEvent");
+  }
   std::shared_ptr<Buffer> mask_dev;
   if (mask_host) {
     mask_dev = std::make_shared<Buffer>(dev, (size_t)(S * S) * 4);
@@ -500,10 +520,10 @@ void attention_host(AttentionKind kind, const void* q, const void* k, const void
   cuda_check(cudaStreamSynchronize(st.run), "cudaStreamSynchronize");
   cuda_check(cudaStreamSynchronize(st.out), "cudaStreamSynchronize");
   if (rc_first != AR_OK) throw Error(std::string("attention_host: ") + ar_attn_strerror(rc_first));
-  for (int i = 0; i < slots; i++) {
-    const int status = ar_attn_last_status(slot[i].ws->ptr(), st.run);
-    if (status != AR_OK) throw Error(std::string("attention_host: ") + ar_attn_strerror(status));
-  }
+  // A slot's own status word only tells about the last chunk that used it; the library's accumulator covers all of
+  // them (reading it clears it).
+  const int status = ar_attn_last_status(nullptr, st.run);
+  if (status != AR_OK) throw Error(std::string("attention_host: ") + ar_attn_strerror(status));
 }
 
 Tensor Tensor::attention_kind(const Tensor& key, const Tensor& value, const Tensor* attn_mask, double dropout_p,

@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(256) quantize_pipe_kernel(const void* __restri
                                                             const float* __restrict__ k_mean, int8_t* __restrict__ q8,
                                                             int8_t* __restrict__ k8, float* __restrict__ q_scale,
                                                             float* __restrict__ k_scale, int S, int BHq, int BHk,
-                                                            int smooth, int fp8, uint32_t* status) {
+                                                            int smooth, int fp8, uint32_t* status, uint32_t* sticky) {
   using P = QuantPipe<DTYPE, D>;
   constexpr int CH = D / 8;
   constexpr int NCHUNK = 128 * CH / 256;
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(256) quantize_pipe_kernel(const void* __restri
 #pragma unroll
       for (int i = 0; i < 8; i++) mu[i] = k_mean[(size_t)bh * D + c * 8 + i];
     }
-    const bool ok = arptx::mbar_wait(&full[stage], (uint32_t)(it / ST) & 1u, &abort_flag, status, 0x40);
+    const bool ok = arptx::mbar_wait(&full[stage], (uint32_t)(it / ST) & 1u, arptx::WaitCtx{&abort_flag, status, sticky}, 0x40);
     if (!__syncthreads_and(ok)) break;  // a copy that never lands: the status word says so, the CTA leaves together
     const uint8_t* blockp = ring + stage * P::BLOCK_BYTES;
     float x[NCHUNK][8];
@@ -494,7 +494,7 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
     int grid = (dev < 64 ? sm_count[dev] : 148) * P::CTAS_PER_SM;
     if (grid > items) grid = items;
     kern<<<grid, 256, P::SMEM_BYTES, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale, a.k_scale, a.S, bhq, bhk,
-                                               a.smooth, a.fp8, a.status);
+                                               a.smooth, a.fp8, a.status, a.sticky);
   } else {
     quantize_kernel<DTYPE, D><<<dim3(nblk, bhq + bhk, 1), 256, 0, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale,
                                                                            a.k_scale, a.S, bhq, a.smooth, a.fp8);

@@ -56,8 +56,6 @@ int static_scratch(void** out) {
   return AR_OK;
 }
 
-inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
-
 bool tile_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t B, int64_t H, int64_t S,
               int64_t D) {
   return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, 128 / esize, 128, nullptr);
@@ -75,16 +73,8 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
   if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15u) != 0) return AR_ERR_ALIGNMENT;
   if (mask && ((uintptr_t)mask & 3u)) return AR_ERR_ALIGNMENT;
   // the layout of ar_attn_forward's Sage workspace, placed in the static array
-  const int64_t nblk = (S + 127) / 128;
-  size_t off = 256;
-  const size_t o_q8 = off;  off = up256(off + (size_t)(B * Hq * S * D));
-  const size_t o_k8 = off;  off = up256(off + (size_t)(B * Hkv * S * D));
-  const size_t o_qs = off;  off = up256(off + sizeof(float) * (size_t)(B * Hq * nblk));
-  const size_t o_ks = off;  off = up256(off + sizeof(float) * (size_t)(B * Hkv * nblk));
-  const size_t o_km = off;  off = up256(off + sizeof(float) * (size_t)(B * Hkv * D));
-  const size_t o_v16 = off;
-  if (dtype == AR_DTYPE_F32) off = up256(off + 2 * (size_t)(B * Hkv * S * D));
-  if (off > (size_t)AR_SAGE_STATIC_SCRATCH_BYTES) return AR_ERR_TOO_LARGE;
+  const ar::SageLayout L = ar::sage_layout(dtype, B, Hq, Hkv, S, D);
+  if (L.total > (size_t)AR_SAGE_STATIC_SCRATCH_BYTES) return AR_ERR_TOO_LARGE;
 
   int major = 0, dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -98,22 +88,25 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
   uint8_t* ws = (uint8_t*)base;
   cudaStream_t stream = (cudaStream_t)cu_stream;
 
-  int8_t* q8 = (int8_t*)(ws + o_q8);
-  int8_t* k8 = (int8_t*)(ws + o_k8);
-  float* qs = (float*)(ws + o_qs);
-  float* ks = (float*)(ws + o_ks);
-  float* km = (float*)(ws + o_km);
+  int8_t* q8 = (int8_t*)(ws + L.q8);
+  int8_t* k8 = (int8_t*)(ws + L.k8);
+  float* qs = (float*)(ws + L.q_scale);
+  float* ks = (float*)(ws + L.k_scale);
+  float* km = (float*)(ws + L.k_mean);
+  uint32_t *lib_launch = nullptr, *lib_sticky = nullptr;
+  ar::library_status_words(&lib_launch, &lib_sticky);  // an expiry also shows in ar_attn_last_status(NULL, ..)
   ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
   // the status word is the one part of the shared scratch that must start at zero; both kernels report to it
   p.status = (uint32_t*)ws;
+  p.sticky = lib_sticky;
   if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
   int launches = 0;
   if (ar::launch_sage_prologue(p, stream, &launches) != cudaSuccess) return AR_ERR_CUDA;
   const void* v16 = v;
   if (dtype == AR_DTYPE_F32) {
-    if (ar::launch_f32_to_bf16((const float*)v, ws + o_v16, B * Hkv * S * D, stream) != cudaSuccess) return AR_ERR_CUDA;
+    if (ar::launch_f32_to_bf16((const float*)v, ws + L.v16, B * Hkv * S * D, stream) != cudaSuccess) return AR_ERR_CUDA;
     launches++;
-    v16 = ws + o_v16;
+    v16 = ws + L.v16;
   }
   ar::TcArgs a;
   memset(&a, 0, sizeof(a));
@@ -130,6 +123,7 @@ extern "C" int ar_sage_forward_static(int dtype, const void* q, const void* k, c
   a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
   a.causal = causal ? 1 : 0;
   a.status = (uint32_t*)ws;
+  a.sticky = lib_sticky;
   if (!tile_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
       !tile_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
       !tile_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))

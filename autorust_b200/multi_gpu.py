@@ -2,8 +2,9 @@
 
 Attention over disjoint (batch, head) pairs is independent, so the flattened batch x kv-head axis is
 cut into `world` contiguous ranges (GQA groups stay whole, K/V are never replicated), each rank runs
-the forward on its slab, and the output slabs are all-gathered with NCCL through libar_gather.so
-(include/ar_attn_gather.h).  The reference has no multi-device code (CURRENT_STATE.md:64,469).
+the forward on its slab, and the output slabs are gathered on every rank through libar_gather.so
+(include/ar_attn_gather.h): stored into the peers' mapped buffers by the attention kernel itself (fused), pushed by the
+copy engines, or all-gathered by NCCL.  The reference has no multi-device code (CURRENT_STATE.md:64,469).
 """
 from __future__ import annotations
 
@@ -77,6 +78,8 @@ def load() -> ctypes.CDLL:
     L.ar_gather_p2p_open.argtypes = [p, ctypes.c_size_t]
     L.ar_gather_p2p_buffer.argtypes = [p]
     L.ar_gather_p2p_buffer.restype = p
+    L.ar_gather_p2p_peer.argtypes = [p, ci]
+    L.ar_gather_p2p_peer.restype = p
     L.ar_gather_p2p_push.argtypes = [p, ctypes.c_size_t, ctypes.c_size_t, p]
     L.ar_gather_p2p_fence.argtypes = [p, p]
     L.ar_gather_p2p_close.argtypes = [p]
@@ -149,6 +152,23 @@ class Gather:
 
         self._p2p = torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
         return self._p2p.view(dtype).view(*shape)
+
+    def p2p_replicas(self, part) -> list[int]:
+        """Addresses, in this process, of the place of `part` (a piece of the tensor p2p_open returned) in every
+        PEER's buffer: what the attention kernel takes as `replicas` to store its output rows there itself (the
+        fused gather).  Nothing is ever read through them."""
+        off = part.data_ptr() - self._p2p.data_ptr()
+        if off < 0 or off + part.numel() * part.element_size() > self._p2p.numel():
+            raise ValueError("p2p_replicas: the piece lies outside the gather buffer")
+        out = []
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            base = load().ar_gather_p2p_peer(self._h, r)
+            if not base:
+                raise RuntimeError("ar_gather_p2p_peer: the buffers are not open")
+            out.append(int(base) + off)
+        return out
 
     def p2p_push(self, part, stream=None) -> None:
         """Queues the copy of `part` (a contiguous piece of the tensor p2p_open returned) to every peer."""

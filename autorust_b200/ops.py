@@ -64,12 +64,22 @@ def supported(mode, q: torch.Tensor, k: torch.Tensor, causal=False, has_mask=Fal
                                                   int(causal), int(has_mask)))
 
 
+def _replica_array(replicas):
+    """Device addresses (ints) of the further output buffers as a C array of void*."""
+    if not replicas:
+        return None, 0
+    arr = (ctypes.c_void_p * len(replicas))(*[int(r) for r in replicas])
+    return arr, len(replicas)
+
+
 def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None = None,
                  causal: bool = False, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                 stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+                 stream: torch.cuda.Stream | None = None, replicas=None) -> torch.Tensor:
     """o = softmax(q k^T / sqrt(D) + mask) v through ar_attn_forward, asynchronously on `stream`
     (default: torch's current stream).  `workspace` is a uint8 CUDA tensor of at least
-    workspace_bytes(); one is allocated when the mode needs it and none is given."""
+    workspace_bytes(); one is allocated when the mode needs it and none is given.
+    `replicas`: device addresses of further buffers (e.g. peers' buffers mapped into this process) that receive the
+    same bf16 output rows at the same offsets (ar_attn_forward_replicated)."""
     L = _abi.load()
     _check_qkv(q, k, v)
     m = mode_code(mode)
@@ -83,13 +93,17 @@ def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
     need = int(L.ar_attn_workspace_bytes(m, _dtype_code(q), B, Hq, Hkv, S, D))
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    reps, nrep = _replica_array(replicas)
     with torch.cuda.device(q.device):
         s = stream if stream is not None else torch.cuda.current_stream()
-        rc = L.ar_attn_forward(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                               mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal),
-                               workspace.data_ptr() if workspace is not None else None,
-                               workspace.numel() * workspace.element_size() if workspace is not None else 0,
-                               s.cuda_stream)
+        tail = (mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal),
+                workspace.data_ptr() if workspace is not None else None,
+                workspace.numel() * workspace.element_size() if workspace is not None else 0, s.cuda_stream)
+        if nrep:
+            rc = L.ar_attn_forward_replicated(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                              reps, nrep, *tail)
+        else:
+            rc = L.ar_attn_forward(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), *tail)
     _abi.check(rc, "ar_attn_forward")
     # keep the scratch alive until the stream has consumed it
     if workspace is not None:
@@ -205,7 +219,7 @@ def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=
 
 
 def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None, causal=False, stream=None,
-                                out_dtype=torch.bfloat16):
+                                out_dtype=torch.bfloat16, replicas=None):
     """The Sage attention kernel alone, on the tensors sage_quantize returned (v must be bf16); uint8 q8 / k8
     (the FP8 prologue's output) select the FP8 kernel."""
     L = _abi.load()
@@ -227,15 +241,25 @@ def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None
         _check_dense("out", out, (B, Hq, S, D), out.dtype, dev)
     with torch.cuda.device(q8.device):
         s = stream if stream is not None else torch.cuda.current_stream()
-        fn = L.ar_sage_attention_prequantized_fp8 if q8.dtype == torch.uint8 else L.ar_sage_attention_prequantized
-        rc = fn(q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v.data_ptr(), out.data_ptr(),
-                _dtype_code(out), mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal), None,
-                s.cuda_stream)
+        reps, nrep = _replica_array(replicas)
+        if nrep:
+            if q8.dtype == torch.uint8 or out.dtype != torch.bfloat16:
+                raise TypeError("replicated output: INT8 operands and a bfloat16 output")
+            rc = L.ar_sage_attention_prequantized_replicated(
+                q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v.data_ptr(), out.data_ptr(), reps,
+                nrep, mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal), None, s.cuda_stream)
+        else:
+            fn = L.ar_sage_attention_prequantized_fp8 if q8.dtype == torch.uint8 else L.ar_sage_attention_prequantized
+            rc = fn(q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v.data_ptr(), out.data_ptr(),
+                    _dtype_code(out), mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal), None,
+                    s.cuda_stream)
     _abi.check(rc, "ar_sage_attention_prequantized")
     return out
 
 
 def last_status(workspace: torch.Tensor | None = None) -> int:
+    """Synchronises the current stream and reads a status word: a workspace's (its last launch), or with None the
+    library's accumulator over every launch since it was last read (reading clears it)."""
     L = _abi.load()
     return int(L.ar_attn_last_status(workspace.data_ptr() if workspace is not None else None,
                                      torch.cuda.current_stream().cuda_stream))

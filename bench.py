@@ -22,6 +22,7 @@ over the N ranks, strong scaling, with and without the output gather) at every N
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -320,7 +321,7 @@ def long_context_slab(torch, device, pair_begin: int, pair_end: int):
     return q, k, v
 
 
-def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=True, steps=3) -> dict:
+def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=True, fused=True, steps=3) -> dict:
     """Benchmark configuration 5: ONE global tensor B=16, H=64, S=16384, D=128, causal Sage, cut over the ranks
     along the flattened (batch, head) axis (1024 pairs -> 1024 / N per rank, strong scaling); every rank ends up
     with the whole bf16 output.  The inputs of pair p depend on p alone (a generator seeded per group of 8 pairs),
@@ -354,13 +355,22 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
             gather.p2p_close()
     if not p2p:
         full = torch.empty((world, n_local, S, D), dtype=torch.bfloat16, device=device)
-    npieces = 8 if p2p else 1
+    fused = fused and p2p
+    npieces = 8 if (p2p and not fused) else 1
     per = n_local // npieces
 
-    def compute(h0, h1):
-        rc = L.ar_sage_attention_prequantized(q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(),
-                                              ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(), full[rank, h0:h1].data_ptr(),
-                                              _abi.DTYPE_BF16, None, 1, h1 - h0, h1 - h0, S, D, 1, None, stream.cuda_stream)
+    def compute(h0, h1, replicate=False):
+        if replicate:
+            reps = gather.p2p_replicas(full[rank, h0:h1])
+            arr = (ctypes.c_void_p * len(reps))(*reps)
+            rc = L.ar_sage_attention_prequantized_replicated(
+                q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(), ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(),
+                full[rank, h0:h1].data_ptr(), arr, len(reps), None, 1, h1 - h0, h1 - h0, S, D, 1, None, stream.cuda_stream)
+        else:
+            rc = L.ar_sage_attention_prequantized(q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(),
+                                                  ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(), full[rank, h0:h1].data_ptr(),
+                                                  _abi.DTYPE_BF16, None, 1, h1 - h0, h1 - h0, S, D, 1, None,
+                                                  stream.cuda_stream)
         _abi.check(rc, "ar_sage_attention_prequantized")
 
     def step(with_gather: bool):
@@ -369,13 +379,15 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
         _abi.check(rc, "ar_sage_quantize")
         for i in range(npieces):
             h0, h1 = i * per, (i + 1) * per if i + 1 < npieces else n_local
-            compute(h0, h1)
-            if with_gather and p2p:
+            compute(h0, h1, replicate=with_gather and fused)
+            if with_gather and p2p and not fused:
                 done = torch.cuda.Event()
                 done.record(stream)
                 comm_stream.wait_event(done)
                 gather.p2p_push(full[rank, h0:h1], comm_stream)
-        if with_gather and p2p:
+        if with_gather and fused:
+            gather.p2p_fence(stream)
+        elif with_gather and p2p:
             gather.p2p_fence(comm_stream)
             stream.wait_stream(comm_stream)
         elif with_gather and world > 1:
@@ -417,7 +429,8 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
            "ms_per_step_excluding_gather": ms_compute, "tops_excluding_gather": ops / (ms_compute * 1e-3) / 1e12,
            "ms_per_step_including_gather": ms_total, "tops_including_gather": ops / (ms_total * 1e-3) / 1e12,
            "gather_bytes_received_per_rank": (world - 1) * n_local * S * D * 2,
-           "gather": ("peer-to-peer copies on the copy engines, 8 pieces under the following pieces' kernels" if p2p
+           "gather": ("stored into every rank's buffer by the attention kernel's epilogue" if fused else
+                      "peer-to-peer copies on the copy engines, 8 pieces under the following pieces' kernels" if p2p
                       else "NCCL all-gather in place after the kernel") if world > 1 else None,
            "gather_verified": bool(ok) if world > 1 else None, "output_checksum": checksum,
            "timing": "CUDA events on the launching stream, max over ranks; flops 4*B*H*S^2*D/2"}
@@ -458,7 +471,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1:
         from autorust_b200 import multi_gpu
         gather = multi_gpu.Gather(rank, world, local_rank)  # NCCL communicator of libar_gather.so
-        if args.gather == "p2p":
+        if args.gather in ("fused", "p2p"):
             # copy-engine gather: this rank's outputs land in gathered[rank] and are pushed to the peers piece by piece.
             # Every rank has to have its peers mapped; if one could not, all of them take the NCCL form.
             try:
@@ -474,8 +487,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device)
     # N > 1, copy-engine gather: pieces of the flattened (batch, head) axis, each a whole number of waves of CTAs
     # as far as possible, with a short last piece so that little is left to push when the step's last kernel ends.
+    fused = p2p and args.gather == "fused"
     pieces = []
-    if p2p:
+    if p2p and not fused:
         import math
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         ctas_per_head = (S + 255) // 256                      # one CTA per pair of 128-row query tiles
@@ -527,12 +541,34 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             e1.record(stream)
             kernel_events.append((e0, e1, (h1 - h0) / H))
 
+    def attend_fused(record):
+        """The attention kernel over the whole batch; its epilogue stores every output row into this rank's gather
+        buffer and into the same place of every peer's."""
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        reps = gather.p2p_replicas(gathered[rank])
+        arr = (ctypes.c_void_p * len(reps))(*reps)
+        rc = L.ar_sage_attention_prequantized_replicated(q8.data_ptr(), k8.data_ptr(), qs.data_ptr(), ks.data_ptr(),
+                                                         v.data_ptr(), gathered[rank].data_ptr(), arr, len(reps), None,
+                                                         B, H, H, S, D, int(w["causal"]), None, stream.cuda_stream)
+        _abi.check(rc, "ar_sage_attention_prequantized_replicated")
+        if record:
+            e1.record(stream)
+            kernel_events.append((e0, e1, B))
+
     def step(record=False):
         """Prologue + attention over this rank's batch (the two C-ABI calls ar_attn_forward makes for
         the Sage mode, issued apart so the attention kernel can be bracketed by events)."""
         if world == 1:
             quantise(0, B)
             attend(0, B, record)
+            return
+        if fused:
+            quantise(0, B)
+            attend_fused(record)
+            gather.p2p_fence(stream)
             return
         if p2p:
             quantise(0, B)  # the prologue once for the whole batch, then the attention kernel piece by piece
@@ -671,7 +707,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         gather.p2p_close()
     long_context = None
     if not args.no_long_context:
-        long_context = long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=p2p)
+        long_context = long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=p2p, fused=fused)
 
     if rank == 0:
         line = {
@@ -680,10 +716,12 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
             "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (benchmark configuration 3)",
                        **w, "global_batch": B * world, "partition": ("one batch of B per rank (independent (batch, head) pairs, no reduction); bf16 "
-                       "outputs gathered on every rank " + ("piece by piece (37, 37, 37, 9, 8 heads: whole waves of CTAs, "
-                       "short tail) under the next piece's kernel, by peer-to-peer copies on the copy engines (CUDA IPC "
-                       "over NVLink) closed by a 4-byte NCCL all-reduce" if p2p else "per batch element under the next "
-                       "element's kernels, by NCCL all-gather"))
+                       "outputs gathered on every rank " + ("by the attention kernel itself: its epilogue stores every row "
+                       "into the same place of every rank's buffer (peers mapped by CUDA IPC over NVLink; plain stores), "
+                       "closed by a 4-byte NCCL all-reduce" if fused else "piece by piece (37, 37, 37, 9, 8 heads: whole "
+                       "waves of CTAs, short tail) under the next piece's kernel, by peer-to-peer copies on the copy engines "
+                       "(CUDA IPC over NVLink) closed by a 4-byte NCCL all-reduce" if p2p else "per batch element under the "
+                       "next element's kernels, by NCCL all-gather"))
                        if world > 1 else "single GPU",
                        "l2": "inputs (805 MB) exceed L2 (126 MB); no flush needed",
                        "timing": "CUDA events on the launching stream, max over ranks"},
@@ -706,8 +744,9 @@ def main() -> None:
     ap.add_argument("--no-vit", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the bf16_fwd and config2 legs")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=16 H=64 S=16384 causal leg")
-    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
-                    help="N > 1: how the output slabs reach the other ranks (copy engines, or NCCL's all-gather kernels)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "p2p", "nccl"],
+                    help="N > 1: how the output slabs reach the other ranks (stored by the attention kernel's epilogue, "
+                         "pushed by the copy engines, or NCCL's all-gather kernels)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

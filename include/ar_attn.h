@@ -94,6 +94,19 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
                     int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
                     size_t workspace_bytes, void* cu_stream);
 
+/* ar_attn_forward whose bf16 output rows are also stored, at the same offsets, into up to 7 further buffers
+ * (`replicas`, device pointers, 16-byte aligned): buffers of other GPUs of the box that the caller mapped into this
+ * process (CUDA IPC / peer access).  The kernel's epilogue writes every finished 128-byte run of a row to `o` and to
+ * each replica with plain stores -- nothing is read from a replica, no copy engine or second kernel is involved --
+ * so that head-parallel ranks assemble the whole output on every GPU while they compute (include/ar_attn_gather.h
+ * maps the buffers and provides the fence that closes a round).  The reference has no multi-device code
+ * (CURRENT_STATE.md:64,469; src/runtime/ops_cuda.rs:1162-1169): this call has no counterpart there.
+ * AR_MODE_BF16, AR_MODE_SAGE_INT8 and AR_MODE_SAGE_FP8 with dtype AR_DTYPE_BF16; n_replicas = 0 is ar_attn_forward. */
+int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
+                               void* const* replicas, int n_replicas, const float* mask, int64_t B, int64_t Hq,
+                               int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace, size_t workspace_bytes,
+                               void* cu_stream);
+
 /* ar_attn_forward on tensors that are views: element (b, h, s, d) of q lies at
  * q + b * q_strides[0] + h * q_strides[1] + s * q_strides[2] + d (strides in elements, d contiguous), likewise k, v
  * and o.  This is how the caller of the operator holds them: the projections write [B, S, H, D] (or one fused
@@ -157,6 +170,13 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
                                    void* cu_stream);
 
+/* ar_sage_attention_prequantized with a bf16 output that is also stored into `replicas` (see
+ * ar_attn_forward_replicated). */
+int ar_sage_attention_prequantized_replicated(const int8_t* q8, const int8_t* k8, const float* q_scale,
+                                              const float* k_scale, const void* v_bf16, void* o, void* const* replicas,
+                                              int n_replicas, const float* mask, int64_t B, int64_t Hq, int64_t Hkv,
+                                              int64_t S, int64_t D, int causal, void* status_word, void* cu_stream);
+
 /* The FP8 attention kernel alone, on tensors ar_sage_quantize_fp8 produced: E4M3 QK^T with f32 accumulation
  * (`ar_mma_qk` under AR_FP8, src/runtime/cuda_flash_sage.rs:140-160), otherwise as above. */
 int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, const float* q_scale,
@@ -178,15 +198,21 @@ int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, con
  * capture.  All calls on a device share the array and it keeps the previous call's contents (the status
  * word is cleared per call, the rest is rewritten before it is read): calls that overlap on one GPU
  * race -- order them on a stream, or use ar_attn_forward with separate workspaces.
- * After the stream is synchronised, ar_attn_last_status cannot see this call's status word; a launch that
- * did not finish shows up as wrong output.  dtype, pointers, shapes, mask and causal as ar_attn_forward. */
+ * A bounded wait that ran out inside this call is reported by ar_attn_last_status(NULL, stream), like every other
+ * launch of the library.  The array is materialised on a device by the first call there (CUDA loads the library's
+ * device code lazily): that call may fail with AR_ERR_CUDA when the device's memory has already been given away,
+ * so make it at start-up, before stream capture and before another allocator takes the GPU.
+ * dtype, pointers, shapes, mask and causal as ar_attn_forward. */
 int ar_sage_forward_static(int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* cu_stream);
 
-/* Reads the device status word of a workspace after synchronising `cu_stream`: AR_OK, or
- * AR_ERR_DEVICE_WAIT when a bounded wait expired inside a kernel (the launch then returned
- * without finishing its tile).  Stands where the reference has only `cuStreamSynchronize`'s
- * error (src/runtime/ops_cuda.rs:1013-1016). */
+/* Synchronises `cu_stream` and reads a device status word: AR_OK, or AR_ERR_DEVICE_WAIT when a bounded wait
+ * expired inside a kernel (the launch then returned without finishing its tile; later CTAs of that launch leave at
+ * once).  Stands where the reference has only `cuStreamSynchronize`'s error (src/runtime/ops_cuda.rs:1013-1016).
+ * workspace != NULL (a workspace, or the word given as `status_word`): the status of the LAST launch that used it --
+ * every launch clears its word first.  workspace == NULL: the library's accumulator on the current device, into
+ * which every expiry of every launch is OR-ed as well; reading it clears it, so one call after a batch of launches
+ * covers all of them. */
 int ar_attn_last_status(void* workspace, void* cu_stream);
 
 /* Number of launches per kernel family since the library was loaded: the

@@ -39,13 +39,24 @@ int ar_gather_allgather(void* comm, void* o_full, int64_t elems_per_rank, int dt
 int ar_gather_allgather_into(void* comm, const void* send, void* recv, int64_t elems_per_rank, int dtype,
                              void* cu_stream);
 
-/* ---- The same gather on the copy engines.
+/* ---- The same gather without NCCL's kernels.
  * NCCL's all-gather kernels take SMs, and the attention kernel fills an SM with each CTA, so a gather that runs
- * beside the next chunk's attention costs that chunk the SMs NCCL holds.  This form takes none: every rank owns one
- * buffer of the gathered size, the buffers are mapped into each other's address spaces once (CUDA IPC over the
- * NVLink peers), the attention kernel writes its slab straight into the local buffer, and a push is world - 1
- * peer-to-peer cudaMemcpyAsync calls.  NCCL remains the control plane: it ships the IPC handles and closes a
- * round of pushes (a 4-byte all-reduce queued behind them). */
+ * beside the next chunk's attention costs that chunk the SMs NCCL holds.  Here every rank owns one buffer of the
+ * gathered size and the buffers are mapped into each other's address spaces once (CUDA IPC over the NVLink peers).
+ * Two ways to fill them:
+ *   fused       the attention kernel itself stores every finished output row into the local buffer AND into each
+ *               peer's (ar_attn_forward_replicated / ar_sage_attention_prequantized_replicated of ar_attn.h, given
+ *               ar_gather_p2p_peer's addresses): the slab leaves over the whole length of the kernel and nothing is
+ *               left to move when it ends;
+ *   copy engine the kernel writes its slab into the local buffer and ar_gather_p2p_push queues world - 1
+ *               peer-to-peer cudaMemcpyAsync calls behind it.
+ * NCCL remains the control plane: it ships the IPC handles and closes a round (ar_gather_p2p_fence: a 4-byte
+ * all-reduce queued behind the stores or copies).
+ * Reuse of the buffers: a rank may start the NEXT round's stores into its peers as soon as its own fence has passed,
+ * which says nothing about whether the peers are done READING the previous round.  A consumer that reads its
+ * buffer on the device therefore calls ar_gather_p2p_fence once more after its reads (the all-reduce is a barrier
+ * across the ranks' streams) before anyone produces into the buffers again, or alternates between two opened
+ * sets. */
 
 /* Allocates this rank's buffer of `bytes` (the same on every rank) and opens the peers' buffers.  Collective:
  * every rank calls it, with its device current.  0 on success. */
@@ -54,14 +65,18 @@ int ar_gather_p2p_open(void* comm, size_t bytes);
 /* This rank's buffer (device memory owned by the library until ar_gather_p2p_close), or NULL. */
 void* ar_gather_p2p_buffer(void* comm);
 
+/* The address, in this process, of rank `rank`'s buffer (this rank's own for rank == its rank): what the fused form
+ * hands to the attention kernel as a replica, plus the slab's offset.  Only ever stored to.  NULL when not open. */
+void* ar_gather_p2p_peer(void* comm, int rank);
+
 /* Copies [offset, offset + bytes) of the local buffer to the same range of every peer's buffer, asynchronously,
  * after whatever `cu_stream` holds at the time of the call (the kernel that produced the range).  The copies run on
- * streams of the library's own, one peer after the other round-robin over them, so that several copy engines work at
- * once; ar_gather_p2p_fence joins them back into `cu_stream`. */
+ * a stream of the library's own, one peer after the other (measured faster on eight GPUs than several peers at
+ * once); ar_gather_p2p_fence joins them back into `cu_stream`. */
 int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream);
 
-/* Queues on `cu_stream` the point after which every push that any rank queued before ITS fence has landed in
- * this rank's buffer.  Collective. */
+/* Queues on `cu_stream` the point after which everything that any rank queued before ITS fence -- pushes, or
+ * kernels that store into the peers -- has landed in this rank's buffer.  Collective. */
 int ar_gather_p2p_fence(void* comm, void* cu_stream);
 
 /* Unmaps the peers' buffers and frees the local one.  Collective in effect: no peer may still push. */

@@ -1,6 +1,6 @@
 """Head-parallel sharding: partition arithmetic, the N > 1 path on CPU ranks (gloo, world_size 2), a rank
-that never joins (host-side failure, no GPU involved), and -- on a box with two GPUs -- the NCCL gather
-against the single-GPU result."""
+that never joins (host-side failure, no GPU involved), and -- on a box with two GPUs -- the three forms of the
+output gather (NCCL, copy engines, stored by the attention kernel itself) against the single-GPU result."""
 from __future__ import annotations
 
 import datetime
@@ -94,7 +94,6 @@ def _gpu_rank(rank, world, port, seed, result):
     import torch.distributed as dist
     from autorust_b200 import ops
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    os.environ["AR_GATHER_STREAMS"] = "3"  # the copy-engine gather cut over several streams (its default is one)
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             timeout=datetime.timedelta(seconds=120))
@@ -132,6 +131,25 @@ def _gpu_rank(rank, world, port, seed, result):
     ref_all = ops.attn_forward("bf16", q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
     torch.cuda.synchronize()
     p2p_ok = torch.equal(buf.reshape(B * H, S, D).view(torch.int16), ref_all.reshape(B * H, S, D).view(torch.int16))
+    # the fused form: the kernel's epilogue stores this rank's rows into its own buffer and into the peer's
+    dist.barrier()
+    buf.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    fused_ok = True
+    for mode in ("bf16", "sage"):
+        mine = buf[rank].view(1, hq_local, S, D)
+        ops.attn_forward(mode, q[sh.q_begin:sh.q_end].view(1, hq_local, S, D), k[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D),
+                         v[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D), None, True, out=mine,
+                         replicas=gather.p2p_replicas(buf[rank]))
+        gather.p2p_fence()
+        torch.cuda.synchronize()
+        ref_m = ops.attn_forward(mode, q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
+        torch.cuda.synchronize()
+        fused_ok = fused_ok and torch.equal(buf.reshape(B * H, S, D).view(torch.int16),
+                                            ref_m.reshape(B * H, S, D).view(torch.int16))
+        dist.barrier()  # nobody stores the next mode's rows while a peer still compares
+    p2p_ok = p2p_ok and fused_ok
     flags = [None] * world
     dist.all_gather_object(flags, bool(p2p_ok))
     if rank == 0:

@@ -5,7 +5,8 @@ allocator, paths that cannot take cudaMalloc's device-wide synchronisation).  It
 
 Checked here, through the C ABI: two calls in a row on different inputs each reproduce what
 ar_attn_forward (Sage mode, caller workspace) returns for the same inputs, and a problem that does not
-fit the built-in scratch is refused with AR_ERR_TOO_LARGE before anything is launched.  The file name
+fit the built-in scratch is refused with AR_ERR_TOO_LARGE before anything is launched; from the second call on,
+the device's free memory is the same before and after a call.  The file name
 sorts last so that a run stopping at the first failure has already covered every other test.
 """
 from __future__ import annotations
@@ -24,13 +25,18 @@ def _inputs(torch, seed, B, H, Hkv, S, D, dtype):
     return q, k, v
 
 
-def _static_forward(L, abi, torch, q, k, v, causal):
+def _static_forward(L, abi, torch, q, k, v, causal, check_memory=False):
     B, H, S, D = q.shape
     out = torch.empty_like(q)
     dt = abi.DTYPE_BF16 if q.dtype == torch.bfloat16 else abi.DTYPE_F32
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = L.ar_sage_forward_static(dt, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None, B, H,
                                   k.shape[1], S, D, int(causal), torch.cuda.current_stream().cuda_stream)
     assert rc == abi.AR_OK, abi.strerror(rc)
+    torch.cuda.synchronize()
+    if check_memory:  # not the first call on the device, which materialises the library's array
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
     return out
 
 
@@ -41,9 +47,9 @@ def test_static_scratch_entry_matches_workspace_entry_twice(attn_lib):
         pytest.fail("needs a CUDA device")
     L = attn_lib
     cases = [(11, 1, 4, 2, 1000, 128, torch.bfloat16, True), (12, 2, 2, 2, 777, 128, torch.float32, False)]
-    for seed, B, H, Hkv, S, D, dtype, causal in cases:  # two calls in a row share the same scratch
+    for i, (seed, B, H, Hkv, S, D, dtype, causal) in enumerate(cases):  # two calls in a row share the same scratch
         q, k, v = _inputs(torch, seed, B, H, Hkv, S, D, dtype)
-        got = _static_forward(L, _abi, torch, q, k, v, causal)
+        got = _static_forward(L, _abi, torch, q, k, v, causal, check_memory=i > 0)
         want = ops.attn_forward("sage", q, k, v, None, causal)
         torch.cuda.synchronize()
         assert not torch.isnan(got.float()).any()
@@ -54,7 +60,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice(attn_lib):
     # and once more on the first inputs: the scratch still holds the second call's data
     seed, B, H, Hkv, S, D, dtype, causal = cases[0]
     q, k, v = _inputs(torch, seed, B, H, Hkv, S, D, dtype)
-    again = _static_forward(L, _abi, torch, q, k, v, causal)
+    again = _static_forward(L, _abi, torch, q, k, v, causal, check_memory=True)
     want = ops.attn_forward("sage", q, k, v, None, causal)
     torch.cuda.synchronize()
     assert torch.equal(again, want)
