@@ -14,9 +14,11 @@ the reference's only head size) to pin the oracle's rounding models and to compa
 reference's on the same inputs.  TEST INFRASTRUCTURE ONLY.
 
 Usage: python oracle/build_ref.py [path/to/autorust]
+(default: $AUTORUST_REFERENCE_DIR, else the directory `reference` beside this repository)
 """
 from __future__ import annotations
 
+import os
 import re
 import shutil
 import subprocess
@@ -57,7 +59,7 @@ def extract(rust_text: str) -> str:
 
 
 def main() -> int:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AUTORUST_REFERENCE_DIR") or HERE.parent.parent / "reference")
     src_dir = ref / "src" / "runtime"
     if not src_dir.is_dir():
         print(f"reference tree not found at {ref}: nothing built")

@@ -1,7 +1,7 @@
 """Runs one attention configuration a few times and prints its device time: the small, self-ending
 case to put under a profiler (or to time a shape that is not the benchmark's).
 
-    python -m autorust_b200.profile_case --mode sage --B 1 --H 32 --S 8192 --D 128 --iters 3
+    python profile_case.py --mode sage --B 1 --H 32 --S 8192 --D 128 --iters 3
 """
 from __future__ import annotations
 
@@ -9,7 +9,11 @@ import argparse
 
 import torch
 
-from . import ops
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+from autorust_b200 import ops  # noqa: E402
 
 
 def main() -> None:

@@ -10,6 +10,7 @@ Usage:  python tests/golden/make_sdpa_golden.py [path/to/autorust]
 from __future__ import annotations
 
 import json
+import os
 import re
 import sys
 from pathlib import Path
@@ -33,7 +34,8 @@ def parse(text: str) -> list[dict]:
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = Path(sys.argv[1] if len(sys.argv) > 1 else
+               os.environ.get("AUTORUST_REFERENCE_DIR") or Path(__file__).resolve().parents[3] / "reference")
     text = (ref / "tests" / "attention_golden.rs").read_text()
     cases = parse(text)
     assert len(cases) == 6, f"expected 6 golden cases, found {len(cases)}"
