@@ -40,7 +40,7 @@ bool device_ok() {
 bool make_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t B, int64_t H, int64_t S,
               int64_t D) {
   int tm = 0;
-  return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, 128 / esize, 128, &tm);
+  return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, (int)(128 / esize < D ? 128 / esize : D), 128, &tm);
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }

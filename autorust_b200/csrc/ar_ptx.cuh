@@ -216,6 +216,11 @@ __host__ __device__ constexpr uint64_t make_sdesc_sw128(uint32_t smem_addr, uint
   return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
          ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
 }
+// The same with the 64-byte swizzle (layout type 4): K-major rows of 64 bytes, 8-row groups 512 bytes apart.
+__host__ __device__ constexpr uint64_t make_sdesc_sw64(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (4ull << 61);
+}
 
 // TMEM address: lane in bits [16,32), 32-bit column in bits [0,16).
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint32_t col) {

@@ -46,6 +46,10 @@ using namespace arptx;
 __device__ int g_test_skip_k_tile = -1;
 #endif
 
+// Up to this length a CTA of the D = 64 bf16 kernel takes one query tile instead of two (measured: S=100 22.9 against
+// 33.8 us, S=197 46.5 against 48.7 us for 768 heads; from S=512 on the two-tile form is ahead, 37.2 against 37.8 us).
+constexpr int SHORT_SEQUENCE = 256;
+
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per step
 constexpr int NPART = 2;  // P of a step is handed to the MMA warp in two halves of 64 keys
@@ -55,12 +59,23 @@ constexpr float LOG2E = 1.4426950408889634f;
 // masked row, as in the reference).
 constexpr float NEG = -1e30f * LOG2E;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
-constexpr int NUM_THREADS = 384;    // 3 warpgroups: softmax 0, softmax 1, {TMA producer, MMA issuer, 2 idle warps}
-constexpr int SOFTMAX_REGS = 216;   // register budget of the softmax warps after setmaxnreg
-constexpr int SERVICE_REGS = 72;    // ... and of the third warpgroup
-// setmaxnreg moves registers inside the pool the CTA was launched with (168 per thread for 384 threads);
-// an increase that the pool cannot cover waits forever.
-static_assert(8 * 32 * SOFTMAX_REGS + 4 * 32 * SERVICE_REGS <= 168 * NUM_THREADS, "register pool of the CTA");
+// Shape of a CTA.  TILES = 2: two query tiles, 384 threads -- softmax warpgroup 0, softmax warpgroup 1,
+// {TMA producer, MMA issuer, 2 idle warps}; one CTA per SM (all 512 TMEM columns).  TILES = 1: one query tile,
+// 256 threads, 256 TMEM columns and at most half of the shared memory and registers, so that two CTAs share an SM:
+// the form for short sequences, where a CTA is a chain of latencies (loads, two or three key steps, epilogue) with
+// nothing of its own to overlap them with.
+// setmaxnreg moves registers inside the pool the CTA was launched with (168 per thread for 384 threads, 128 per
+// thread for 256 threads at two CTAs per SM); an increase that the pool cannot cover waits forever.
+template <int TILES>
+struct Shape {
+  static constexpr int NUM_THREADS = 128 * TILES + 128;
+  static constexpr int MIN_CTAS = TILES == 1 ? 2 : 1;
+  static constexpr int LAUNCH_REGS = TILES == 1 ? 128 : 168;
+  static constexpr int SOFTMAX_REGS = TILES == 1 ? 208 : 216;  // softmax warps after setmaxnreg
+  static constexpr int SERVICE_REGS = TILES == 1 ? 48 : 72;    // the last warpgroup
+  static_assert(TILES * 4 * 32 * SOFTMAX_REGS + 4 * 32 * SERVICE_REGS <= LAUNCH_REGS * NUM_THREADS, "register pool of the CTA");
+  static_assert(LAUNCH_REGS * NUM_THREADS * MIN_CTAS <= 65536, "register file of the SM");
+};
 
 // One lane of a converged warp (elect.sync).
 __device__ __forceinline__ bool elect_one() {
@@ -263,15 +278,20 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
   l += lsum + lsum_hi;
 }
 
-template <int MODE, int D>
+template <int MODE, int D, int TILES = 2>
 struct Cfg {
   static constexpr bool QUANT = MODE == TC_SAGE || MODE == TC_SAGE_FP8;  // 8-bit Q and K with per-block scales
   static constexpr int QK_ESIZE = QUANT ? 1 : MODE == TC_TF32 ? 4 : 2;
   static constexpr int QK_ROW_BYTES = D * QK_ESIZE;
-  static_assert(QK_ROW_BYTES % 128 == 0, "Q/K rows must fill whole 128-byte swizzle atoms");
-  static constexpr int QK_BOXES = QK_ROW_BYTES / 128;
-  static constexpr int QK_BOX_ELEMS = 128 / QK_ESIZE;
+  // Q and K rows lie in shared memory as boxes of 128 bytes with the 128-byte swizzle, or -- 8-bit rows of D = 64
+  // -- as one box of 64 bytes with the 64-byte swizzle
+  static constexpr int QK_BOX_BYTES = QK_ROW_BYTES >= 128 ? 128 : 64;
+  static_assert(QK_ROW_BYTES % QK_BOX_BYTES == 0, "Q/K rows must fill whole swizzle atoms");
+  static constexpr int QK_BOXES = QK_ROW_BYTES / QK_BOX_BYTES;
+  static constexpr int QK_BOX_ELEMS = QK_BOX_BYTES / QK_ESIZE;
   static constexpr int QK_TILE_BYTES = BM * QK_ROW_BYTES;
+  // a Q tile's place also stages the output rows of the replicated epilogue: 128 rows x 128 bytes at least
+  static constexpr int Q_TILE_STRIDE = QK_TILE_BYTES >= BM * 128 ? QK_TILE_BYTES : BM * 128;
   static constexpr int QK_KSTEPS = QK_ROW_BYTES / 32;  // one MMA consumes 32 bytes of K extent
   // V operand of the PV MMA.  bf16: the row-major [keys, D] tile itself, consumed MN-major (boxes of 64
   // d-columns).  TF32: tcgen05 has no MN-major tf32 operand, so the tile comes from a transposed copy
@@ -281,11 +301,13 @@ struct Cfg {
   static constexpr int V_BOX_BYTES = MODE == TC_TF32 ? D * 128 : BN * 128;
   static constexpr int V_TILE_BYTES = BN * D * V_ESIZE;
   static constexpr int PV_KSTEPS = MODE == TC_TF32 ? BN / 8 : BN / 16;
-  static constexpr int STAGES = (2 * QK_TILE_BYTES + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2;
-  static constexpr int SMEM_TILES = 2 * QK_TILE_BYTES + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
+  static constexpr int STAGES =
+      TILES == 1 ? 2 : ((2 * Q_TILE_STRIDE + 3 * (QK_TILE_BYTES + V_TILE_BYTES) <= 200 * 1024) ? 3 : 2);
+  static constexpr int SMEM_TILES = TILES * Q_TILE_STRIDE + STAGES * (QK_TILE_BYTES + V_TILE_BYTES);
   static constexpr int NUM_BARS = 2 + 4 * STAGES + 4 + 2 * NPART;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static_assert(TILES == 2 || SMEM_BYTES <= 113 * 1024, "two one-tile CTAs must fit an SM");
   static constexpr int QK_KIND = MODE == TC_SAGE ? KIND_I8 : MODE == TC_SAGE_FP8 ? KIND_F8 : MODE == TC_TF32 ? KIND_TF32 : KIND_F16;
   static constexpr uint32_t IDESC_QK = MODE == TC_SAGE       ? make_idesc(2, 1, 1, 0, 0, BM, BN)  // s8 x s8 -> s32
                                        : MODE == TC_SAGE_FP8 ? make_idesc(1, 0, 0, 0, 0, BM, BN)  // e4m3 x e4m3 -> f32
@@ -294,19 +316,21 @@ struct Cfg {
   static constexpr uint32_t IDESC_PV = MODE == TC_TF32 ? make_idesc(1, 2, 2, 0, 0, BM, D) : make_idesc(1, 1, 1, 0, 1, BM, D);
 };
 
-template <int MODE, int D>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int MODE, int D, int TILES>
+__global__ void __launch_bounds__(Shape<TILES>::NUM_THREADS, Shape<TILES>::MIN_CTAS)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
                    int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
                    const OutReplicas reps, uint32_t* status, uint32_t* sticky) {
-  using C = Cfg<MODE, D>;
+  using C = Cfg<MODE, D, TILES>;
   constexpr int ST = C::STAGES;
+  constexpr int W_PROD = 4 * TILES;     // warp that loads
+  constexpr int W_MMA = 4 * TILES + 1;  // warp that issues the MMAs
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + 2 * C::QK_TILE_BYTES;
+  uint8_t* sK = sQ + TILES * C::Q_TILE_STRIDE;
   uint8_t* sV = sK + ST * C::QK_TILE_BYTES;
   uint64_t* bars = (uint64_t*)(sV + ST * C::V_TILE_BYTES);
   uint64_t* q_full = bars;             // [2]
@@ -338,11 +362,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   };
   // causal: heavy (late) query tiles first, so that the last CTAs of the grid are the light ones
   const int qblock = causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int q0 = qblock * (2 * BM);
+  const int q0 = qblock * (TILES * BM);
   const int nkv_all = (N + BN - 1) / BN;
-  int nkv[2];
+  int nkv[2] = {0, 0};
 #pragma unroll
-  for (int t = 0; t < 2; t++) {
+  for (int t = 0; t < TILES; t++) {
     const int row0 = q0 + t * BM;
     nkv[t] = row0 >= N ? 0 : (causal ? min(nkv_all, (row0 + BM - 1) / BN + 1) : nkv_all);
   }
@@ -350,11 +374,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   // Q and one K/V pair per ring stage: nothing to wait for, the stages are empty
   auto issue_q = [&]() {
-    for (int t = 0; t < 2; t++) {
+    for (int t = 0; t < TILES; t++) {
       if (nkv[t] == 0) continue;
       mbar_arrive_expect_tx(&q_full[t], C::QK_TILE_BYTES);
       for (int bx = 0; bx < C::QK_BOXES; bx++)
-        load_tile(sQ + t * C::QK_TILE_BYTES + bx * (BM * 128), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS, q0 + t * BM, h, 0);
+        load_tile(sQ + t * C::Q_TILE_STRIDE + bx * (BM * C::QK_BOX_BYTES), &tm_q, &q_full[t], bx * C::QK_BOX_ELEMS,
+                  q0 + t * BM, h, 0);
     }
   };
   auto issue_k = [&](int j) {
@@ -366,7 +391,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #endif
     mbar_arrive_expect_tx(&k_full[s], C::QK_TILE_BYTES);
     for (int bx = 0; bx < C::QK_BOXES; bx++)
-      load_tile(sK + s * C::QK_TILE_BYTES + bx * (BN * 128), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN, kvh, 1);
+      load_tile(sK + s * C::QK_TILE_BYTES + bx * (BN * C::QK_BOX_BYTES), &tm_k, &k_full[s], bx * C::QK_BOX_ELEMS, j * BN,
+                kvh, 1);
   };
   auto issue_v = [&](int j) {
     const int s = j % ST;
@@ -382,7 +408,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   // The producer thread sets up the barriers and starts the first loads itself, before the CTA meets: the copies
   // are in flight while the TMEM allocation and the barrier complete (a CTA of a short sequence is mostly latency).
   bool lost = false;  // (meaningful in the producer thread only)
-  if (warp == 8 && lane == 0) {
+  if (warp == W_PROD && lane == 0) {
     // A launch whose status word is already set (a wait ran out in an earlier CTA) is lost: this CTA only allocates
     // and frees its TMEM, so that the rest of the grid drains in microseconds instead of one wait budget per wave.
     lost = status != nullptr && (*(volatile uint32_t*)status & 0x80000000u) != 0;
@@ -411,8 +437,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   }
-  if (warp == 9) {
-    tmem_alloc(tmem_slot, 512);
+  if (warp == W_MMA) {
+    tmem_alloc(tmem_slot, 256 * TILES);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -420,8 +446,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after();
   const uint32_t tb = *tmem_slot;
 
-  if (warp >= 8) setmaxnreg_dec<SERVICE_REGS>();
-  if (warp == 8) {
+  if (warp >= W_PROD) setmaxnreg_dec<Shape<TILES>::SERVICE_REGS>();
+  if (warp == W_PROD) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int issued = lost ? 0 : preloaded;
@@ -441,7 +467,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (*abort_flag && !lost) {
         // A wait ran out somewhere in this CTA.  Let the loads this thread started land (bounded)
         // before the CTA's shared memory is handed back.
-        for (int t = 0; t < 2; t++)
+        for (int t = 0; t < TILES; t++)
           if (nkv[t] > 0) mbar_wait_quiet(&q_full[t], 0);
         for (int j = max(0, issued - ST); j < issued; j++) {
           mbar_wait_quiet(&k_full[j % ST], (j / ST) & 1);
@@ -449,7 +475,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == W_MMA) {
     // -------------------------------------------------------------- MMA issuer
     // The whole warp walks the loop, converged, and one elected lane issues the tcgen05 instructions:
     // in a region the compiler sees as divergent every one of them is wrapped in an election and its
@@ -458,7 +484,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     {
       // Descriptor words that never change: the high halves, and the low halves (address >> 4) of the
       // first Q tile, K stage and V stage.  Per instruction only a constant is added to a low word.
-      const uint64_t qk_proto = make_sdesc_sw128(0, 16, 1024);
+      const uint64_t qk_proto = C::QK_BOX_BYTES == 128 ? make_sdesc_sw128(0, 16, 1024) : make_sdesc_sw64(0, 16, 512);
       const uint64_t v_proto = make_sdesc_sw128(0, BN * 128, 1024);
       const uint32_t qk_hi = (uint32_t)(qk_proto >> 32), v_hi = (uint32_t)(v_proto >> 32);
       const uint32_t qk_lo = (uint32_t)qk_proto, v_lo = (uint32_t)v_proto;
@@ -467,17 +493,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const uint32_t v_lo0 = v_lo | (smem_u32(sV) >> 4);
       auto issue_qk = [&](int t, int ks) {
         const uint32_t d = tb + t * 128;
-        const uint32_t qa = q_lo0 + t * (C::QK_TILE_BYTES >> 4);
+        const uint32_t qa = q_lo0 + t * (C::Q_TILE_STRIDE >> 4);
         const uint32_t ka = k_lo0 + ks * (C::QK_TILE_BYTES >> 4);
         if (!elect_one()) return;
 #pragma unroll
         for (int s = 0; s < C::QK_KSTEPS; s++) {
-          const uint32_t off = ((s >> 2) * (BM * 128) + (s & 3) * 32) >> 4;
+          constexpr int KS_PER_BOX = C::QK_BOX_BYTES / 32;  // one instruction consumes 32 bytes of a row
+          const uint32_t off = ((s / KS_PER_BOX) * (BM * C::QK_BOX_BYTES) + (s % KS_PER_BOX) * 32) >> 4;
           mma_ss_lohi<C::QK_KIND>(d, qa + off, qk_hi, ka + off, qk_hi, C::IDESC_QK, s > 0);
         }
       };
       auto issue_pv = [&](int t, int vs, bool acc, int hf) {
-        const uint32_t d = tb + 256 + t * 128;
+        const uint32_t d = tb + TILES * 128 + t * 128;
         const uint32_t a = tb + t * 128;
         const uint32_t va = v_lo0 + vs * (C::V_TILE_BYTES >> 4);
         if (!elect_one()) return;
@@ -494,7 +521,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
       bool ok = true;
       if (nkv_max > 0) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, wctx, 0x20));
-      for (int t = 0; t < 2 && ok; t++) {
+      for (int t = 0; t < TILES && ok; t++) {
         if (nkv[t] == 0) continue;
         ok = __all_sync(0xffffffffu, mbar_wait(&q_full[t], 0, wctx, 0x21));
         if (!ok) break;
@@ -513,7 +540,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           ok = __all_sync(0xffffffffu, mbar_wait(&k_full[s1], ((j + 1) / ST) & 1, wctx, 0x24));
           if (!ok) break;
         }
-        for (int t = 0; t < 2 && ok; t++) {
+        for (int t = 0; t < TILES && ok; t++) {
           if (j >= nkv[t]) continue;
           // P arrives in NPART parts: the first PV MMAs run under the exponentials of the later parts
 #pragma unroll
@@ -536,15 +563,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (j + 1 < nkv_max) commit_one(&k_empty[s1]);
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < W_PROD) {
     // ------------------------------------------------------------ softmax warps
-    setmaxnreg_inc<SOFTMAX_REGS>();
+    setmaxnreg_inc<Shape<TILES>::SOFTMAX_REGS>();
     const int t = warp >> 2;
     const int r = tid & 127;
     const int row = q0 + t * BM + r;
     const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
     const uint32_t tS = tmem_addr(tb, lane_base, t * 128);
-    const uint32_t tO = tmem_addr(tb, lane_base, 256 + t * 128);
+    const uint32_t tO = tmem_addr(tb, lane_base, TILES * 128 + t * 128);
     const float scale_log2 = (1.0f / sqrtf((float)D)) * LOG2E;
     const int nblk = nkv_all;
     float qs = 1.f;
@@ -630,8 +657,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           // QK^T of the tile has completed), 128 rows x 128 bytes per pass of 64 columns, the 16-byte chunk c of row
           // r kept at c ^ (r & 7); each warp reads back only the 32 rows it wrote and stores every run to the local
           // buffer and to each replica (plain stores; nothing is read from a replica).
-          uint8_t* stage = sQ + t * C::QK_TILE_BYTES;
-          static_assert(C::QK_TILE_BYTES >= BM * 128, "staging area of the epilogue");
+          uint8_t* stage = sQ + t * C::Q_TILE_STRIDE;
+          static_assert(C::Q_TILE_STRIDE >= BM * 128, "staging area of the epilogue");
           const int wrow0 = (warp & 3) * 32;
 #pragma unroll 1
           for (int pass = 0; pass < D / 64; pass++) {
@@ -673,13 +700,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tb, 512);
+  if (warp == W_MMA) tmem_dealloc(tb, 256 * TILES);
 }
 
-template <int MODE, int D>
+template <int MODE, int D, int TILES>
 cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
-  using C = Cfg<MODE, D>;
-  auto kern = attn_fwd_tc_kernel<MODE, D>;
+  using C = Cfg<MODE, D, TILES>;
+  auto kern = attn_fwd_tc_kernel<MODE, D, TILES>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -689,10 +716,11 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  dim3 grid((a.S + 2 * BM - 1) / (2 * BM), a.B * a.Hq, 1);
-  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale, a.k_scale, a.S,
-                                                     a.Hq, a.Hkv, a.causal, a.out_f32, a.token_major, a.o_sb, a.o_sh,
-                                                     a.o_ss, a.replicas, a.status, a.sticky);
+  dim3 grid((a.S + TILES * BM - 1) / (TILES * BM), a.B * a.Hq, 1);
+  kern<<<grid, Shape<TILES>::NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale,
+                                                                   a.k_scale, a.S, a.Hq, a.Hkv, a.causal, a.out_f32,
+                                                                   a.token_major, a.o_sb, a.o_sh, a.o_ss, a.replicas,
+                                                                   a.status, a.sticky);
   return cudaGetLastError();
 }
 
@@ -724,24 +752,30 @@ bool make_tile_map(CUtensorMap* m, const void* ptr, int cu_dtype, int esize, lon
                        head_first ? (cuuint32_t)box_rows : 1u, 1u};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   if (token_major_bit) *token_major_bit = head_first ? 1 : 0;
+  // boxes of 128 bytes take the 128-byte swizzle; 64-byte boxes (8-bit rows of D = 64) the 64-byte one
+  const CUtensorMapSwizzle swz = box_inner * esize >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   return enc(m, (CUtensorMapDataType)cu_dtype, 4, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 bool attn_tc_has(int mode, int D) {
   if (mode == TC_BF16) return D == 64 || D == 128;
-  if (mode == TC_SAGE || mode == TC_SAGE_FP8) return D == 128;
+  if (mode == TC_SAGE || mode == TC_SAGE_FP8) return D == 64 || D == 128;
   if (mode == TC_TF32) return D == 64;  // the reference's only head size; two f32 query tiles of D=128 do not fit
   return false;
 }
 
 cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
-  if (a.mode == TC_BF16 && a.D == 128) return launch_one<TC_BF16, 128>(a, stream);
-  if (a.mode == TC_BF16 && a.D == 64) return launch_one<TC_BF16, 64>(a, stream);
-  if (a.mode == TC_SAGE && a.D == 128) return launch_one<TC_SAGE, 128>(a, stream);
-  if (a.mode == TC_SAGE_FP8 && a.D == 128) return launch_one<TC_SAGE_FP8, 128>(a, stream);
-  if (a.mode == TC_TF32 && a.D == 64) return launch_one<TC_TF32, 64>(a, stream);
+  // short sequences at D = 64: one query tile per CTA, two CTAs per SM
+  if (a.mode == TC_BF16 && a.D == 64 && a.S <= SHORT_SEQUENCE) return launch_one<TC_BF16, 64, 1>(a, stream);
+  if (a.mode == TC_BF16 && a.D == 128) return launch_one<TC_BF16, 128, 2>(a, stream);
+  if (a.mode == TC_BF16 && a.D == 64) return launch_one<TC_BF16, 64, 2>(a, stream);
+  if (a.mode == TC_SAGE && a.D == 128) return launch_one<TC_SAGE, 128, 2>(a, stream);
+  if (a.mode == TC_SAGE && a.D == 64) return launch_one<TC_SAGE, 64, 2>(a, stream);
+  if (a.mode == TC_SAGE_FP8 && a.D == 128) return launch_one<TC_SAGE_FP8, 128, 2>(a, stream);
+  if (a.mode == TC_SAGE_FP8 && a.D == 64) return launch_one<TC_SAGE_FP8, 64, 2>(a, stream);
+  if (a.mode == TC_TF32 && a.D == 64) return launch_one<TC_TF32, 64, 2>(a, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -58,7 +58,7 @@ int static_scratch(void** out) {
 
 bool tile_map(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esize, int64_t B, int64_t H, int64_t S,
               int64_t D) {
-  return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, 128 / esize, 128, nullptr);
+  return ar::make_tile_map(m, ptr, (int)dt, esize, B, H, S, D, H * S * D, S * D, D, (int)(128 / esize < D ? 128 / esize : D), 128, nullptr);
 }
 
 }  // namespace

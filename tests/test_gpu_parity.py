@@ -235,6 +235,26 @@ def test_sage_large_scales_take_the_converting_path(ops, oracle_lib, gain, n, ca
     assert max_abs(got, model) < 2e-2 and cosine(got, model) > 0.9999
 
 
+@pytest.mark.parametrize("mode,model", [("sage", 3), ("sage_fp8", 4)])
+@pytest.mark.parametrize("n,causal,hq,hkv", [(1, False, 2, 2), (33, False, 2, 2), (100, True, 2, 2), (197, False, 4, 2),
+                                             (789, False, 2, 2), (1000, True, 4, 2)])
+def test_sage_head_dim_64(ops, oracle_lib, mode, model, n, causal, hq, hkv):
+    """D = 64, the reference's only head size (src/runtime/cuda_flash_sage.rs:33): 64-byte INT8 / E4M3 rows, staged
+    with the 64-byte swizzle.  Against the quantised model with per-block scales, and against exact."""
+    q, k, v = normal_qkv(n, 1, hq, hkv, n, 64, k_offset_sigma=2.0)
+    qb, kb, vb = (oracle_lib.f32_to_bf16(x) for x in (q, k, v))
+    got = oracle_lib.bf16_to_f32(run_bf16(ops, mode, qb, kb, vb, None, causal))
+    want = oracle_lib.bf16_to_f32(oracle_lib.flash(model, qb, kb, vb, None, causal, block=128, smooth=True))
+    assert max_abs(got, want) < 2e-2 and cosine(got, want) > 0.9999
+    exact = oracle_lib.flash(0, oracle_lib.bf16_to_f32(qb), oracle_lib.bf16_to_f32(kb), oracle_lib.bf16_to_f32(vb),
+                             None, causal)
+    assert cosine(got, exact) >= (0.999 if mode == "sage" else 0.995)
+    if mode == "sage":  # the reference test's sawtooth inputs and bound (tests/sage_int8.rs:133-148), f32 tensors
+        qs, ks_, vs = sawtooth_qkv(1, hq, hkv, n, 64)
+        gots = run_f32(ops, "sage", qs, ks_, vs, None, causal)
+        assert max_abs(gots, oracle_lib.flash(3, qs, ks_, vs, None, causal, block=128, smooth=True)) < 2e-3
+
+
 def test_sage_with_mask(ops, oracle_lib):
     q, k, v = sawtooth_qkv(1, 2, 2, 200, 128)
     mask = sawtooth_mask(200)
