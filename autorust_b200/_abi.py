@@ -9,7 +9,7 @@ from pathlib import Path
 
 LIB_DIR = Path(__file__).resolve().parent / "lib"
 
-MODE_EXACT_F32, MODE_TF32, MODE_BF16, MODE_SAGE_INT8, MODE_SAGE_FP8 = 0, 1, 2, 3, 4
+MODE_EXACT_F32, MODE_TF32, MODE_BF16, MODE_SAGE_INT8, MODE_SAGE_FP8, MODE_SAGE_INT8_ROWS = 0, 1, 2, 3, 4, 5
 DTYPE_F32, DTYPE_BF16 = 0, 1
 
 AR_OK = 0

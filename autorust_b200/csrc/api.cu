@@ -11,7 +11,7 @@
 
 namespace {
 
-std::atomic<uint64_t> g_selected[5];
+std::atomic<uint64_t> g_selected[6];
 std::atomic<uint64_t> g_launches;
 
 // The library's status block on each device.  Word 0: launch status of calls that bring no workspace (cleared before
@@ -65,6 +65,7 @@ bool mode_has_kernel(int mode, int dtype, int64_t B, int64_t Hq, int64_t S, int6
     case AR_MODE_BF16: return dtype == AR_DTYPE_BF16 && ar::attn_tc_has(ar::TC_BF16, (int)D);
     case AR_MODE_SAGE_INT8: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE, (int)D);
     case AR_MODE_SAGE_FP8: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE_FP8, (int)D);
+    case AR_MODE_SAGE_INT8_ROWS: return (dtype == AR_DTYPE_BF16 || dtype == AR_DTYPE_F32) && ar::attn_tc_has(ar::TC_SAGE, (int)D);
     default: return false;
   }
 }
@@ -110,8 +111,8 @@ bool library_status_words(uint32_t** launch_word, uint32_t** sticky_word) {
   return true;
 }
 
-SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
-  const int64_t nblk = (S + 127) / 128;
+SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t block) {
+  const int64_t nblk = (S + block - 1) / block;
   SageLayout L;
   size_t off = STATUS_BYTES;
   L.q8 = off; off = align_up(off + (size_t)(B * Hq * S * D), 256);
@@ -128,7 +129,7 @@ SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,
 // Lets other translation units of the library feed the launch counters.
 void count_launches(int mode, int kernels) {
   g_launches += (uint64_t)kernels;
-  if (mode >= 0 && mode < 5) g_selected[mode]++;
+  if (mode >= 0 && mode < 6) g_selected[mode]++;
 }
 }  // namespace ar
 
@@ -148,6 +149,7 @@ int ar_attn_supported(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, i
 size_t ar_attn_workspace_bytes(int mode, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
   if (check_shape(B, Hq, Hkv, S, D) != AR_OK) return 0;
   if (mode == AR_MODE_SAGE_INT8 || mode == AR_MODE_SAGE_FP8) return sage_layout(dtype, B, Hq, Hkv, S, D).total;
+  if (mode == AR_MODE_SAGE_INT8_ROWS) return sage_layout(dtype, B, Hq, Hkv, S, D, 1).total;
   if (mode == AR_MODE_TF32)  // status block + the transposed copy of V, rows padded to a multiple of 4 keys
     return STATUS_BYTES + align_up(sizeof(float) * (size_t)(B * Hkv * D) * (size_t)((S + 3) / 4 * 4), 256);
   return 0;
@@ -160,12 +162,14 @@ int sage_quantize_any(const void* q, const void* k, int dtype, int8_t* q8, int8_
   if (!q || !k || !q8 || !k8 || !q_scale || !k_scale || !k_mean) return AR_ERR_NULL;
   int rc = check_shape(B, Hq, Hkv, S, D);
   if (rc != AR_OK) return rc;
-  if (block != 128 || (D != 64 && D != 128) || (dtype != AR_DTYPE_F32 && dtype != AR_DTYPE_BF16)) return AR_ERR_UNSUPPORTED;
+  if ((block != 128 && block != 1) || (D != 64 && D != 128) || (dtype != AR_DTYPE_F32 && dtype != AR_DTYPE_BF16))
+    return AR_ERR_UNSUPPORTED;
   if (B * (Hq + Hkv) > 65535) return AR_ERR_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8)) return AR_ERR_ALIGNMENT;
   if (!aligned4(q_scale) || !aligned4(k_scale) || !aligned4(k_mean)) return AR_ERR_ALIGNMENT;
   if (!device_ok()) return AR_ERR_NO_DEVICE;
   ar::PrologueArgs a{q, k, dtype, q8, k8, q_scale, k_scale, k_mean, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, smooth};
+  a.block = block;
   a.fp8 = fp8;
   // this entry point has no workspace: its status goes to the library's own word (ar_attn_last_status(NULL, ...))
   a.status = status_ptr(nullptr);
@@ -252,15 +256,18 @@ int forward_impl(int mode, int dtype, const void* q, const void* k, const void* 
         !ar::make_tile_map(&a.tm_v, vt, (int)CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, Hkv, D, S_pad, Hkv * D * S_pad, D * S_pad,
                            S_pad, 32, (int)D, nullptr))
       return AR_ERR_CUDA;
-  } else {  // AR_MODE_SAGE_INT8, AR_MODE_SAGE_FP8
-    const SageLayout L = sage_layout(dtype, B, Hq, Hkv, S, D);
+  } else {  // AR_MODE_SAGE_INT8, AR_MODE_SAGE_FP8, AR_MODE_SAGE_INT8_ROWS
+    // _ROWS is the reference kernel's own form: one scale per query row and per key row, K not smoothed
+    const bool rows = mode == AR_MODE_SAGE_INT8_ROWS;
+    const SageLayout L = sage_layout(dtype, B, Hq, Hkv, S, D, rows ? 1 : 128);
     uint8_t* ws = (uint8_t*)workspace;
     int8_t* q8 = (int8_t*)(ws + L.q8);
     int8_t* k8 = (int8_t*)(ws + L.k8);
     float* qs = (float*)(ws + L.q_scale);
     float* ks = (float*)(ws + L.k_scale);
     float* km = (float*)(ws + L.k_mean);
-    ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, 1};
+    ar::PrologueArgs p{q, k, dtype, q8, k8, qs, ks, km, (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, rows ? 0 : 1};
+    p.block = rows ? 1 : 128;
     p.fp8 = mode == AR_MODE_SAGE_FP8;
     p.status = status;  // shared with the attention kernel: cleared once, before the first launch
     p.sticky = sticky_ptr();
@@ -281,12 +288,14 @@ int forward_impl(int mode, int dtype, const void* q, const void* k, const void* 
     a.out_f32 = dtype == AR_DTYPE_F32;
     a.q_scale = qs;
     a.k_scale = ks;
+    a.scale_rows = rows ? 1 : 0;
     if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
         !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
         !make_map(&a.tm_v, v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
       return AR_ERR_CUDA;
   }
-  if (mode != AR_MODE_SAGE_INT8 && mode != AR_MODE_SAGE_FP8 && cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess)
+  if (mode != AR_MODE_SAGE_INT8 && mode != AR_MODE_SAGE_FP8 && mode != AR_MODE_SAGE_INT8_ROWS &&
+      cudaMemsetAsync(status, 0, sizeof(uint32_t), stream) != cudaSuccess)
     return AR_ERR_CUDA;
   cudaError_t e = ar::launch_attn_tc(a, stream);
   if (e != cudaSuccess) return AR_ERR_CUDA;
@@ -493,7 +502,7 @@ int ar_attn_last_status(void* workspace, void* cu_stream) {
 }
 
 
-uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 5) ? g_selected[mode].load() : 0; }
+uint64_t ar_attn_selections(int mode) { return (mode >= 0 && mode < 6) ? g_selected[mode].load() : 0; }
 uint64_t ar_attn_launch_count(void) { return g_launches.load(); }
 
 const char* ar_attn_strerror(int status) {

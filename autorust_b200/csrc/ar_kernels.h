@@ -30,8 +30,9 @@ struct TcArgs {
   long long o_sb, o_sh, o_ss;
   int out_f32;
   const float* mask;    // [S, S] additive or null
-  const float* q_scale; // TC_SAGE: [B*Hq, nblk]
-  const float* k_scale; // TC_SAGE: [B*Hkv, nblk]
+  const float* q_scale; // TC_SAGE: [B*Hq, nblk]; with scale_rows [B*Hq, S]
+  const float* k_scale; // TC_SAGE: [B*Hkv, nblk]; with scale_rows [B*Hkv, S]
+  int scale_rows;       // 1: one scale per query row and per key row (the reference's granularity) instead of per 128-token block
   int B, Hq, Hkv, S;
   int causal;
   OutReplicas replicas; // bf16 output only
@@ -60,7 +61,7 @@ bool library_status_words(uint32_t** launch_word, uint32_t** sticky_word);
 struct SageLayout {
   size_t q8, k8, q_scale, k_scale, k_mean, v16, total;
 };
-SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D);
+SageLayout sage_layout(int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t block = 128);
 
 // Exact f32 forward on FFMA (attn_fwd_exact.cu).
 struct ExactArgs {
@@ -92,6 +93,7 @@ struct PrologueArgs {
   float *q_scale, *k_scale, *k_mean;
   int B, Hq, Hkv, S, D;
   int smooth;
+  int block = 128;             // tokens per scale: 128, or 1 (one scale per row)
   int fp8 = 0;                 // 0: INT8, scale amax/127 (the default); 1: FP8 E4M3, scale amax/448
   uint32_t* status = nullptr;  // device word a bounded wait that ran out is recorded in; cleared by the caller
   uint32_t* sticky = nullptr;  // the library's accumulator of the same bits

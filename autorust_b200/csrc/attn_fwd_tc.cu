@@ -129,7 +129,7 @@ __device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& p0, float& p1) 
 template <int MODE, int D, int EDGE>
 __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float& l, float c, int j, int col0, int row,
                                              int N, int causal, const float* __restrict__ mask, uint32_t tS,
-                                             uint32_t tO, uint64_t* p_parts) {
+                                             uint32_t tO, uint64_t* p_parts, const float* __restrict__ kcol = nullptr) {
   float mc;  // row maximum of this step in the scaled (log2) domain
   // INT8 scores stay integers through the maximum on interior steps only; a bounds-only boundary step converts
   // them first (the same exact bit trick as below), so that the excluded columns can be marked with -inf
@@ -162,7 +162,9 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sv)[BN], float& m, float
 #pragma unroll
     for (int i = 0; i < BN; i++) {
       const int col = col0 + i;
-      float x = MODE == TC_SAGE ? (float)(int)sv[i] * c : __uint_as_float(sv[i]) * c;
+      // kcol: one scale per key (the element-wise path is the only one that takes per-row scales)
+      const float ci = (EDGE == 1 && kcol != nullptr) ? c * (col < N ? kcol[i] : 0.f) : c;
+      float x = MODE == TC_SAGE ? (float)(int)sv[i] * ci : __uint_as_float(sv[i]) * ci;
       if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
       if (col >= N || (causal && col > row)) x = NEG;
       sv[i] = __float_as_uint(x);
@@ -322,7 +324,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
                    int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
-                   const OutReplicas reps, uint32_t* status, uint32_t* sticky) {
+                   const OutReplicas reps, int scale_rows, uint32_t* status, uint32_t* sticky) {
   using C = Cfg<MODE, D, TILES>;
   constexpr int ST = C::STAGES;
   constexpr int W_PROD = 4 * TILES;     // warp that loads
@@ -575,7 +577,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float scale_log2 = (1.0f / sqrtf((float)D)) * LOG2E;
     const int nblk = nkv_all;
     float qs = 1.f;
-    if (C::QUANT && nkv[t] > 0) qs = q_scale[(size_t)bh * nblk + (q0 / BM + t)];
+    if (C::QUANT && nkv[t] > 0)
+      qs = scale_rows ? (row < N ? q_scale[(size_t)bh * N + row] : 1.f) : q_scale[(size_t)bh * nblk + (q0 / BM + t)];
     float m = NEG, l = 0.f;
 
     bool ok = true;
@@ -590,22 +593,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
       float c = scale_log2;
-      if (C::QUANT) c *= qs * k_scale[(size_t)kvbh * nblk + j];
+      if (C::QUANT) c *= scale_rows ? qs : qs * k_scale[(size_t)kvbh * nblk + j];
+      const float* kcol = (C::QUANT && scale_rows) ? k_scale + (size_t)kvbh * N + j * BN : nullptr;
       const int col0 = j * BN;
       // INT8 steps whose scale is too large for the folded conversion (see softmax_step) convert first, as the
       // boundary paths do; |s| <= 127 * 127 * 128 and m <= |s| * c keep 12582912 * c + m below 2^14 otherwise
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr) ||
-                        (MODE == TC_SAGE && c >= FOLD_MAX_C);
+                        (MODE == TC_SAGE && c >= FOLD_MAX_C) || kcol != nullptr;
       // Separate instantiations: the interior step must not carry the merge points of the boundary paths
       // (that alone costs it ~300 cycles of scheduling freedom).  A boundary step without an additive mask and
       // masks by -inf and runs the interior code (INT8 scores are converted first); an additive mask, whose -1e30
       // must tie with the initial running max, takes the element-wise path.
       if (!edge)
         softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      else if (mask == nullptr)
+      else if (mask == nullptr && kcol == nullptr)
         softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      else
-        softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
+      else  // an additive mask, or one scale per key: element by element
+        softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t], kcol);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_part[NPART * t + NPART - 1]);
@@ -720,7 +724,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   kern<<<grid, Shape<TILES>::NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale,
                                                                    a.k_scale, a.S, a.Hq, a.Hkv, a.causal, a.out_f32,
                                                                    a.token_major, a.o_sb, a.o_sh, a.o_ss, a.replicas,
-                                                                   a.status, a.sticky);
+                                                                   a.scale_rows, a.status, a.sticky);
   return cudaGetLastError();
 }
 

@@ -256,6 +256,40 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
   }
 }
 
+// One scale per ROW (the reference's own granularity, src/runtime/cuda_flash_sage.rs:209-222): D / 8 threads share a
+// row, 256 / (D / 8) rows per CTA; rows are numbered over Q first, then K.  Same scalar arithmetic as above.
+template <int DTYPE, int D>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const void* __restrict__ Q, const void* __restrict__ K,
+                                                            const float* __restrict__ k_mean, int8_t* __restrict__ q8,
+                                                            int8_t* __restrict__ k8, float* __restrict__ q_scale,
+                                                            float* __restrict__ k_scale, int S, long long q_rows,
+                                                            long long all_rows, int smooth, int fp8) {
+  constexpr int CH = D / 8;
+  const int tid = threadIdx.x;
+  const int c = tid % CH;
+  const long long r = (long long)blockIdx.x * (256 / CH) + tid / CH;
+  if (r >= all_rows) return;  // (whole groups of CH lanes leave together: the shuffles below stay inside a group)
+  const bool is_k = r >= q_rows;
+  const long long rr = is_k ? r - q_rows : r;
+  float x[8];
+  load8<DTYPE>(is_k ? K : Q, (size_t)rr * D + c * 8, x);
+  if (is_k && smooth) {
+    const long long bh = rr / S;
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] = x[i] - k_mean[(size_t)bh * D + c * 8 + i];
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+  const unsigned group = (CH == 32 ? 0xffffffffu : ((1u << CH) - 1u) << ((tid & 31) / CH * CH));
+#pragma unroll
+  for (int sh = CH / 2; sh > 0; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group, amax, sh));
+  const float scale = amax > 0.f ? __fdiv_rn(amax, fp8 ? 448.0f : 127.0f) : 1.0f;
+  const float inv = __fdiv_rn(1.0f, scale);
+  if (c == 0) (is_k ? k_scale : q_scale)[rr] = scale;
+  *(uint2*)((is_k ? k8 : q8) + (size_t)rr * D + c * 8) = quantize8(x, inv, fp8);
+}
+
 // The same quantiser as a persistent, software-pipelined kernel: every CTA walks a strided list of
 // 128-token blocks (Q blocks first, then K blocks); one thread brings block i + STAGES - 1 into a
 // shared-memory ring with a bulk copy while the CTA reduces and stores block i, so that each SM keeps
@@ -474,7 +508,12 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  if ((((uintptr_t)a.q | (uintptr_t)a.k) & 15u) == 0) {
+  if (a.block == 1) {
+    const long long q_rows = (long long)bhq * a.S, all_rows = q_rows + (long long)bhk * a.S;
+    const int rows_per_cta = 256 / (D / 8);
+    quantize_rows_kernel<DTYPE, D><<<(unsigned)((all_rows + rows_per_cta - 1) / rows_per_cta), 256, 0, stream>>>(
+        a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale, a.k_scale, a.S, q_rows, all_rows, a.smooth, a.fp8);
+  } else if ((((uintptr_t)a.q | (uintptr_t)a.k) & 15u) == 0) {
     // bulk copies need 16-byte aligned sources: the pipelined kernel, one or two CTAs per SM
     using P = QuantPipe<DTYPE, D>;
     auto kern = quantize_pipe_kernel<DTYPE, D>;

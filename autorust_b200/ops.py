@@ -11,7 +11,7 @@ import torch
 from . import _abi
 
 _MODE_NAMES = {"exact": _abi.MODE_EXACT_F32, "tf32": _abi.MODE_TF32, "bf16": _abi.MODE_BF16,
-               "sage": _abi.MODE_SAGE_INT8, "sage_fp8": _abi.MODE_SAGE_FP8}
+               "sage": _abi.MODE_SAGE_INT8, "sage_fp8": _abi.MODE_SAGE_FP8, "sage_rows": _abi.MODE_SAGE_INT8_ROWS}
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -192,9 +192,9 @@ def train_backward(q, k, v, o, d_o, lse, mask=None, causal: bool = False, stream
     return dq, dk, dv
 
 
-def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=None, fp8: bool = False):
+def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=None, fp8: bool = False, block: int = 128):
     """The Sage prologue on its own: returns (q8, k8, q_scale, k_scale, k_mean).  fp8: E4M3 bit patterns in
-    uint8 tensors and scales amax / 448 instead of INT8 and amax / 127."""
+    uint8 tensors and scales amax / 448 instead of INT8 and amax / 127.  block: tokens per scale, 128 or 1."""
     L = _abi.load()
     if q.dim() != 4 or k.dim() != 4 or not (q.is_cuda and k.is_cuda) or not (q.is_contiguous() and k.is_contiguous()):
         raise ValueError("q and k must be contiguous CUDA tensors [B, H, S, D]: there is no CPU path")
@@ -202,7 +202,7 @@ def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=
         raise ValueError("shape or dtype mismatch between q and k")
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
-    nblk = (S + 127) // 128
+    nblk = (S + block - 1) // block
     dev = q.device
     q8 = torch.empty(q.shape, dtype=torch.uint8 if fp8 else torch.int8, device=dev)
     k8 = torch.empty(k.shape, dtype=torch.uint8 if fp8 else torch.int8, device=dev)
@@ -213,7 +213,7 @@ def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=
         s = stream if stream is not None else torch.cuda.current_stream()
         fn = L.ar_sage_quantize_fp8 if fp8 else L.ar_sage_quantize
         rc = fn(q.data_ptr(), k.data_ptr(), _dtype_code(q), q8.data_ptr(), k8.data_ptr(), qs.data_ptr(), ks.data_ptr(),
-                km.data_ptr(), B, Hq, Hkv, S, D, 128, int(smooth), s.cuda_stream)
+                km.data_ptr(), B, Hq, Hkv, S, D, int(block), int(smooth), s.cuda_stream)
     _abi.check(rc, "ar_sage_quantize")
     return q8, k8, qs, ks, km
 

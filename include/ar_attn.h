@@ -45,8 +45,12 @@ enum ar_attn_mode {
   AR_MODE_TF32 = 1,      /* f32 tensors, TF32 tensor core src/runtime/cuda_flash_tc.rs:92-376  */
   AR_MODE_BF16 = 2,      /* bf16 in/out, f32 softmax      src/runtime/cuda_flash_bf16.rs:98-428 */
   AR_MODE_SAGE_INT8 = 3, /* INT8 QK^T, bf16 PV            src/runtime/cuda_flash_sage.rs:86-415 */
-  AR_MODE_SAGE_FP8 = 4   /* FP8 E4M3 QK^T, bf16 PV: the AR_FP8 variant of the same file (:92-97,126-129),
+  AR_MODE_SAGE_FP8 = 4,  /* FP8 E4M3 QK^T, bf16 PV: the AR_FP8 variant of the same file (:92-97,126-129),
                             the one the reference's dispatcher takes on sm_89 and later (:77-79) */
+  AR_MODE_SAGE_INT8_ROWS = 5 /* AR_MODE_SAGE_INT8 with the reference kernel's own granularity: one scale per query row
+                            and per key row, K not smoothed (src/runtime/cuda_flash_sage.rs:209-222,315-322).  The
+                            form that can be compared with the reference kernel's output; the per-block form is
+                            the fast one. */
 };
 
 /* Element types of q/k/v/o. */
@@ -147,7 +151,8 @@ int ar_attn_train_backward(const float* q, const float* k, const float* v, const
  * arithmetic of `ar_q4`, src/runtime/cuda_flash_sage.rs:130-135,209-222, which the reference
  * applies per row inside its attention kernel).
  * q8 [B,Hq,S,D], k8 [B,Hkv,S,D] int8; q_scale [B,Hq,ceil(S/block)], k_scale [B,Hkv,ceil(S/block)],
- * k_mean [B,Hkv,D] f32.  block must be 128.  smooth = 0 skips the mean (k_mean is zeroed). */
+ * k_mean [B,Hkv,D] f32.  block is 128, or 1 (one scale per row, the reference's granularity: q_scale [B,Hq,S],
+ * k_scale [B,Hkv,S]).  smooth = 0 skips the mean (k_mean is zeroed). */
 int ar_sage_quantize(const void* q, const void* k, int dtype, int8_t* q8, int8_t* k8, float* q_scale, float* k_scale,
                      float* k_mean, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int block, int smooth,
                      void* cu_stream);

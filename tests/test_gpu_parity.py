@@ -255,6 +255,38 @@ def test_sage_head_dim_64(ops, oracle_lib, mode, model, n, causal, hq, hkv):
         assert max_abs(gots, oracle_lib.flash(3, qs, ks_, vs, None, causal, block=128, smooth=True)) < 2e-3
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("n", [1, 8, 33, 100, 789])  # tests/sage_int8.rs:133
+def test_sage_rows_mode_matches_the_per_row_model(ops, oracle_lib, n, d):
+    """AR_MODE_SAGE_INT8_ROWS: one scale per query row and per key row, K not smoothed -- the reference kernel's own
+    form (src/runtime/cuda_flash_sage.rs:209-222,315-322) -- on the reference test's inputs and bound."""
+    import torch
+    q, k, v = sawtooth_qkv(1, 2, 2, n, d)
+    got = run_f32(ops, "sage_rows", q, k, v)
+    want = oracle_lib.flash(3, q, k, v, None, False, block=1, smooth=False)
+    assert max_abs(got, want) < 2e-3  # tests/sage_int8.rs:148
+    # the per-row quantiser: every bit
+    q8, k8, qs, ks, km = ops.sage_quantize(to_dev(q), to_dev(k), False, block=1)
+    torch.cuda.synchronize()
+    w = oracle_lib.sage_quantize(q, k, 1, False)
+    assert np.array_equal(q8.cpu().numpy(), w[0]) and np.array_equal(k8.cpu().numpy(), w[1])
+    assert np.array_equal(qs.cpu().numpy().view(np.uint32), w[2].view(np.uint32))
+    assert np.array_equal(ks.cpu().numpy().view(np.uint32), w[3].view(np.uint32))
+
+
+def test_sage_rows_mode_causal_mask_gqa(ops, oracle_lib):
+    q, k, v = sawtooth_qkv(2, 4, 2, 200, 64)
+    mask = sawtooth_mask(200)
+    got = run_f32(ops, "sage_rows", q, k, v, mask, True)
+    want = oracle_lib.flash(3, q, k, v, mask, True, block=1, smooth=False)
+    assert max_abs(got, want) < 2e-3
+    qn, kn, vn = normal_qkv(8, 1, 2, 2, 300, 128)
+    qb, kb, vb = (oracle_lib.f32_to_bf16(x) for x in (qn, kn, vn))
+    gotb = oracle_lib.bf16_to_f32(run_bf16(ops, "sage_rows", qb, kb, vb, None, True))
+    wantb = oracle_lib.bf16_to_f32(oracle_lib.flash(3, qb, kb, vb, None, True, block=1, smooth=False))
+    assert max_abs(gotb, wantb) < 2e-2 and cosine(gotb, wantb) > 0.9999
+
+
 def test_sage_with_mask(ops, oracle_lib):
     q, k, v = sawtooth_qkv(1, 2, 2, 200, 128)
     mask = sawtooth_mask(200)

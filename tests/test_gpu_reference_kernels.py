@@ -116,8 +116,28 @@ def test_mask_causal_gqa_table(ref, oracle_lib, attn_lib, label, b, hq, hkv, n, 
 
 
 @pytest.mark.parametrize("n", [1, 8, 33, 100, 789])  # tests/sage_int8.rs:133
-def test_sage_per_row_model_matches_reference_kernel(ref, oracle_lib, n):
+def test_sage_per_row_model_and_kernel_match_reference_kernel(ref, oracle_lib, attn_lib, n):
+    """The reference's Sage kernel against the oracle's per-row model, and OUR Sage kernel in the reference's form
+    (D = 64, one scale per row, no smoothing: AR_MODE_SAGE_INT8_ROWS) against the reference kernel's output."""
+    from autorust_b200 import ops
+    import torch
     q, k, v = inputs(1, 6, 6, n)
-    theirs = run_ref(ref, "ar_flash_sage", to_dev(q), to_dev(k), to_dev(v), None, False).cpu().numpy()
+    tq, tk, tv = to_dev(q), to_dev(k), to_dev(v)
+    theirs = run_ref(ref, "ar_flash_sage", tq, tk, tv, None, False).cpu().numpy()
     model = oracle_lib.flash(3, q, k, v, None, False, block=1, smooth=False)
     assert max_abs(theirs, model) < 2e-3  # tests/sage_int8.rs:148
+    ours = ops.attn_forward("sage_rows", tq, tk, tv)
+    torch.cuda.synchronize()
+    assert max_abs(ours.cpu().numpy(), theirs) < 2e-3
+
+
+def test_sage_rows_mode_with_causal_and_mask_against_reference_kernel(ref, oracle_lib, attn_lib):
+    from autorust_b200 import ops
+    import torch
+    q, k, v = inputs(2, 4, 2, 100)
+    tm = to_dev(sawtooth_mask(100))
+    tq, tk, tv = to_dev(q), to_dev(k), to_dev(v)
+    theirs = run_ref(ref, "ar_flash_sage", tq, tk, tv, tm, True).cpu().numpy()
+    ours = ops.attn_forward("sage_rows", tq, tk, tv, tm, True)
+    torch.cuda.synchronize()
+    assert max_abs(ours.cpu().numpy(), theirs) < 2e-3
