@@ -318,13 +318,15 @@ struct Cfg {
   static constexpr uint32_t IDESC_PV = MODE == TC_TF32 ? make_idesc(1, 2, 2, 0, 0, BM, D) : make_idesc(1, 1, 1, 0, 1, BM, D);
 };
 
-template <int MODE, int D, int TILES>
+// ROWS: Sage with one scale per query row and per key row (an instantiation of its own, so that the per-block kernel
+// carries none of it).
+template <int MODE, int D, int TILES, bool ROWS>
 __global__ void __launch_bounds__(Shape<TILES>::NUM_THREADS, Shape<TILES>::MIN_CTAS)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
                    int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
-                   const OutReplicas reps, int scale_rows, uint32_t* status, uint32_t* sticky) {
+                   const OutReplicas reps, uint32_t* status, uint32_t* sticky) {
   using C = Cfg<MODE, D, TILES>;
   constexpr int ST = C::STAGES;
   constexpr int W_PROD = 4 * TILES;     // warp that loads
@@ -578,7 +580,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int nblk = nkv_all;
     float qs = 1.f;
     if (C::QUANT && nkv[t] > 0)
-      qs = scale_rows ? (row < N ? q_scale[(size_t)bh * N + row] : 1.f) : q_scale[(size_t)bh * nblk + (q0 / BM + t)];
+      qs = ROWS ? (row < N ? q_scale[(size_t)bh * N + row] : 1.f) : q_scale[(size_t)bh * nblk + (q0 / BM + t)];
     float m = NEG, l = 0.f;
 
     bool ok = true;
@@ -593,20 +595,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld32(tS + 96, sv + 96);
       tmem_wait_ld();
       float c = scale_log2;
-      if (C::QUANT) c *= scale_rows ? qs : qs * k_scale[(size_t)kvbh * nblk + j];
-      const float* kcol = (C::QUANT && scale_rows) ? k_scale + (size_t)kvbh * N + j * BN : nullptr;
+      if (C::QUANT) c *= ROWS ? qs : qs * k_scale[(size_t)kvbh * nblk + j];
+      const float* kcol = ROWS ? k_scale + (size_t)kvbh * N + j * BN : nullptr;
       const int col0 = j * BN;
       // INT8 steps whose scale is too large for the folded conversion (see softmax_step) convert first, as the
       // boundary paths do; |s| <= 127 * 127 * 128 and m <= |s| * c keep 12582912 * c + m below 2^14 otherwise
       const bool edge = (col0 + BN > N) || (causal && col0 + BN - 1 > q0 + t * BM) || (mask != nullptr) ||
-                        (MODE == TC_SAGE && c >= FOLD_MAX_C) || kcol != nullptr;
+                        (MODE == TC_SAGE && c >= FOLD_MAX_C) || ROWS;
       // Separate instantiations: the interior step must not carry the merge points of the boundary paths
       // (that alone costs it ~300 cycles of scheduling freedom).  A boundary step without an additive mask and
       // masks by -inf and runs the interior code (INT8 scores are converted first); an additive mask, whose -1e30
       // must tie with the initial running max, takes the element-wise path.
       if (!edge)
         softmax_step<MODE, D, 0>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
-      else if (mask == nullptr && kcol == nullptr)
+      else if (mask == nullptr && !ROWS)
         softmax_step<MODE, D, 2>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t]);
       else  // an additive mask, or one scale per key: element by element
         softmax_step<MODE, D, 1>(sv, m, l, c, j, col0, row, N, causal, mask, tS, tO, &p_part[NPART * t], kcol);
@@ -707,10 +709,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == W_MMA) tmem_dealloc(tb, 256 * TILES);
 }
 
-template <int MODE, int D, int TILES>
+template <int MODE, int D, int TILES, bool ROWS = false>
 cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   using C = Cfg<MODE, D, TILES>;
-  auto kern = attn_fwd_tc_kernel<MODE, D, TILES>;
+  auto kern = attn_fwd_tc_kernel<MODE, D, TILES, ROWS>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -724,7 +726,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   kern<<<grid, Shape<TILES>::NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale,
                                                                    a.k_scale, a.S, a.Hq, a.Hkv, a.causal, a.out_f32,
                                                                    a.token_major, a.o_sb, a.o_sh, a.o_ss, a.replicas,
-                                                                   a.scale_rows, a.status, a.sticky);
+                                                                   a.status, a.sticky);
   return cudaGetLastError();
 }
 
@@ -775,6 +777,9 @@ cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream) {
   if (a.mode == TC_BF16 && a.D == 64 && a.S <= SHORT_SEQUENCE) return launch_one<TC_BF16, 64, 1>(a, stream);
   if (a.mode == TC_BF16 && a.D == 128) return launch_one<TC_BF16, 128, 2>(a, stream);
   if (a.mode == TC_BF16 && a.D == 64) return launch_one<TC_BF16, 64, 2>(a, stream);
+  if (a.mode == TC_SAGE && a.scale_rows && a.D == 128) return launch_one<TC_SAGE, 128, 2, true>(a, stream);
+  if (a.mode == TC_SAGE && a.scale_rows && a.D == 64) return launch_one<TC_SAGE, 64, 2, true>(a, stream);
+  if (a.scale_rows) return cudaErrorInvalidValue;
   if (a.mode == TC_SAGE && a.D == 128) return launch_one<TC_SAGE, 128, 2>(a, stream);
   if (a.mode == TC_SAGE && a.D == 64) return launch_one<TC_SAGE, 64, 2>(a, stream);
   if (a.mode == TC_SAGE_FP8 && a.D == 128) return launch_one<TC_SAGE_FP8, 128, 2>(a, stream);
