@@ -35,6 +35,8 @@ SYMBOLS = (
     "ar_attn_train_forward",
     "ar_attn_train_workspace_bytes",
     "ar_attn_train_backward",
+    "ar_attn_train_tc_workspace_bytes",
+    "ar_attn_train_backward_tc",
     "ar_sage_quantize",
     "ar_sage_quantize_fp8",
     "ar_sage_attention_prequantized",
@@ -86,6 +88,10 @@ def load() -> ctypes.CDLL:
     L.ar_attn_train_workspace_bytes.restype = ctypes.c_size_t
     L.ar_attn_train_backward.argtypes = [p] * 10 + [i64] * 5 + [ci, p, ctypes.c_size_t, p]
     L.ar_attn_train_backward.restype = ci
+    L.ar_attn_train_tc_workspace_bytes.argtypes = [i64, i64, i64, i64, i64]
+    L.ar_attn_train_tc_workspace_bytes.restype = ctypes.c_size_t
+    L.ar_attn_train_backward_tc.argtypes = L.ar_attn_train_backward.argtypes
+    L.ar_attn_train_backward_tc.restype = ci
     L.ar_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, ci, p]
     L.ar_sage_quantize.restype = ci
     L.ar_sage_attention_prequantized.argtypes = [p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]

@@ -35,7 +35,8 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
-KERNEL_SOURCES = ["attn_fwd_tc.cu", "attn_fwd_exact.cu", "attn_train.cu", "sage_prologue.cu", "api.cu", "sage_static.cu"]
+KERNEL_SOURCES = ["attn_fwd_tc.cu", "attn_fwd_exact.cu", "attn_train.cu", "attn_train_tc.cu", "sage_prologue.cu", "api.cu",
+                  "sage_static.cu"]
 
 
 def _nvcc() -> str:
@@ -81,7 +82,7 @@ def build_kernels(force: bool = False) -> Path:
 
 
 # Sources whose device code contains bounded waits: rebuilt with the short budget for the wait-expiry test library.
-WAIT_SOURCES = ["attn_fwd_tc.cu", "sage_prologue.cu"]
+WAIT_SOURCES = ["attn_fwd_tc.cu", "attn_train_tc.cu", "sage_prologue.cu"]
 WAIT_TEST_FLAGS = ["-DAR_WAIT_TEST", "-DAR_WAIT_BUDGET_CYCLES=2000000ll"]
 
 

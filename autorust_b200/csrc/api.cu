@@ -416,6 +416,75 @@ int ar_attn_train_backward(const float* q, const float* k, const float* v, const
 }
 
 namespace {
+struct TrainTcLayout {
+  size_t delta, q16, k16, v16, do16, total;
+};
+TrainTcLayout train_tc_layout(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  TrainTcLayout L;
+  size_t off = STATUS_BYTES;
+  L.delta = off; off = align_up(off + sizeof(float) * (size_t)(B * Hq * S), 256);
+  L.q16 = off; off = align_up(off + 2 * (size_t)(B * Hq * S * D), 256);
+  L.do16 = off; off = align_up(off + 2 * (size_t)(B * Hq * S * D), 256);
+  L.k16 = off; off = align_up(off + 2 * (size_t)(B * Hkv * S * D), 256);
+  L.v16 = off; off = align_up(off + 2 * (size_t)(B * Hkv * S * D), 256);
+  L.total = off;
+  return L;
+}
+}  // namespace
+
+size_t ar_attn_train_tc_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  if (check_shape(B, Hq, Hkv, S, D) != AR_OK) return 0;
+  return train_tc_layout(B, Hq, Hkv, S, D).total;
+}
+
+int ar_attn_train_backward_tc(const float* q, const float* k, const float* v, const float* o, const float* d_o,
+                              const float* lse, const float* mask, float* dq, float* dk, float* dv, int64_t B,
+                              int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                              size_t workspace_bytes, void* cu_stream) {
+  if (!q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv || !workspace) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if ((D != 64 && D != 128) || B * Hq > 65535 || S > (1 << 24)) return AR_ERR_UNSUPPORTED;
+  const TrainTcLayout L = train_tc_layout(B, Hq, Hkv, S, D);
+  if (workspace_bytes < L.total) return AR_ERR_WORKSPACE;
+  for (const void* p : {(const void*)q, (const void*)k, (const void*)v, (const void*)o, (const void*)d_o, (const void*)dq,
+                        (const void*)dk, (const void*)dv, (const void*)workspace})
+    if (!aligned16(p)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(lse) || !aligned4(mask)) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  uint8_t* ws = (uint8_t*)workspace;
+  if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  int launches = 0;
+  // D_i = O_i . dO_i, and the bf16 copies of the four operands
+  if (ar::launch_train_prep(o, d_o, (float*)(ws + L.delta), B * Hq * S, (int)D, stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (ar::launch_f32_to_bf16(q, ws + L.q16, B * Hq * S * D, stream) != cudaSuccess ||
+      ar::launch_f32_to_bf16(d_o, ws + L.do16, B * Hq * S * D, stream) != cudaSuccess ||
+      ar::launch_f32_to_bf16(k, ws + L.k16, B * Hkv * S * D, stream) != cudaSuccess ||
+      ar::launch_f32_to_bf16(v, ws + L.v16, B * Hkv * S * D, stream) != cudaSuccess)
+    return AR_ERR_CUDA;
+  launches += 5;
+  ar::TrainBwdTcArgs a;
+  memset(&a, 0, sizeof(a));
+  if (!make_map(&a.tm_q, ws + L.q16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hq, S, D) ||
+      !make_map(&a.tm_do, ws + L.do16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hq, S, D) ||
+      !make_map(&a.tm_k, ws + L.k16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D) ||
+      !make_map(&a.tm_v, ws + L.v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
+    return AR_ERR_CUDA;
+  a.lse = lse;
+  a.delta = (const float*)(ws + L.delta);
+  a.mask = mask;
+  a.dq = dq; a.dk = dk; a.dv = dv;
+  a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S; a.D = (int)D;
+  a.causal = causal ? 1 : 0;
+  a.status = (uint32_t*)ws;
+  a.sticky = sticky_ptr();
+  const cudaError_t e = ar::launch_attn_train_backward_tc(a, stream, &launches);
+  g_launches += (uint64_t)launches;
+  return e == cudaSuccess ? AR_OK : AR_ERR_CUDA;
+}
+
+namespace {
 int sage_prequantized_any(int mode, const void* q8, const void* k8, const float* q_scale, const float* k_scale,
                           const void* v_bf16, void* o, const ar::OutReplicas& reps, int out_dtype, const float* mask,
                           int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,

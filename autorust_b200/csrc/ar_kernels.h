@@ -84,6 +84,21 @@ struct TrainBwdArgs {
 };
 // Launches prep, dQ and dK/dV; *launches returns the number of kernels.
 cudaError_t launch_attn_train_backward(const TrainBwdArgs& a, cudaStream_t stream, int* launches);
+// delta[row] = O_row . dO_row over `rows` rows of D floats (the first kernel of the backward, on its own).
+cudaError_t launch_train_prep(const float* o, const float* d_o, float* delta, long long rows, int D, cudaStream_t stream);
+
+// The same gradients on the tensor cores (attn_train_tc.cu): bf16 operands (copies the caller made), f32 accumulation.
+struct TrainBwdTcArgs {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;  // bf16 [B, H, S, D], box of 64 columns x 128 rows, 128-byte swizzle
+  const float *lse, *delta, *mask;
+  float *dq, *dk, *dv;
+  int B, Hq, Hkv, S, D;
+  int causal;
+  uint32_t* status;
+  uint32_t* sticky;
+};
+// Launches dQ and dK/dV; *launches is incremented by the number of kernels.
+cudaError_t launch_attn_train_backward_tc(const TrainBwdTcArgs& a, cudaStream_t stream, int* launches);
 
 // Sage prologue (sage_prologue.cu).
 struct PrologueArgs {

@@ -138,6 +138,17 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
+// One lane of a converged warp (elect.sync): a warp that walks its loop converged issues its tcgen05 instructions
+// under this election.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void commit_one(uint64_t* bar) {
+  if (elect_one()) tc_commit(bar);
+}
+
 enum MmaKind { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2, KIND_F8 = 3 };
 
 // D[tmem] (+)= A[smem desc] * B[smem desc] and D[tmem] (+)= A[tmem] * B[smem desc], with the 64-bit shared-memory

@@ -77,16 +77,6 @@ struct Shape {
   static_assert(LAUNCH_REGS * NUM_THREADS * MIN_CTAS <= 65536, "register file of the SM");
 };
 
-// One lane of a converged warp (elect.sync).
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
-__device__ __forceinline__ void commit_one(uint64_t* bar) {
-  if (elect_one()) tc_commit(bar);
-}
-
 // Largest scale c of an INT8 step that may fold its conversion: (12582912 + 127 * 127 * 128) * c < 2^14.
 constexpr float FOLD_MAX_C = 1.0e-3f;
 

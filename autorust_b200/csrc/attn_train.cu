@@ -322,6 +322,11 @@ cudaError_t launch_bwd(const TrainBwdArgs& a, cudaStream_t stream, int* launches
 
 }  // namespace
 
+cudaError_t launch_train_prep(const float* o, const float* d_o, float* delta, long long rows, int D, cudaStream_t stream) {
+  train_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(o, d_o, delta, rows, D);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_attn_train_backward(const TrainBwdArgs& a, cudaStream_t stream, int* launches) {
   if (a.D == 64) return launch_bwd<64>(a, stream, launches);
   if (a.D == 128) return launch_bwd<128>(a, stream, launches);

@@ -257,7 +257,7 @@ void note_sage_unsupported() {  // src/models/flash_attention.rs:322-331
   static std::once_flag once;
   std::call_once(once, [] {
     std::fprintf(stderr,
-                 "[attention] sage: quantized attention needs an sm_100 device and head_dim 128: using the exact kernel\n");
+                 "[attention] sage: quantized attention needs an sm_100 device, tensor cores on and head_dim 64 or 128: using the exact kernel\n");
   });
 }
 }  // namespace

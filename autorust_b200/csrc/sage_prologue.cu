@@ -9,7 +9,7 @@
 // AR_FP8 variant, src/runtime/cuda_flash_sage.rs:92-97,126-129) differs in two places only: scale = amax / 448 and
 // the rounding is cvt.rn.satfinite to E4M3.
 //
-// Both kernels are bandwidth-bound and move 16 bytes per thread per access.  Arithmetic that
+// The kernels are bandwidth-bound and move 16 bytes per thread per access.  Arithmetic that
 // decides bits is kept free of fused multiply-adds and fast-math: every tensor is widened to f32
 // exactly, the K mean is summed in a fixed order (runs of 16 tokens, then the 8 runs of a
 // 128-token span, then the spans, each left to right, times 1.0f / S), K - mean is one f32
@@ -198,64 +198,6 @@ __global__ void __launch_bounds__(MEAN_SLOTS * D) k_mean_cluster_kernel(const vo
   cluster.sync();  // nobody's shared memory goes away while CTA 0 reads it
 }
 
-// One CTA per (tensor row block of 128 tokens, bh).  blockIdx.y < BHq: Q, else K.
-template <int DTYPE, int D>
-__global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ Q, const void* __restrict__ K,
-                                                       const float* __restrict__ k_mean, int8_t* __restrict__ q8,
-                                                       int8_t* __restrict__ k8, float* __restrict__ q_scale,
-                                                       float* __restrict__ k_scale, int S, int BHq, int smooth, int fp8) {
-  constexpr int CH = D / 8;
-  constexpr int NCHUNK = 128 * CH / 256;  // chunks per thread: 8 (D=128) or 4 (D=64)
-  __shared__ float warp_max[8];
-  const int tid = threadIdx.x;
-  const bool is_k = (int)blockIdx.y >= BHq;
-  const int bh = is_k ? blockIdx.y - BHq : blockIdx.y;
-  const void* src = is_k ? K : Q;
-  int8_t* dst = is_k ? k8 : q8;
-  const int nblk = gridDim.x;
-  const int t0 = blockIdx.x * 128;
-  const size_t base = (size_t)bh * S * D;
-  const int c = tid % CH;  // 256 % CH == 0: every chunk of this thread has the same d range
-  float mu[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) mu[i] = 0.f;
-  if (is_k && smooth) {
-#pragma unroll
-    for (int i = 0; i < 8; i++) mu[i] = k_mean[(size_t)bh * D + c * 8 + i];
-  }
-  float x[NCHUNK][8];
-  float amax = 0.f;
-#pragma unroll
-  for (int n = 0; n < NCHUNK; n++) {
-    const int tok = t0 + (tid + 256 * n) / CH;
-    if (tok < S) {
-      load8<DTYPE>(src, base + (size_t)tok * D + c * 8, x[n]);
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        x[n][i] = x[n][i] - mu[i];
-        amax = fmaxf(amax, fabsf(x[n][i]));
-      }
-    }
-  }
-#pragma unroll
-  for (int sh = 16; sh > 0; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
-  if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
-  __syncthreads();
-  amax = warp_max[0];
-#pragma unroll
-  for (int w = 1; w < 8; w++) amax = fmaxf(amax, warp_max[w]);
-  const float scale = amax > 0.f ? __fdiv_rn(amax, fp8 ? 448.0f : 127.0f) : 1.0f;
-  const float inv = __fdiv_rn(1.0f, scale);
-  if (tid == 0) (is_k ? k_scale : q_scale)[(size_t)bh * nblk + blockIdx.x] = scale;
-#pragma unroll
-  for (int n = 0; n < NCHUNK; n++) {
-    const int tok = t0 + (tid + 256 * n) / CH;
-    if (tok < S) {
-      *(uint2*)(dst + base + (size_t)tok * D + c * 8) = quantize8(x[n], inv, fp8);
-    }
-  }
-}
-
 // One scale per ROW (the reference's own granularity, src/runtime/cuda_flash_sage.rs:209-222): D / 8 threads share a
 // row, 256 / (D / 8) rows per CTA; rows are numbered over Q first, then K.  Same scalar arithmetic as above.
 template <int DTYPE, int D>
@@ -294,7 +236,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const void* __restri
 // 128-token blocks (Q blocks first, then K blocks); one thread brings block i + STAGES - 1 into a
 // shared-memory ring with a bulk copy while the CTA reduces and stores block i, so that each SM keeps
 // tens of KB of reads in flight the whole time instead of one load-reduce-store round per CTA.
-// Bit-for-bit the arithmetic of quantize_kernel.  Needs 16-byte aligned Q and K.
+// Needs 16-byte aligned Q and K.
 template <int DTYPE, int D>
 struct QuantPipe {
   static constexpr int ES = DTYPE == 1 ? 2 : 4;
@@ -513,8 +455,9 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
     const int rows_per_cta = 256 / (D / 8);
     quantize_rows_kernel<DTYPE, D><<<(unsigned)((all_rows + rows_per_cta - 1) / rows_per_cta), 256, 0, stream>>>(
         a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale, a.k_scale, a.S, q_rows, all_rows, a.smooth, a.fp8);
-  } else if ((((uintptr_t)a.q | (uintptr_t)a.k) & 15u) == 0) {
-    // bulk copies need 16-byte aligned sources: the pipelined kernel, one or two CTAs per SM
+  } else {
+    // 128-token blocks: the pipelined kernel, one or two CTAs per SM (its bulk copies need 16-byte aligned sources,
+    // which every caller of this function guarantees)
     using P = QuantPipe<DTYPE, D>;
     auto kern = quantize_pipe_kernel<DTYPE, D>;
     static bool configured[64] = {};
@@ -534,9 +477,6 @@ cudaError_t launch_prologue_t(const PrologueArgs& a, cudaStream_t stream, int* l
     if (grid > items) grid = items;
     kern<<<grid, 256, P::SMEM_BYTES, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale, a.k_scale, a.S, bhq, bhk,
                                                a.smooth, a.fp8, a.status, a.sticky);
-  } else {
-    quantize_kernel<DTYPE, D><<<dim3(nblk, bhq + bhk, 1), 256, 0, stream>>>(a.q, a.k, a.k_mean, a.q8, a.k8, a.q_scale,
-                                                                           a.k_scale, a.S, bhq, a.smooth, a.fp8);
   }
   (*launches)++;
   return cudaGetLastError();

@@ -168,8 +168,9 @@ def train_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch
     return o, lse
 
 
-def train_backward(q, k, v, o, d_o, lse, mask=None, causal: bool = False, stream=None):
-    """(dq, dk, dv) from the forward's o and lse and the output gradient d_o (all float32, contiguous)."""
+def train_backward(q, k, v, o, d_o, lse, mask=None, causal: bool = False, stream=None, tensor_cores: bool = False):
+    """(dq, dk, dv) from the forward's o and lse and the output gradient d_o (all float32, contiguous).
+    tensor_cores: the bf16-operand tcgen05 kernels (ar_attn_train_backward_tc) instead of the exact f32 ones."""
     L = _abi.load()
     _check_qkv(q, k, v)
     if q.dtype != torch.float32:
@@ -180,11 +181,13 @@ def train_backward(q, k, v, o, d_o, lse, mask=None, causal: bool = False, stream
     _check_dense("d_o", d_o, q.shape, torch.float32, q.device)
     _check_dense("lse", lse, (B, Hq, S), torch.float32, q.device)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    need = int(L.ar_attn_train_workspace_bytes(B, Hq, S))
+    need = int(L.ar_attn_train_tc_workspace_bytes(B, Hq, k.shape[1], S, D) if tensor_cores
+               else L.ar_attn_train_workspace_bytes(B, Hq, S))
     ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    fn = L.ar_attn_train_backward_tc if tensor_cores else L.ar_attn_train_backward
     with torch.cuda.device(q.device):
         s = stream if stream is not None else torch.cuda.current_stream()
-        rc = L.ar_attn_train_backward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+        rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
                                       mask.data_ptr() if mask is not None else None, dq.data_ptr(), dk.data_ptr(),
                                       dv.data_ptr(), B, Hq, k.shape[1], S, D, int(causal), ws.data_ptr(), need, s.cuda_stream)
     _abi.check(rc, "ar_attn_train_backward")

@@ -258,17 +258,19 @@ def verify_gather(torch, dist, slabs, rank, world) -> tuple[bool, int]:
     return ok, total
 
 
-def time_kernel(torch, fn, iters=10, warm=3, reps=2, sustained=40) -> tuple[float, float]:
+def time_kernel(torch, fn, iters=10, warm=3, reps=3, sustained=40) -> tuple[float, float]:
     """CUDA-event times of fn() in ms, the two ways the tensor peaks were measured: (burst, sustained).
-    Burst: best of `iters` samples, each bracketing `reps` back-to-back calls (so that the host's time to issue a
-    call does not sit between the events of a short kernel), with the GPU idle between samples.  Sustained: the
-    mean over `sustained` back-to-back calls, long enough for the power cap to settle the clock."""
+    Burst: best of `iters` samples; a sample queues one untimed call and, behind it, `reps` timed calls between two
+    events, so that the host's time to issue a call never sits between the events, and the GPU idles between
+    samples.  Sustained: the mean over `sustained` back-to-back calls, long enough for the power cap to settle the
+    clock."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     ts = []
     for _ in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
         e0.record()
         for _ in range(reps):
             fn()
@@ -276,6 +278,7 @@ def time_kernel(torch, fn, iters=10, warm=3, reps=2, sustained=40) -> tuple[floa
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1) / reps)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fn()
     e0.record()
     for _ in range(sustained):
         fn()
@@ -303,7 +306,7 @@ def bf16_legs(torch, device, peaks) -> dict:
                     "kernel_ms_sustained": ms_sus, "tflops_sustained": tf_sus,
                     "frac_of_bf16_peak_sustained": tf_sus / peaks["bf16_tflops_sustained"],
                     "flops": "4*B*H*S^2*D" + ("/2" if causal else ""),
-                    "timing": "CUDA events; burst: best of 10 samples of 2 back-to-back launches, against bf16_tflops; "
+                    "timing": "CUDA events; burst: best of 10 samples of 3 launches queued behind an untimed one, against bf16_tflops; "
                               "sustained: mean of 40 back-to-back launches, against bf16_tflops_sustained "
                               f"(MEASURED_PEAKS.json, {peaks['source']})"}
         del q, k, v, out

@@ -145,6 +145,19 @@ int ar_attn_train_backward(const float* q, const float* k, const float* v, const
                            int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
                            size_t workspace_bytes, void* cu_stream);
 
+/* The same gradients on the tensor cores: every product of the backward is a tcgen05.mma on bf16 copies of q, k, v and
+ * d_o (made inside the call, in the workspace), with f32 accumulation, P and dS rounded to bf16 like P in the
+ * forward.  Arguments as ar_attn_train_backward; the workspace is larger (ar_attn_train_tc_workspace_bytes: the row
+ * scalars D, the four bf16 copies, and the 256-byte status block ar_attn_last_status reads).  A fast mode with the
+ * accuracy of bf16 operands, about 2e-3 of a gradient's largest entry: on the reference test's inputs inside its
+ * absolute 2e-3 (tests/flash_train_cuda.rs:80,102-104) for the plain and masked cases, above it for the causal and GQA
+ * cases, whose gradients are larger; ar_attn_train_backward remains the exact f32 path.  The reference's backward is scalar f32 only (src/runtime/cuda_flash_train.rs:118-309). */
+size_t ar_attn_train_tc_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D);
+int ar_attn_train_backward_tc(const float* q, const float* k, const float* v, const float* o, const float* d_o,
+                              const float* lse, const float* mask, float* dq, float* dk, float* dv, int64_t B,
+                              int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                              size_t workspace_bytes, void* cu_stream);
+
 /* The Sage prologue on its own: optional K mean-smoothing, then symmetric INT8 quantisation of
  * Q and K with one f32 scale per `block` consecutive tokens
  * (scale = amax > 0 ? amax / 127 : 1; q8 = clamp(rn(x * (1 / scale)), -127, 127): the scalar
