@@ -56,6 +56,36 @@ def from_dev_bf16(t) -> np.ndarray:
     return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
 
 
+def torch_f32_attention_error(q, k, v, out, causal: bool):
+    """Every row of every (batch, head) pair of a bf16 result against attention computed by torch in float32 on the
+    same GPU, one pair at a time (an independent cross-check beside the CPU oracle's sampled rows: the oracle pins the
+    semantics, this covers the whole tensor).  q, out: [B, Hq, S, D]; k, v: [B, Hkv, S, D] CUDA tensors.
+    Returns (per-row max-abs as a numpy vector of S entries, the worst over pairs and channels; cosine over everything)."""
+    import torch
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        B, Hq, S, D = q.shape
+        G = Hq // k.shape[1]
+        worst = torch.zeros(S, device=q.device)
+        dot = n_got = n_ref = 0.0
+        keep = torch.ones(S, S, dtype=torch.bool, device=q.device).tril_() if causal else None
+        for b in range(B):
+            for h in range(Hq):
+                s = (q[b, h].float() @ k[b, h // G].float().T) * (1.0 / float(D) ** 0.5)
+                if causal:
+                    s.masked_fill_(~keep, float("-inf"))
+                ref = torch.softmax(s, dim=-1) @ v[b, h // G].float()
+                got = out[b, h].float()
+                worst = torch.maximum(worst, (got - ref).abs().amax(dim=1))
+                dot += float((got.double() * ref.double()).sum())
+                n_got += float((got.double() ** 2).sum())
+                n_ref += float((ref.double() ** 2).sum())
+        return worst.cpu().numpy(), dot / (n_got * n_ref) ** 0.5
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 def to_dev(a: np.ndarray):
     import torch
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()

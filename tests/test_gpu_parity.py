@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from helpers import (cosine, from_dev_bf16, max_abs, normal_qkv, rel_close, sawtooth, sawtooth_mask, to_dev,
-                     to_dev_bf16)
+                     to_dev_bf16, torch_f32_attention_error)
 
 pytestmark = pytest.mark.gpu
 
@@ -442,9 +442,13 @@ def test_bf16_config2_full_size_sampled_and_properties(ops, oracle_lib):
     torch.cuda.synchronize()
     assert ops.last_status(None) == 0
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), "two launches must be bit-identical"
-    rows = [0, 1, 127, 128, 129, 2047, 2048, 4095]
-    worst, cos_min = _sample_check(oracle_lib, q, k, v, out, True, [(0, 0), (3, 17), (7, 31)], rows, H, H)
+    rows = [0, 1, 2, 5, 63, 64, 127, 128, 129, 255, 256, 1000, 2047, 2048, 3071, 4095]
+    pairs = [(0, 0), (1, 5), (2, 30), (3, 17), (4, 8), (5, 23), (6, 12), (7, 31)]
+    worst, cos_min = _sample_check(oracle_lib, q, k, v, out, True, pairs, rows, H, H)
     assert worst <= 2e-2 and cos_min >= 0.999
+    # the whole tensor: every row of all 256 pairs against float32 attention on the same GPU
+    per_row, cos_all = torch_f32_attention_error(q, k, v, out, True)
+    assert per_row.max() <= 2e-2 and cos_all >= 0.9999, (per_row.max(), cos_all)
     # size-independent properties: doubling V doubles O exactly (power of two), and every output lies
     # inside the per-channel range of its head's V (softmax weights are a convex combination)
     outd = ops.attn_forward("bf16", q, k, v * 2, None, True)
@@ -473,9 +477,13 @@ def test_sage_config3_full_size_sampled_and_properties(ops, oracle_lib):
     out2 = ops.attn_forward("sage", q, k, v, None, False, workspace=ws)
     torch.cuda.synchronize()
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
-    rows = [0, 127, 128, 4095, 4096, 8191]
-    worst, cos_min = _sample_check(oracle_lib, q, k, v, out, False, [(0, 0), (2, 9), (3, 31)], rows, H, H)
+    rows = [0, 1, 127, 128, 129, 1000, 4095, 4096, 6000, 8064, 8190, 8191]
+    pairs = [(0, 0), (0, 21), (1, 7), (1, 30), (2, 9), (2, 16), (3, 3), (3, 31)]
+    worst, cos_min = _sample_check(oracle_lib, q, k, v, out, False, pairs, rows, H, H)
     assert worst <= 2e-2 and cos_min >= 0.999
+    # the whole tensor: every row of all 128 pairs against float32 attention on the same GPU
+    per_row, cos_all = torch_f32_attention_error(q, k, v, out, False)
+    assert per_row.max() <= 2e-2 and cos_all >= 0.9995, (per_row.max(), cos_all)
     # INT8 tensors and scales of sampled heads: bit-exact against the oracle prologue
     q8, k8, qs, ks, km = ops.sage_quantize(q, k, True)
     torch.cuda.synchronize()
