@@ -31,6 +31,7 @@ SYMBOLS = (
     "ar_attn_workspace_bytes",
     "ar_attn_forward",
     "ar_attn_forward_replicated",
+    "ar_attn_forward_reporting",
     "ar_attn_forward_strided",
     "ar_attn_train_forward",
     "ar_attn_train_workspace_bytes",
@@ -41,6 +42,7 @@ SYMBOLS = (
     "ar_sage_quantize_fp8",
     "ar_sage_attention_prequantized",
     "ar_sage_attention_prequantized_replicated",
+    "ar_sage_attention_prequantized_reporting",
     "ar_sage_attention_prequantized_fp8",
     "ar_sage_forward_static",
     "ar_attn_last_status",
@@ -80,6 +82,12 @@ def load() -> ctypes.CDLL:
     L.ar_attn_forward_replicated.restype = ci
     L.ar_sage_attention_prequantized_replicated.argtypes = [p, p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]
     L.ar_sage_attention_prequantized_replicated.restype = ci
+    L.ar_sage_attention_prequantized_reporting.argtypes = [p, p, p, p, p, p, ci, p, p, ctypes.c_uint32, p, i64, i64, i64, i64,
+                                                           i64, ci, p, p]
+    L.ar_sage_attention_prequantized_reporting.restype = ci
+    L.ar_attn_forward_reporting.argtypes = [ci, ci, p, p, p, p, p, p, ctypes.c_uint32, p, i64, i64, i64, i64, i64, ci, p,
+                                            ctypes.c_size_t, p]
+    L.ar_attn_forward_reporting.restype = ci
     L.ar_attn_forward_strided.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, p, p, p, p, ctypes.c_size_t, p]
     L.ar_attn_forward_strided.restype = ci
     L.ar_attn_train_forward.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p]

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <nccl.h>
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -27,7 +28,24 @@ struct Comm {
   cudaEvent_t ring[kEvents] = {};
   int next_event = 0;
   bool side_dirty = false;
+  // progressive form: per-pair counters on the device, flags in mapped host memory, the epoch last handed out
+  uint32_t* pair_count = nullptr;
+  uint32_t* pair_flag_host = nullptr;
+  uint32_t* pair_flag_dev = nullptr;
+  int64_t report_pairs = 0;
+  uint32_t epoch = 0;
+  cudaEvent_t launch_done = nullptr;
 };
+void free_reports(Comm* c) {
+  if (c->pair_count) cudaFree(c->pair_count);
+  if (c->pair_flag_host) cudaFreeHost(c->pair_flag_host);
+  if (c->launch_done) cudaEventDestroy(c->launch_done);
+  c->pair_count = nullptr;
+  c->pair_flag_host = nullptr;
+  c->pair_flag_dev = nullptr;
+  c->launch_done = nullptr;
+  c->report_pairs = 0;
+}
 bool cuda_ok(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return true;
   g_err = std::string(what) + ": " + cudaGetErrorString(e);
@@ -201,6 +219,96 @@ int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream)
   return 0;
 }
 
+int ar_gather_p2p_reports(void* comm, int64_t n_pairs, uint32_t** pair_count, uint32_t** pair_flag) {
+  if (!comm || !pair_count || !pair_flag || n_pairs <= 0) return -2;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->local) return -5;
+  if (n_pairs > c->report_pairs) {
+    if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return -6;
+    free_reports(c);
+    const size_t bytes = (size_t)n_pairs * sizeof(uint32_t);
+    void* dev_view = nullptr;
+    const bool ok = cuda_ok(cudaMalloc((void**)&c->pair_count, bytes), "cudaMalloc") &&
+                    cuda_ok(cudaMemset(c->pair_count, 0, bytes), "cudaMemset") &&
+                    cuda_ok(cudaHostAlloc((void**)&c->pair_flag_host, bytes, cudaHostAllocMapped), "cudaHostAlloc") &&
+                    cuda_ok(cudaHostGetDevicePointer(&dev_view, c->pair_flag_host, 0), "cudaHostGetDevicePointer") &&
+                    cuda_ok(cudaEventCreateWithFlags(&c->launch_done, cudaEventDisableTiming), "cudaEventCreate");
+    if (!ok) {
+      free_reports(c);
+      return -6;
+    }
+    std::memset(c->pair_flag_host, 0, bytes);
+    c->pair_flag_dev = static_cast<uint32_t*>(dev_view);
+    c->report_pairs = n_pairs;
+  }
+  *pair_count = c->pair_count;
+  *pair_flag = c->pair_flag_dev;
+  return 0;
+}
+
+uint32_t ar_gather_p2p_next_epoch(void* comm) {
+  if (!comm) return 0;
+  Comm* c = static_cast<Comm*>(comm);
+  if (++c->epoch == 0) c->epoch = 1;
+  return c->epoch;
+}
+
+int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_pair, int64_t n_pairs,
+                                   int64_t pairs_per_group, uint32_t epoch, void* cu_stream) {
+  if (!comm) return -2;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->local || !c->pair_flag_host || n_pairs <= 0 || n_pairs > c->report_pairs || pairs_per_group <= 0 ||
+      epoch == 0 || bytes_per_pair == 0)
+    return -5;
+  if (offset > c->bytes || (size_t)n_pairs > (c->bytes - offset) / bytes_per_pair) return -5;
+  if (!cuda_ok(cudaEventRecord(c->launch_done, (cudaStream_t)cu_stream), "cudaEventRecord")) return -6;
+  volatile const uint32_t* flag = c->pair_flag_host;
+  const auto t0 = std::chrono::steady_clock::now();
+  bool launch_over = false;
+  for (int64_t p0 = 0; p0 < n_pairs; p0 += pairs_per_group) {
+    const int64_t p1 = p0 + pairs_per_group < n_pairs ? p0 + pairs_per_group : n_pairs;
+    // the group's pairs, in any order of arrival
+    for (int64_t p = p0; p < p1; p++) {
+      uint32_t spins = 0;
+      while (flag[p] != epoch) {
+        if ((++spins & 0x3ff) != 0) continue;
+        if (!launch_over) {
+          const cudaError_t q = cudaEventQuery(c->launch_done);
+          if (q == cudaSuccess) {
+            launch_over = true;  // every flag the kernel was going to write is visible now: look once more
+            continue;
+          }
+          if (q != cudaErrorNotReady) {
+            cuda_ok(q, "cudaEventQuery");
+            return -6;
+          }
+        } else {
+          // the launch is over and this pair was never reported: it failed (a bounded wait ran out)
+          g_err = "ar_gather_p2p_push_progressive: the launch ended without reporting pair " + std::to_string(p);
+          return -7;
+        }
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) {
+          g_err = "ar_gather_p2p_push_progressive: no report within 30 s";
+          return -8;
+        }
+      }
+    }
+    if (c->world < 2) continue;
+    const size_t off = offset + (size_t)p0 * bytes_per_pair;
+    const size_t bytes = (size_t)(p1 - p0) * bytes_per_pair;
+    const char* src = static_cast<const char*>(c->local) + off;
+    for (int i = 1; i < c->world; i++) {
+      const int r = (c->rank + i) % c->world;
+      if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + off, src, bytes, cudaMemcpyDeviceToDevice,
+                                   c->side),
+                   "cudaMemcpyAsync(peer)"))
+        return -6;
+    }
+    c->side_dirty = true;
+  }
+  return 0;
+}
+
 int ar_gather_p2p_fence(void* comm, void* cu_stream) {
   if (!comm) return -2;
   Comm* c = static_cast<Comm*>(comm);
@@ -240,6 +348,7 @@ void ar_gather_p2p_close(void* comm) {  // (also the way out of a failed open: e
       cudaEventDestroy(c->ring[i]);
       c->ring[i] = nullptr;
     }
+  free_reports(c);
   cudaFree(c->local);
   c->local = nullptr;
   c->bytes = 0;

@@ -196,7 +196,7 @@ int ar_sage_quantize_fp8(const void* q, const void* k, int dtype, uint8_t* q8, u
 
 namespace {
 int forward_impl(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const ar::OutReplicas& reps,
-                 const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal,
+                 const ar::OutProgress& progress, const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal,
                  void* workspace, size_t workspace_bytes, void* cu_stream) {
   if (!q || !k || !v || !o) return AR_ERR_NULL;
   int rc = check_shape(B, Hq, Hkv, S, D);
@@ -211,6 +211,7 @@ int forward_impl(int mode, int dtype, const void* q, const void* k, const void* 
 
   if (reps.n > 0 && (mode == AR_MODE_EXACT_F32 || mode == AR_MODE_TF32 || dtype != AR_DTYPE_BF16))
     return AR_ERR_UNSUPPORTED;  // replicas receive bf16 rows of the tensor-core kernels
+  if (progress.count && mode == AR_MODE_EXACT_F32) return AR_ERR_UNSUPPORTED;  // reports come from the tensor-core kernel
   if (mode == AR_MODE_EXACT_F32) {
     ar::ExactArgs a{(const float*)q, (const float*)k, (const float*)v, (float*)o, mask,
                     (int)B, (int)Hq, (int)Hkv, (int)S, (int)D, causal};
@@ -236,6 +237,9 @@ int forward_impl(int mode, int dtype, const void* q, const void* k, const void* 
   a.status = status;
   a.sticky = sticky_ptr();
   a.replicas = reps;
+  a.progress = progress;
+  if (progress.count && cudaMemsetAsync(progress.count, 0, (size_t)(B * Hq) * sizeof(uint32_t), stream) != cudaSuccess)
+    return AR_ERR_CUDA;
   if (mode == AR_MODE_BF16) {
     a.mode = ar::TC_BF16;
     a.out_f32 = 0;
@@ -310,7 +314,29 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
                     size_t workspace_bytes, void* cu_stream) {
   ar::OutReplicas none;
   none.n = 0;
-  return forward_impl(mode, dtype, q, k, v, o, none, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes, cu_stream);
+  return forward_impl(mode, dtype, q, k, v, o, none, ar::OutProgress{nullptr, nullptr, 0}, mask, B, Hq, Hkv, S, D, causal,
+                      workspace, workspace_bytes, cu_stream);
+}
+
+namespace {
+bool progress_ok(uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch, ar::OutProgress* out) {
+  if (!pair_count || !pair_flag || epoch == 0) return false;
+  if (((uintptr_t)pair_count & 3u) != 0 || ((uintptr_t)pair_flag & 3u) != 0) return false;
+  *out = ar::OutProgress{pair_count, pair_flag, epoch};
+  return true;
+}
+}  // namespace
+
+int ar_attn_forward_reporting(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
+                              uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch, const float* mask, int64_t B,
+                              int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                              size_t workspace_bytes, void* cu_stream) {
+  ar::OutReplicas none;
+  none.n = 0;
+  ar::OutProgress progress;
+  if (!progress_ok(pair_count, pair_flag, epoch, &progress)) return AR_ERR_NULL;
+  return forward_impl(mode, dtype, q, k, v, o, none, progress, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes,
+                      cu_stream);
 }
 
 int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
@@ -319,7 +345,8 @@ int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k
                                void* cu_stream) {
   ar::OutReplicas reps;
   if (!replicas_ok(replicas, n_replicas, &reps)) return n_replicas > 7 ? AR_ERR_UNSUPPORTED : AR_ERR_ALIGNMENT;
-  return forward_impl(mode, dtype, q, k, v, o, reps, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes, cu_stream);
+  return forward_impl(mode, dtype, q, k, v, o, reps, ar::OutProgress{nullptr, nullptr, 0}, mask, B, Hq, Hkv, S, D, causal,
+                      workspace, workspace_bytes, cu_stream);
 }
 
 int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
@@ -486,7 +513,8 @@ int ar_attn_train_backward_tc(const float* q, const float* k, const float* v, co
 
 namespace {
 int sage_prequantized_any(int mode, const void* q8, const void* k8, const float* q_scale, const float* k_scale,
-                          const void* v_bf16, void* o, const ar::OutReplicas& reps, int out_dtype, const float* mask,
+                          const void* v_bf16, void* o, const ar::OutReplicas& reps, const ar::OutProgress& progress,
+                          int out_dtype, const float* mask,
                           int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
                           void* cu_stream) {
   if (!q8 || !k8 || !q_scale || !k_scale || !v_bf16 || !o) return AR_ERR_NULL;
@@ -518,6 +546,9 @@ int sage_prequantized_any(int mode, const void* q8, const void* k8, const float*
   a.status = status;
   a.sticky = sticky_ptr();
   a.replicas = reps;
+  a.progress = progress;
+  if (progress.count && cudaMemsetAsync(progress.count, 0, (size_t)(B * Hq) * sizeof(uint32_t), stream) != cudaSuccess)
+    return AR_ERR_CUDA;
   if (!make_map(&a.tm_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hq, S, D) ||
       !make_map(&a.tm_k, k8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, Hkv, S, D) ||
       !make_map(&a.tm_v, v_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
@@ -536,8 +567,21 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    void* cu_stream) {
   ar::OutReplicas none;
   none.n = 0;
-  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, none, out_dtype, mask, B, Hq, Hkv, S,
-                               D, causal, status_word, cu_stream);
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, none,
+                               ar::OutProgress{nullptr, nullptr, 0}, out_dtype, mask, B, Hq, Hkv, S, D, causal, status_word,
+                               cu_stream);
+}
+int ar_sage_attention_prequantized_reporting(const int8_t* q8, const int8_t* k8, const float* q_scale,
+                                             const float* k_scale, const void* v_bf16, void* o, int out_dtype,
+                                             uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch,
+                                             const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                                             int causal, void* status_word, void* cu_stream) {
+  ar::OutReplicas none;
+  none.n = 0;
+  ar::OutProgress progress;
+  if (!progress_ok(pair_count, pair_flag, epoch, &progress)) return AR_ERR_NULL;
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, none, progress, out_dtype, mask, B,
+                               Hq, Hkv, S, D, causal, status_word, cu_stream);
 }
 int ar_sage_attention_prequantized_replicated(const int8_t* q8, const int8_t* k8, const float* q_scale,
                                               const float* k_scale, const void* v_bf16, void* o, void* const* replicas,
@@ -545,8 +589,9 @@ int ar_sage_attention_prequantized_replicated(const int8_t* q8, const int8_t* k8
                                               int64_t S, int64_t D, int causal, void* status_word, void* cu_stream) {
   ar::OutReplicas reps;
   if (!replicas_ok(replicas, n_replicas, &reps)) return n_replicas > 7 ? AR_ERR_UNSUPPORTED : AR_ERR_ALIGNMENT;
-  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, reps, AR_DTYPE_BF16, mask, B, Hq, Hkv,
-                               S, D, causal, status_word, cu_stream);
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, reps,
+                               ar::OutProgress{nullptr, nullptr, 0}, AR_DTYPE_BF16, mask, B, Hq, Hkv, S, D, causal,
+                               status_word, cu_stream);
 }
 int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, const float* q_scale,
                                        const float* k_scale, const void* v_bf16, void* o, int out_dtype,
@@ -554,8 +599,9 @@ int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, con
                                        int causal, void* status_word, void* cu_stream) {
   ar::OutReplicas none;
   none.n = 0;
-  return sage_prequantized_any(AR_MODE_SAGE_FP8, q8, k8, q_scale, k_scale, v_bf16, o, none, out_dtype, mask, B, Hq, Hkv, S,
-                               D, causal, status_word, cu_stream);
+  return sage_prequantized_any(AR_MODE_SAGE_FP8, q8, k8, q_scale, k_scale, v_bf16, o, none,
+                               ar::OutProgress{nullptr, nullptr, 0}, out_dtype, mask, B, Hq, Hkv, S, D, causal, status_word,
+                               cu_stream);
 }
 
 int ar_attn_last_status(void* workspace, void* cu_stream) {

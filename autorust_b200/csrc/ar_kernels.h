@@ -16,6 +16,14 @@ struct OutReplicas {
   int n;
 };
 
+// Completion reports of a forward launch, for a host that moves finished output while the kernel is still running:
+// every CTA adds one to count[pair] (device memory, zero at launch) after its rows are visible system-wide, and the
+// CTA that brings the counter to the number of CTAs per pair writes `epoch` to flag[pair] (mapped host memory).
+struct OutProgress {
+  uint32_t* count;  // null: no reports
+  uint32_t* flag;
+  uint32_t epoch;
+};
 struct TcArgs {
   int mode;             // TcMode
   int D;                // 64 or 128
@@ -36,6 +44,7 @@ struct TcArgs {
   int B, Hq, Hkv, S;
   int causal;
   OutReplicas replicas; // bf16 output only
+  OutProgress progress;
   uint32_t* status;     // the launch's device status word: zero at launch, set when a bounded wait ran out
   uint32_t* sticky;     // the library's accumulator of the same bits (nullable)
 };

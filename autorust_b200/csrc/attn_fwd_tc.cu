@@ -316,7 +316,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
                    int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
-                   const OutReplicas reps, uint32_t* status, uint32_t* sticky) {
+                   const OutReplicas reps, const OutProgress progress, uint32_t* status, uint32_t* sticky) {
   using C = Cfg<MODE, D, TILES>;
   constexpr int ST = C::STAGES;
   constexpr int W_PROD = 4 * TILES;     // warp that loads
@@ -697,6 +697,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (warp == W_MMA) tmem_dealloc(tb, 256 * TILES);
+  if (progress.count != nullptr && tid == 0 && *abort_flag == 0) {
+    // Completion report.  The barrier above orders every thread's output rows before this thread, and a release
+    // is cumulative: the rows are visible device-wide (in L2, where this GPU's copy engines read) before the CTA is
+    // counted.  The pair's last CTA acquires the others' counts and releases the flag to the host.
+    uint32_t before;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(progress.count + bh) : "memory");
+    if (before + 1u == gridDim.x)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(progress.flag + bh), "r"(progress.epoch) : "memory");
+  }
 }
 
 template <int MODE, int D, int TILES, bool ROWS = false>
@@ -716,7 +725,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   kern<<<grid, Shape<TILES>::NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale,
                                                                    a.k_scale, a.S, a.Hq, a.Hkv, a.causal, a.out_f32,
                                                                    a.token_major, a.o_sb, a.o_sh, a.o_ss, a.replicas,
-                                                                   a.status, a.sticky);
+                                                                   a.progress, a.status, a.sticky);
   return cudaGetLastError();
 }
 

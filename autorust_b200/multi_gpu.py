@@ -81,6 +81,10 @@ def load() -> ctypes.CDLL:
     L.ar_gather_p2p_peer.argtypes = [p, ci]
     L.ar_gather_p2p_peer.restype = p
     L.ar_gather_p2p_push.argtypes = [p, ctypes.c_size_t, ctypes.c_size_t, p]
+    L.ar_gather_p2p_reports.argtypes = [p, i64, ctypes.POINTER(p), ctypes.POINTER(p)]
+    L.ar_gather_p2p_next_epoch.argtypes = [p]
+    L.ar_gather_p2p_next_epoch.restype = ctypes.c_uint32
+    L.ar_gather_p2p_push_progressive.argtypes = [p, ctypes.c_size_t, ctypes.c_size_t, i64, i64, ctypes.c_uint32, p]
     L.ar_gather_p2p_fence.argtypes = [p, p]
     L.ar_gather_p2p_close.argtypes = [p]
     L.ar_gather_p2p_close.restype = None
@@ -180,6 +184,29 @@ class Gather:
         rc = load().ar_gather_p2p_push(self._h, off, part.numel() * part.element_size(), s.cuda_stream)
         if rc != 0:
             raise RuntimeError("ar_gather_p2p_push: " + load().ar_gather_last_error().decode())
+
+    def p2p_reports(self, n_pairs: int):
+        """(pair_count, pair_flag, epoch) for the next reporting launch over `n_pairs` (batch, head) pairs: the words
+        the attention entry points take as `reports`, with a fresh epoch."""
+        count, flag = ctypes.c_void_p(), ctypes.c_void_p()
+        if load().ar_gather_p2p_reports(self._h, n_pairs, ctypes.byref(count), ctypes.byref(flag)) != 0:
+            raise RuntimeError("ar_gather_p2p_reports: " + load().ar_gather_last_error().decode())
+        return count.value, flag.value, int(load().ar_gather_p2p_next_epoch(self._h))
+
+    def p2p_push_progressive(self, part, reports, pairs_per_group: int = 4, stream=None) -> None:
+        """Right after a launch that writes `part` (this rank's [pairs, S, D]-shaped piece of the tensor p2p_open
+        returned) and reports with `reports`: watches the reports and queues every finished group of pairs to the
+        peers' copy engines while the kernel runs.  Returns when the last group is queued."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        if not part.is_contiguous():
+            raise ValueError("p2p_push_progressive: the piece must be contiguous")
+        n_pairs = part.numel() // (part.shape[-1] * part.shape[-2])
+        off = part.data_ptr() - self._p2p.data_ptr()
+        rc = load().ar_gather_p2p_push_progressive(self._h, off, part.shape[-1] * part.shape[-2] * part.element_size(),
+                                                   n_pairs, pairs_per_group, reports[2], s.cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"ar_gather_p2p_push_progressive ({rc}): " + load().ar_gather_last_error().decode())
 
     def p2p_fence(self, stream=None) -> None:
         """Collective.  After this point of `stream`, every push queued by any rank before its own fence has

@@ -74,12 +74,15 @@ def _replica_array(replicas):
 
 def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None = None,
                  causal: bool = False, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                 stream: torch.cuda.Stream | None = None, replicas=None) -> torch.Tensor:
+                 stream: torch.cuda.Stream | None = None, replicas=None, reports=None) -> torch.Tensor:
     """o = softmax(q k^T / sqrt(D) + mask) v through ar_attn_forward, asynchronously on `stream`
     (default: torch's current stream).  `workspace` is a uint8 CUDA tensor of at least
     workspace_bytes(); one is allocated when the mode needs it and none is given.
     `replicas`: device addresses of further buffers (e.g. peers' buffers mapped into this process) that receive the
-    same bf16 output rows at the same offsets (ar_attn_forward_replicated)."""
+    same bf16 output rows at the same offsets (ar_attn_forward_replicated).
+    `reports` = (pair_count, pair_flag, epoch): device addresses of B * Hq counters and of B * Hq host-visible flags;
+    the kernel writes `epoch` to a pair's flag as soon as all of its output rows are visible
+    (ar_attn_forward_reporting)."""
     L = _abi.load()
     _check_qkv(q, k, v)
     m = mode_code(mode)
@@ -99,7 +102,12 @@ def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
         tail = (mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal),
                 workspace.data_ptr() if workspace is not None else None,
                 workspace.numel() * workspace.element_size() if workspace is not None else 0, s.cuda_stream)
-        if nrep:
+        if reports is not None:
+            if nrep:
+                raise TypeError("completion reports and replicas exclude each other")
+            rc = L.ar_attn_forward_reporting(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                             reports[0], reports[1], reports[2], *tail)
+        elif nrep:
             rc = L.ar_attn_forward_replicated(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                               reps, nrep, *tail)
         else:
@@ -222,9 +230,10 @@ def sage_quantize(q: torch.Tensor, k: torch.Tensor, smooth: bool = True, stream=
 
 
 def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None, causal=False, stream=None,
-                                out_dtype=torch.bfloat16, replicas=None):
+                                out_dtype=torch.bfloat16, replicas=None, reports=None):
     """The Sage attention kernel alone, on the tensors sage_quantize returned (v must be bf16); uint8 q8 / k8
-    (the FP8 prologue's output) select the FP8 kernel."""
+    (the FP8 prologue's output) select the FP8 kernel.  reports = (pair_count, pair_flag, epoch): device addresses
+    and epoch of the completion reports per (batch, head) pair (INT8 operands)."""
     L = _abi.load()
     B, Hq, S, D = q8.shape
     Hkv = k8.shape[1]
@@ -245,7 +254,14 @@ def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None
     with torch.cuda.device(q8.device):
         s = stream if stream is not None else torch.cuda.current_stream()
         reps, nrep = _replica_array(replicas)
-        if nrep:
+        if reports is not None:
+            if q8.dtype == torch.uint8 or nrep:
+                raise TypeError("completion reports: INT8 operands, no replicas")
+            rc = L.ar_sage_attention_prequantized_reporting(
+                q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v.data_ptr(), out.data_ptr(),
+                _dtype_code(out), reports[0], reports[1], reports[2], mask.data_ptr() if mask is not None else None, B, Hq,
+                Hkv, S, D, int(causal), None, s.cuda_stream)
+        elif nrep:
             if q8.dtype == torch.uint8 or out.dtype != torch.bfloat16:
                 raise TypeError("replicated output: INT8 operands and a bfloat16 output")
             rc = L.ar_sage_attention_prequantized_replicated(

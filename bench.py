@@ -339,7 +339,8 @@ def long_context_slab(torch, device, pair_begin: int, pair_end: int):
     return q, k, v
 
 
-def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=True, fused=True, steps=3) -> dict:
+def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=True, fused=True, progressive=False,
+                     steps=3) -> dict:
     """Benchmark configuration 5: ONE global tensor B=16, H=64, S=16384, D=128, causal Sage, cut over the ranks
     along the flattened (batch, head) axis (1024 pairs -> 1024 / N per rank, strong scaling); every rank ends up
     with the whole bf16 output.  The inputs of pair p depend on p alone (a generator seeded per group of 8 pairs),
@@ -374,11 +375,18 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
     if not p2p:
         full = torch.empty((world, n_local, S, D), dtype=torch.bfloat16, device=device)
     fused = fused and p2p
-    npieces = 8 if (p2p and not fused) else 1
+    progressive = progressive and p2p
+    npieces = 8 if (p2p and not fused and not progressive) else 1
     per = n_local // npieces
+    group = max(1, n_local // 32)  # pairs handed to the copy engines at once by the progressive form
 
-    def compute(h0, h1, replicate=False):
-        if replicate:
+    def compute(h0, h1, replicate=False, reports=None):
+        if reports is not None:
+            rc = L.ar_sage_attention_prequantized_reporting(
+                q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(), ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(),
+                full[rank, h0:h1].data_ptr(), _abi.DTYPE_BF16, reports[0], reports[1], reports[2], None, 1, h1 - h0,
+                h1 - h0, S, D, 1, None, stream.cuda_stream)
+        elif replicate:
             reps = gather.p2p_replicas(full[rank, h0:h1])
             arr = (ctypes.c_void_p * len(reps))(*reps)
             rc = L.ar_sage_attention_prequantized_replicated(
@@ -395,6 +403,12 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
         rc = L.ar_sage_quantize(q.data_ptr(), k.data_ptr(), _abi.DTYPE_BF16, q8.data_ptr(), k8.data_ptr(), qs.data_ptr(),
                                 ks.data_ptr(), km.data_ptr(), 1, n_local, n_local, S, D, 128, 1, stream.cuda_stream)
         _abi.check(rc, "ar_sage_quantize")
+        if with_gather and progressive:
+            reports = gather.p2p_reports(n_local)
+            compute(0, n_local, reports=reports)
+            gather.p2p_push_progressive(full[rank], reports, pairs_per_group=group, stream=stream)
+            gather.p2p_fence(stream)
+            return
         for i in range(npieces):
             h0, h1 = i * per, (i + 1) * per if i + 1 < npieces else n_local
             compute(h0, h1, replicate=with_gather and fused)
@@ -447,7 +461,9 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
            "ms_per_step_excluding_gather": ms_compute, "tops_excluding_gather": ops / (ms_compute * 1e-3) / 1e12,
            "ms_per_step_including_gather": ms_total, "tops_including_gather": ops / (ms_total * 1e-3) / 1e12,
            "gather_bytes_received_per_rank": (world - 1) * n_local * S * D * 2,
-           "gather": ("stored into every rank's buffer by the attention kernel's epilogue" if fused else
+           "gather": (f"finished groups of {group} pairs, reported by the kernel while it runs, pushed by the copy engines "
+                      "under the rest of the kernel" if progressive else
+                      "stored into every rank's buffer by the attention kernel's epilogue" if fused else
                       "peer-to-peer copies on the copy engines, 8 pieces under the following pieces' kernels" if p2p
                       else "NCCL all-gather in place after the kernel") if world > 1 else None,
            "gather_verified": bool(ok) if world > 1 else None, "output_checksum": checksum,
@@ -489,7 +505,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1:
         from autorust_b200 import multi_gpu
         gather = multi_gpu.Gather(rank, world, local_rank)  # NCCL communicator of libar_gather.so
-        if args.gather in ("fused", "p2p"):
+        if args.gather in ("progressive", "fused", "p2p"):
             # copy-engine gather: this rank's outputs land in gathered[rank] and are pushed to the peers piece by piece.
             # Every rank has to have its peers mapped; if one could not, all of them take the NCCL form.
             try:
@@ -506,8 +522,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     # N > 1, copy-engine gather: pieces of the flattened (batch, head) axis, each a whole number of waves of CTAs
     # as far as possible, with a short last piece so that little is left to push when the step's last kernel ends.
     fused = p2p and args.gather == "fused"
+    progressive = p2p and args.gather == "progressive"
+    group = max(1, (B * H) // 32)  # pairs handed to the copy engines at once by the progressive form
     pieces = []
-    if p2p and not fused:
+    if p2p and not fused and not progressive:
         import math
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         ctas_per_head = (S + 255) // 256                      # one CTA per pair of 128-row query tiles
@@ -576,12 +594,35 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             e1.record(stream)
             kernel_events.append((e0, e1, B))
 
+    def attend_reporting(record):
+        """The attention kernel over the whole batch, written into this rank's gather buffer; it reports every
+        finished (batch, head) pair to the host, which hands finished groups to the copy engines while it runs."""
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        reports = gather.p2p_reports(B * H)
+        rc = L.ar_sage_attention_prequantized_reporting(q8.data_ptr(), k8.data_ptr(), qs.data_ptr(), ks.data_ptr(),
+                                                        v.data_ptr(), gathered[rank].data_ptr(), _abi.DTYPE_BF16,
+                                                        reports[0], reports[1], reports[2], None, B, H, H, S, D,
+                                                        int(w["causal"]), None, stream.cuda_stream)
+        _abi.check(rc, "ar_sage_attention_prequantized_reporting")
+        if record:
+            e1.record(stream)
+            kernel_events.append((e0, e1, B))
+        gather.p2p_push_progressive(gathered[rank], reports, pairs_per_group=group, stream=stream)
+
     def step(record=False):
         """Prologue + attention over this rank's batch (the two C-ABI calls ar_attn_forward makes for
         the Sage mode, issued apart so the attention kernel can be bracketed by events)."""
         if world == 1:
             quantise(0, B)
             attend(0, B, record)
+            return
+        if progressive:
+            quantise(0, B)
+            attend_reporting(record)
+            gather.p2p_fence(stream)
             return
         if fused:
             quantise(0, B)
@@ -725,7 +766,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         gather.p2p_close()
     long_context = None
     if not args.no_long_context:
-        long_context = long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=p2p, fused=fused)
+        long_context = long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=p2p, fused=fused,
+                                        progressive=progressive)
 
     if rank == 0:
         line = {
@@ -734,7 +776,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
             "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (benchmark configuration 3)",
                        **w, "global_batch": B * world, "partition": ("one batch of B per rank (independent (batch, head) pairs, no reduction); bf16 "
-                       "outputs gathered on every rank " + ("by the attention kernel itself: its epilogue stores every row "
+                       "outputs gathered on every rank " + (f"by the copy engines under the kernel: the kernel reports every "
+                       f"finished (batch, head) pair to the host while it runs, and a host thread queues each finished group "
+                       f"of {group} pairs as peer-to-peer copies at once (CUDA IPC over NVLink), closed by a 4-byte NCCL "
+                       "all-reduce" if progressive else "by the attention kernel itself: its epilogue stores every row "
                        "into the same place of every rank's buffer (peers mapped by CUDA IPC over NVLink; plain stores), "
                        "closed by a 4-byte NCCL all-reduce" if fused else "piece by piece (37, 37, 37, 9, 8 heads: whole "
                        "waves of CTAs, short tail) under the next piece's kernel, by peer-to-peer copies on the copy engines "
@@ -762,7 +807,7 @@ def main() -> None:
     ap.add_argument("--no-vit", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the bf16_fwd and config2 legs")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=16 H=64 S=16384 causal leg")
-    ap.add_argument("--gather", default="fused", choices=["fused", "p2p", "nccl"],
+    ap.add_argument("--gather", default="fused", choices=["fused", "progressive", "p2p", "nccl"],
                     help="N > 1: how the output slabs reach the other ranks (stored by the attention kernel's epilogue, "
                          "pushed by the copy engines, or NCCL's all-gather kernels)")
     args = ap.parse_args()

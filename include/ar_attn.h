@@ -120,6 +120,18 @@ int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k
  * Strided tensors are taken by AR_MODE_BF16 (all loads are TMA tiles); with dense strides every mode is accepted and
  * the call is ar_attn_forward.  Every stride times the element size must be a multiple of 16 bytes
  * (AR_ERR_ALIGNMENT otherwise). */
+/* ar_attn_forward that reports, while it runs, which (batch, head) pairs of the output are finished -- for a host
+ * that moves finished pairs elsewhere (to the other GPUs of a head-parallel run, include/ar_attn_gather.h's
+ * progressive push) under the rest of the kernel.  pair_count: B * Hq words of DEVICE memory for the kernel's own
+ * use (the call zeroes them on the stream; one launch at a time per set of words).  pair_flag: B * Hq words
+ * the HOST can read while the kernel runs (mapped pinned memory, as the device sees it).  When every output row of
+ * pair p is visible system-wide the kernel writes `epoch` (non-zero, different from the previous launch's) to
+ * pair_flag[p].  Tensor-core modes only.  No counterpart in the reference, which is single-device. */
+int ar_attn_forward_reporting(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
+                              uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch, const float* mask, int64_t B,
+                              int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                              size_t workspace_bytes, void* cu_stream);
+
 int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
                             int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, const int64_t* q_strides,
                             const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
@@ -187,6 +199,13 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    const void* v_bf16, void* o, int out_dtype, const float* mask, int64_t B,
                                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
                                    void* cu_stream);
+
+/* ar_sage_attention_prequantized with completion reports per (batch, head) pair (see ar_attn_forward_reporting). */
+int ar_sage_attention_prequantized_reporting(const int8_t* q8, const int8_t* k8, const float* q_scale,
+                                             const float* k_scale, const void* v_bf16, void* o, int out_dtype,
+                                             uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch,
+                                             const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                                             int causal, void* status_word, void* cu_stream);
 
 /* ar_sage_attention_prequantized with a bf16 output that is also stored into `replicas` (see
  * ar_attn_forward_replicated). */

@@ -43,13 +43,18 @@ int ar_gather_allgather_into(void* comm, const void* send, void* recv, int64_t e
  * NCCL's all-gather kernels take SMs, and the attention kernel fills an SM with each CTA, so a gather that runs
  * beside the next chunk's attention costs that chunk the SMs NCCL holds.  Here every rank owns one buffer of the
  * gathered size and the buffers are mapped into each other's address spaces once (CUDA IPC over the NVLink peers).
- * Two ways to fill them:
+ * Three ways to fill them:
  *   fused       the attention kernel itself stores every finished output row into the local buffer AND into each
  *               peer's (ar_attn_forward_replicated / ar_sage_attention_prequantized_replicated of ar_attn.h, given
  *               ar_gather_p2p_peer's addresses): the slab leaves over the whole length of the kernel and nothing is
  *               left to move when it ends;
  *   copy engine the kernel writes its slab into the local buffer and ar_gather_p2p_push queues world - 1
- *               peer-to-peer cudaMemcpyAsync calls behind it.
+ *               peer-to-peer cudaMemcpyAsync calls behind it;
+ *   progressive the kernel writes its slab into the local buffer and reports every finished (batch, head) pair to
+ *               the host while it runs (ar_attn_forward_reporting / ar_sage_attention_prequantized_reporting);
+ *               ar_gather_p2p_push_progressive, called right after the launch, watches the reports and hands each
+ *               finished group of pairs to the copy engines at once.  The slab crosses NVLink at copy-engine rate
+ *               under the kernel, which gives no SM time to it; what is left after the kernel is one group.
  * NCCL remains the control plane: it ships the IPC handles and closes a round (ar_gather_p2p_fence: a 4-byte
  * all-reduce queued behind the stores or copies).
  * Reuse of the buffers: a rank may start the NEXT round's stores into its peers as soon as its own fence has passed,
@@ -74,6 +79,24 @@ void* ar_gather_p2p_peer(void* comm, int rank);
  * a stream of the library's own, one peer after the other (measured faster on eight GPUs than several peers at
  * once); ar_gather_p2p_fence joins them back into `cu_stream`. */
 int ar_gather_p2p_push(void* comm, size_t offset, size_t bytes, void* cu_stream);
+
+/* The words the progressive form needs, for up to `n_pairs` (batch, head) pairs of this rank's slab: device
+ * counters and flags in mapped host memory, both as the DEVICE addresses the attention entry point
+ * takes.  Valid until ar_gather_p2p_close; a later call with a larger n_pairs replaces them.  0 on success. */
+int ar_gather_p2p_reports(void* comm, int64_t n_pairs, uint32_t** pair_count, uint32_t** pair_flag);
+
+/* A fresh non-zero epoch for the next reporting launch. */
+uint32_t ar_gather_p2p_next_epoch(void* comm);
+
+/* Call right after a reporting launch was queued on `cu_stream` with this comm's words and `epoch`: pair p of the
+ * launch lies at [offset + p * bytes_per_pair, + bytes_per_pair) of the local buffer.  The calling thread watches the
+ * flags and, group of `pairs_per_group` by group, queues the peer-to-peer copies of a group on the library's stream
+ * as soon as its last pair is reported.  Returns when the copies of the last group are queued (the kernel is then
+ * all but finished); ar_gather_p2p_fence joins them into `cu_stream`.  The watch is bounded: it ends when an event
+ * recorded behind the launch has completed (flags still missing then mean the launch failed: -7) or after 30 s
+ * (-8).  0 on success. */
+int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_pair, int64_t n_pairs,
+                                   int64_t pairs_per_group, uint32_t epoch, void* cu_stream);
 
 /* Queues on `cu_stream` the point after which everything that any rank queued before ITS fence -- pushes, or
  * kernels that store into the peers -- has landed in this rank's buffer.  Collective. */

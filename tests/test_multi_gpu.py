@@ -1,6 +1,7 @@
 """Head-parallel sharding: partition arithmetic, the N > 1 path on CPU ranks (gloo, world_size 2), a rank
-that never joins (host-side failure, no GPU involved), and -- on a box with two GPUs -- the three forms of the
-output gather (NCCL, copy engines, stored by the attention kernel itself) against the single-GPU result."""
+that never joins (host-side failure, no GPU involved), and -- on a box with two GPUs -- the four forms of the
+output gather (NCCL, copy engines, stored by the attention kernel itself, copy engines fed by the kernel's
+completion reports) against the single-GPU result."""
 from __future__ import annotations
 
 import datetime
@@ -149,7 +150,26 @@ def _gpu_rank(rank, world, port, seed, result):
         fused_ok = fused_ok and torch.equal(buf.reshape(B * H, S, D).view(torch.int16),
                                             ref_m.reshape(B * H, S, D).view(torch.int16))
         dist.barrier()  # nobody stores the next mode's rows while a peer still compares
-    p2p_ok = p2p_ok and fused_ok
+    # the progressive form: the kernel reports finished pairs to the host while it runs, the host hands each finished
+    # group to the copy engines at once
+    progressive_ok = True
+    for mode, group in (("bf16", 1), ("sage", 3), ("bf16", 64)):
+        buf.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        mine = buf[rank].view(1, hq_local, S, D)
+        reports = gather.p2p_reports(hq_local)
+        ops.attn_forward(mode, q[sh.q_begin:sh.q_end].view(1, hq_local, S, D), k[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D),
+                         v[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D), None, True, out=mine, reports=reports)
+        gather.p2p_push_progressive(buf[rank], reports, pairs_per_group=group)
+        gather.p2p_fence()
+        torch.cuda.synchronize()
+        ref_m = ops.attn_forward(mode, q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
+        torch.cuda.synchronize()
+        progressive_ok = progressive_ok and torch.equal(buf.reshape(B * H, S, D).view(torch.int16),
+                                                        ref_m.reshape(B * H, S, D).view(torch.int16))
+        dist.barrier()
+    p2p_ok = p2p_ok and fused_ok and progressive_ok
     flags = [None] * world
     dist.all_gather_object(flags, bool(p2p_ok))
     if rank == 0:
