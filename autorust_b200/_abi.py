@@ -11,6 +11,7 @@ LIB_DIR = Path(__file__).resolve().parent / "lib"
 
 MODE_EXACT_F32, MODE_TF32, MODE_BF16, MODE_SAGE_INT8, MODE_SAGE_FP8, MODE_SAGE_INT8_ROWS = 0, 1, 2, 3, 4, 5
 DTYPE_F32, DTYPE_BF16 = 0, 1
+REPLICAS_MULTICAST = -1  # n_replicas: replicas[0] is one address of an NVLink multicast object
 
 AR_OK = 0
 AR_ERR_UNSUPPORTED = -1
@@ -82,11 +83,11 @@ def load() -> ctypes.CDLL:
     L.ar_attn_forward_replicated.restype = ci
     L.ar_sage_attention_prequantized_replicated.argtypes = [p, p, p, p, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, p, p]
     L.ar_sage_attention_prequantized_replicated.restype = ci
-    L.ar_sage_attention_prequantized_reporting.argtypes = [p, p, p, p, p, p, ci, p, p, ctypes.c_uint32, p, i64, i64, i64, i64,
-                                                           i64, ci, p, p]
+    L.ar_sage_attention_prequantized_reporting.argtypes = [p, p, p, p, p, p, ci, p, ci, p, p, ctypes.c_uint32, p, i64, i64,
+                                                           i64, i64, i64, ci, p, p]
     L.ar_sage_attention_prequantized_reporting.restype = ci
-    L.ar_attn_forward_reporting.argtypes = [ci, ci, p, p, p, p, p, p, ctypes.c_uint32, p, i64, i64, i64, i64, i64, ci, p,
-                                            ctypes.c_size_t, p]
+    L.ar_attn_forward_reporting.argtypes = [ci, ci, p, p, p, p, p, ci, p, p, ctypes.c_uint32, p, i64, i64, i64, i64, i64, ci,
+                                            p, ctypes.c_size_t, p]
     L.ar_attn_forward_reporting.restype = ci
     L.ar_attn_forward_strided.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, p, p, p, p, ctypes.c_size_t, p]
     L.ar_attn_forward_strided.restype = ci

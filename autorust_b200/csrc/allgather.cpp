@@ -25,6 +25,9 @@ struct Comm {
   // the pushes go out on a stream of the library's own; events tie it to the caller's
   static constexpr int kEvents = 64;
   cudaStream_t side = nullptr;
+  static constexpr int kMaxCopyStreams = 8;
+  cudaStream_t more[kMaxCopyStreams] = {};  // further streams of the progressive copies (more[0] is `side`)
+  int n_copy_streams = 1;
   cudaEvent_t ring[kEvents] = {};
   int next_event = 0;
   bool side_dirty = false;
@@ -253,13 +256,25 @@ uint32_t ar_gather_p2p_next_epoch(void* comm) {
   return c->epoch;
 }
 
+int ar_gather_p2p_copy_streams(void* comm, int n) {
+  if (!comm) return -2;
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c->side || n < 1 || n > Comm::kMaxCopyStreams) return -5;
+  c->more[0] = c->side;
+  for (int i = 1; i < n; i++)
+    if (!c->more[i] && !cuda_ok(cudaStreamCreateWithFlags(&c->more[i], cudaStreamNonBlocking), "cudaStreamCreate")) return -6;
+  c->n_copy_streams = n;
+  return 0;
+}
+
 int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_pair, int64_t n_pairs,
-                                   int64_t pairs_per_group, uint32_t epoch, void* cu_stream) {
+                                   int64_t pairs_per_group, uint32_t epoch, int first_peer, void* cu_stream) {
   if (!comm) return -2;
   Comm* c = static_cast<Comm*>(comm);
   if (!c->local || !c->pair_flag_host || n_pairs <= 0 || n_pairs > c->report_pairs || pairs_per_group <= 0 ||
-      epoch == 0 || bytes_per_pair == 0)
+      epoch == 0 || bytes_per_pair == 0 || first_peer < 1 || first_peer > c->world)
     return -5;
+  c->more[0] = c->side;
   if (offset > c->bytes || (size_t)n_pairs > (c->bytes - offset) / bytes_per_pair) return -5;
   if (!cuda_ok(cudaEventRecord(c->launch_done, (cudaStream_t)cu_stream), "cudaEventRecord")) return -6;
   volatile const uint32_t* flag = c->pair_flag_host;
@@ -297,14 +312,21 @@ int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_p
     const size_t off = offset + (size_t)p0 * bytes_per_pair;
     const size_t bytes = (size_t)(p1 - p0) * bytes_per_pair;
     const char* src = static_cast<const char*>(c->local) + off;
-    for (int i = 1; i < c->world; i++) {
+    for (int i = first_peer; i < c->world; i++) {
       const int r = (c->rank + i) % c->world;
       if (!cuda_ok(cudaMemcpyAsync(static_cast<char*>(c->peer[(size_t)r]) + off, src, bytes, cudaMemcpyDeviceToDevice,
-                                   c->side),
+                                   c->more[i % c->n_copy_streams]),
                    "cudaMemcpyAsync(peer)"))
         return -6;
+      c->side_dirty = true;
     }
-    c->side_dirty = true;
+  }
+  // the further streams join the first one, which the fence joins into the caller's
+  for (int i = 1; i < c->n_copy_streams && c->side_dirty; i++) {
+    cudaEvent_t done = c->ring[c->next_event];
+    c->next_event = (c->next_event + 1) % Comm::kEvents;
+    if (!cuda_ok(cudaEventRecord(done, c->more[i]), "cudaEventRecord")) return -6;
+    if (!cuda_ok(cudaStreamWaitEvent(c->side, done, 0), "cudaStreamWaitEvent")) return -6;
   }
   return 0;
 }
@@ -312,7 +334,11 @@ int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_p
 int ar_gather_p2p_fence(void* comm, void* cu_stream) {
   if (!comm) return -2;
   Comm* c = static_cast<Comm*>(comm);
-  if (!c->fence_word) return -5;
+  if (!c->fence_word) {  // (a fence without opened buffers: rounds whose stores went through a multicast object)
+    if (!cuda_ok(cudaMalloc((void**)&c->fence_word, sizeof(int)), "cudaMalloc") ||
+        !cuda_ok(cudaMemset(c->fence_word, 0, sizeof(int)), "cudaMemset"))
+      return -6;
+  }
   // the caller's stream first collects the side streams' copies
   if (c->side_dirty) {
     cudaEvent_t done = c->ring[c->next_event];
@@ -332,13 +358,27 @@ int ar_gather_p2p_fence(void* comm, void* cu_stream) {
 void ar_gather_p2p_close(void* comm) {  // (also the way out of a failed open: every member may be half set up)
   if (!comm) return;
   Comm* c = static_cast<Comm*>(comm);
-  if (!c->local) return;
+  if (!c->local) {
+    if (c->fence_word) {
+      cudaDeviceSynchronize();
+      cudaFree(c->fence_word);
+      c->fence_word = nullptr;
+    }
+    return;
+  }
   cudaDeviceSynchronize();
   for (int r = 0; r < (int)c->peer.size(); r++)
     if (r != c->rank && c->peer[(size_t)r]) cudaIpcCloseMemHandle(c->peer[(size_t)r]);
   c->peer.clear();
   if (c->fence_word) cudaFree(c->fence_word);
   c->fence_word = nullptr;
+  for (int i = 1; i < Comm::kMaxCopyStreams; i++)
+    if (c->more[i]) {
+      cudaStreamDestroy(c->more[i]);
+      c->more[i] = nullptr;
+    }
+  c->more[0] = nullptr;
+  c->n_copy_streams = 1;
   if (c->side) {
     cudaStreamDestroy(c->side);
     c->side = nullptr;

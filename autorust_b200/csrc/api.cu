@@ -91,6 +91,14 @@ uint32_t* sticky_ptr() {
 
 bool replicas_ok(void* const* replicas, int n, ar::OutReplicas* out) {
   out->n = 0;
+  out->multicast = 0;
+  if (n == AR_REPLICAS_MULTICAST) {
+    if (!replicas || !replicas[0] || ((uintptr_t)replicas[0] & 15u) != 0) return false;
+    out->p[0] = replicas[0];
+    out->n = 1;
+    out->multicast = 1;
+    return true;
+  }
   if (n < 0 || n > 7 || (n > 0 && !replicas)) return false;
   for (int i = 0; i < n; i++) {
     if (!replicas[i] || ((uintptr_t)replicas[i] & 15u) != 0) return false;
@@ -314,6 +322,7 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
                     size_t workspace_bytes, void* cu_stream) {
   ar::OutReplicas none;
   none.n = 0;
+  none.multicast = 0;
   return forward_impl(mode, dtype, q, k, v, o, none, ar::OutProgress{nullptr, nullptr, 0}, mask, B, Hq, Hkv, S, D, causal,
                       workspace, workspace_bytes, cu_stream);
 }
@@ -328,14 +337,14 @@ bool progress_ok(uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch, ar::
 }  // namespace
 
 int ar_attn_forward_reporting(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
-                              uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch, const float* mask, int64_t B,
-                              int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
-                              size_t workspace_bytes, void* cu_stream) {
-  ar::OutReplicas none;
-  none.n = 0;
+                              void* const* replicas, int n_replicas, uint32_t* pair_count, uint32_t* pair_flag,
+                              uint32_t epoch, const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                              int causal, void* workspace, size_t workspace_bytes, void* cu_stream) {
+  ar::OutReplicas reps;
+  if (!replicas_ok(replicas, n_replicas, &reps)) return n_replicas > 7 ? AR_ERR_UNSUPPORTED : AR_ERR_ALIGNMENT;
   ar::OutProgress progress;
   if (!progress_ok(pair_count, pair_flag, epoch, &progress)) return AR_ERR_NULL;
-  return forward_impl(mode, dtype, q, k, v, o, none, progress, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes,
+  return forward_impl(mode, dtype, q, k, v, o, reps, progress, mask, B, Hq, Hkv, S, D, causal, workspace, workspace_bytes,
                       cu_stream);
 }
 
@@ -567,20 +576,22 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
                                    void* cu_stream) {
   ar::OutReplicas none;
   none.n = 0;
+  none.multicast = 0;
   return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, none,
                                ar::OutProgress{nullptr, nullptr, 0}, out_dtype, mask, B, Hq, Hkv, S, D, causal, status_word,
                                cu_stream);
 }
 int ar_sage_attention_prequantized_reporting(const int8_t* q8, const int8_t* k8, const float* q_scale,
                                              const float* k_scale, const void* v_bf16, void* o, int out_dtype,
-                                             uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch,
-                                             const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
-                                             int causal, void* status_word, void* cu_stream) {
-  ar::OutReplicas none;
-  none.n = 0;
+                                             void* const* replicas, int n_replicas, uint32_t* pair_count,
+                                             uint32_t* pair_flag, uint32_t epoch, const float* mask, int64_t B, int64_t Hq,
+                                             int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
+                                             void* cu_stream) {
+  ar::OutReplicas reps;
+  if (!replicas_ok(replicas, n_replicas, &reps)) return n_replicas > 7 ? AR_ERR_UNSUPPORTED : AR_ERR_ALIGNMENT;
   ar::OutProgress progress;
   if (!progress_ok(pair_count, pair_flag, epoch, &progress)) return AR_ERR_NULL;
-  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, none, progress, out_dtype, mask, B,
+  return sage_prequantized_any(AR_MODE_SAGE_INT8, q8, k8, q_scale, k_scale, v_bf16, o, reps, progress, out_dtype, mask, B,
                                Hq, Hkv, S, D, causal, status_word, cu_stream);
 }
 int ar_sage_attention_prequantized_replicated(const int8_t* q8, const int8_t* k8, const float* q_scale,
@@ -599,6 +610,7 @@ int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, con
                                        int causal, void* status_word, void* cu_stream) {
   ar::OutReplicas none;
   none.n = 0;
+  none.multicast = 0;
   return sage_prequantized_any(AR_MODE_SAGE_FP8, q8, k8, q_scale, k_scale, v_bf16, o, none,
                                ar::OutProgress{nullptr, nullptr, 0}, out_dtype, mask, B, Hq, Hkv, S, D, causal, status_word,
                                cu_stream);

@@ -11,9 +11,13 @@ enum TcMode { TC_BF16 = 0, TC_SAGE = 1, TC_TF32 = 2, TC_SAGE_FP8 = 3 };  // TC_S
 
 // Further buffers that receive the same bf16 output rows as `out`, at the same offsets: buffers of other GPUs
 // mapped into this process (the fused output gather).  Plain stores only; nothing is ever read from them.
+// multicast: p[0] is instead ONE address of an NVLink multicast object that covers the output's place on every GPU of
+// the group, this one included: the kernel issues one multimem.st per 16 bytes, the switch delivers it everywhere,
+// and `out` itself is not written separately.
 struct OutReplicas {
   void* p[7];
   int n;
+  int multicast;
 };
 
 // Completion reports of a forward launch, for a host that moves finished output while the kernel is still running:

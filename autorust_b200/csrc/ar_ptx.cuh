@@ -93,6 +93,13 @@ __device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity) 
   return true;
 }
 
+// 16 bytes to an address of an NVLink multicast object: the switch replicates the store to every GPU bound to it.
+__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

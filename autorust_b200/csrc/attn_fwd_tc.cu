@@ -683,8 +683,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               if (grow < N) {
                 const size_t off = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)grow * o_ss) * 2 +
                                    (size_t)(pass * 128 + ch * 16);
-                *(uint4*)((uint8_t*)out + off) = w;
-                for (int e = 0; e < reps.n; e++) *(uint4*)((uint8_t*)reps.p[e] + off) = w;
+                if (reps.multicast) {
+                  multimem_st16((uint8_t*)reps.p[0] + off, w);  // one store, delivered to every GPU by the switch
+                } else {
+                  *(uint4*)((uint8_t*)out + off) = w;
+                  for (int e = 0; e < reps.n; e++) *(uint4*)((uint8_t*)reps.p[e] + off) = w;
+                }
               }
             }
             __syncwarp();

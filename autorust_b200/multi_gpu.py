@@ -9,6 +9,7 @@ copy engines, or all-gathered by NCCL.  The reference has no multi-device code (
 from __future__ import annotations
 
 import ctypes
+import sys
 from dataclasses import dataclass
 
 from . import _abi
@@ -84,7 +85,8 @@ def load() -> ctypes.CDLL:
     L.ar_gather_p2p_reports.argtypes = [p, i64, ctypes.POINTER(p), ctypes.POINTER(p)]
     L.ar_gather_p2p_next_epoch.argtypes = [p]
     L.ar_gather_p2p_next_epoch.restype = ctypes.c_uint32
-    L.ar_gather_p2p_push_progressive.argtypes = [p, ctypes.c_size_t, ctypes.c_size_t, i64, i64, ctypes.c_uint32, p]
+    L.ar_gather_p2p_push_progressive.argtypes = [p, ctypes.c_size_t, ctypes.c_size_t, i64, i64, ctypes.c_uint32, ci, p]
+    L.ar_gather_p2p_copy_streams.argtypes = [p, ci]
     L.ar_gather_p2p_fence.argtypes = [p, p]
     L.ar_gather_p2p_close.argtypes = [p]
     L.ar_gather_p2p_close.restype = None
@@ -115,6 +117,7 @@ class Gather:
             raise RuntimeError("ar_gather_init: " + L.ar_gather_last_error().decode())
         self.rank, self.world = rank, world
         self._p2p = None
+        self._mc = None
 
     def allgather_into(self, send, recv, stream=None) -> None:
         """recv[r] <- rank r's `send` (contiguous CUDA tensors, bf16 or f32), asynchronously on `stream`."""
@@ -157,15 +160,18 @@ class Gather:
         self._p2p = torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
         return self._p2p.view(dtype).view(*shape)
 
-    def p2p_replicas(self, part) -> list[int]:
-        """Addresses, in this process, of the place of `part` (a piece of the tensor p2p_open returned) in every
-        PEER's buffer: what the attention kernel takes as `replicas` to store its output rows there itself (the
-        fused gather).  Nothing is ever read through them."""
+    def p2p_replicas(self, part, count: int | None = None) -> list[int]:
+        """Addresses, in this process, of the place of `part` (a piece of the tensor p2p_open returned) in the
+        PEERS' buffers, in ring order from rank + 1 (all of them, or the first `count`): what the attention kernel
+        takes as `replicas` to store its output rows there itself (the fused gather).  Nothing is ever read through
+        them."""
         off = part.data_ptr() - self._p2p.data_ptr()
         if off < 0 or off + part.numel() * part.element_size() > self._p2p.numel():
             raise ValueError("p2p_replicas: the piece lies outside the gather buffer")
         out = []
-        for r in range(self.world):
+        n = self.world - 1 if count is None else min(count, self.world - 1)
+        for i in range(1, n + 1):
+            r = (self.rank + i) % self.world
             if r == self.rank:
                 continue
             base = load().ar_gather_p2p_peer(self._h, r)
@@ -193,10 +199,17 @@ class Gather:
             raise RuntimeError("ar_gather_p2p_reports: " + load().ar_gather_last_error().decode())
         return count.value, flag.value, int(load().ar_gather_p2p_next_epoch(self._h))
 
-    def p2p_push_progressive(self, part, reports, pairs_per_group: int = 4, stream=None) -> None:
+    def p2p_copy_streams(self, n: int) -> None:
+        """Spreads the progressive copies over `n` streams of the library (1 to 8)."""
+        if load().ar_gather_p2p_copy_streams(self._h, n) != 0:
+            raise RuntimeError("ar_gather_p2p_copy_streams: " + load().ar_gather_last_error().decode())
+
+    def p2p_push_progressive(self, part, reports, pairs_per_group: int = 4, stream=None, kernel_peers: int = 0) -> None:
         """Right after a launch that writes `part` (this rank's [pairs, S, D]-shaped piece of the tensor p2p_open
         returned) and reports with `reports`: watches the reports and queues every finished group of pairs to the
-        peers' copy engines while the kernel runs.  Returns when the last group is queued."""
+        peers' copy engines while the kernel runs -- to all peers, or to those after the first `kernel_peers` of the
+        ring, which the kernel serves itself (p2p_replicas(part, kernel_peers)).  Returns when the last group is
+        queued."""
         import torch
         s = stream if stream is not None else torch.cuda.current_stream()
         if not part.is_contiguous():
@@ -204,9 +217,50 @@ class Gather:
         n_pairs = part.numel() // (part.shape[-1] * part.shape[-2])
         off = part.data_ptr() - self._p2p.data_ptr()
         rc = load().ar_gather_p2p_push_progressive(self._h, off, part.shape[-1] * part.shape[-2] * part.element_size(),
-                                                   n_pairs, pairs_per_group, reports[2], s.cuda_stream)
+                                                   n_pairs, pairs_per_group, reports[2], 1 + kernel_peers, s.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"ar_gather_p2p_push_progressive ({rc}): " + load().ar_gather_last_error().decode())
+
+    def multicast_open(self, shape, dtype, group=None):
+        """Collective over `group` (default: torch.distributed's world, which must be initialised).  Allocates a
+        buffer of `shape` on every rank as torch symmetric memory and binds them to one NVLink multicast object: a
+        store to the multicast address of a place lands in that place of EVERY rank's buffer, replicated by the
+        NVSwitch.  Returns this rank's buffer, or None when the box has no multicast support (the ranks agree).
+        The attention kernel writes through it with replicas=multicast_replica(piece)."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        dev = torch.device("cuda", torch.cuda.current_device())
+        try:
+            buf = symm.empty(*shape, dtype=dtype, device=dev)
+            handle = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+            mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+        except Exception as exc:  # no symmetric memory on this build or box: the caller takes another form
+            print(f"[multi_gpu] rank {self.rank}: symmetric memory unavailable ({exc})", file=sys.stderr)
+            buf, handle, mc = None, None, 0
+        agree = torch.tensor([1 if mc else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
+        if not bool(agree.item()):
+            del handle, buf
+            return None
+        self._mc = (buf, handle, mc)
+        return buf
+
+    def multicast_replica(self, part):
+        """("multicast", address) of `part` (a piece of the tensor multicast_open returned) inside the multicast
+        object: what the attention entry points take as `replicas`."""
+        buf, _, mc = self._mc
+        off = part.data_ptr() - buf.data_ptr()
+        if off < 0 or off + part.numel() * part.element_size() > buf.numel() * buf.element_size():
+            raise ValueError("multicast_replica: the piece lies outside the buffer")
+        return ("multicast", mc + off)
+
+    def multicast_close(self) -> None:
+        """Drops the buffer and its multicast binding (every rank calls it, with nothing in flight: a rank that goes
+        away while its memory is still bound disturbs the others' links)."""
+        import torch
+        torch.cuda.synchronize()
+        self._mc = None
 
     def p2p_fence(self, stream=None) -> None:
         """Collective.  After this point of `stream`, every push queued by any rank before its own fence has
@@ -224,6 +278,8 @@ class Gather:
 
     def close(self) -> None:
         if self._h:
+            if self._mc is not None:
+                self.multicast_close()
             self._p2p = None
             load().ar_gather_destroy(self._h)
             self._h = None

@@ -65,9 +65,12 @@ def supported(mode, q: torch.Tensor, k: torch.Tensor, causal=False, has_mask=Fal
 
 
 def _replica_array(replicas):
-    """Device addresses (ints) of the further output buffers as a C array of void*."""
+    """Device addresses (ints) of the further output buffers as a C array of void*; ("multicast", address) for one
+    address of an NVLink multicast object that covers every GPU."""
     if not replicas:
         return None, 0
+    if isinstance(replicas, tuple) and len(replicas) == 2 and replicas[0] == "multicast":
+        return (ctypes.c_void_p * 1)(int(replicas[1])), -1
     arr = (ctypes.c_void_p * len(replicas))(*[int(r) for r in replicas])
     return arr, len(replicas)
 
@@ -103,10 +106,8 @@ def attn_forward(mode, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
                 workspace.data_ptr() if workspace is not None else None,
                 workspace.numel() * workspace.element_size() if workspace is not None else 0, s.cuda_stream)
         if reports is not None:
-            if nrep:
-                raise TypeError("completion reports and replicas exclude each other")
             rc = L.ar_attn_forward_reporting(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                             reports[0], reports[1], reports[2], *tail)
+                                             reps, nrep, reports[0], reports[1], reports[2], *tail)
         elif nrep:
             rc = L.ar_attn_forward_replicated(m, _dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                               reps, nrep, *tail)
@@ -255,12 +256,12 @@ def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None
         s = stream if stream is not None else torch.cuda.current_stream()
         reps, nrep = _replica_array(replicas)
         if reports is not None:
-            if q8.dtype == torch.uint8 or nrep:
-                raise TypeError("completion reports: INT8 operands, no replicas")
+            if q8.dtype == torch.uint8:
+                raise TypeError("completion reports: INT8 operands")
             rc = L.ar_sage_attention_prequantized_reporting(
                 q8.data_ptr(), k8.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v.data_ptr(), out.data_ptr(),
-                _dtype_code(out), reports[0], reports[1], reports[2], mask.data_ptr() if mask is not None else None, B, Hq,
-                Hkv, S, D, int(causal), None, s.cuda_stream)
+                _dtype_code(out), reps, nrep, reports[0], reports[1], reports[2],
+                mask.data_ptr() if mask is not None else None, B, Hq, Hkv, S, D, int(causal), None, s.cuda_stream)
         elif nrep:
             if q8.dtype == torch.uint8 or out.dtype != torch.bfloat16:
                 raise TypeError("replicated output: INT8 operands and a bfloat16 output")

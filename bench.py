@@ -340,7 +340,7 @@ def long_context_slab(torch, device, pair_begin: int, pair_end: int):
 
 
 def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=True, fused=True, progressive=False,
-                     steps=3) -> dict:
+                     multicast=False, steps=3) -> dict:
     """Benchmark configuration 5: ONE global tensor B=16, H=64, S=16384, D=128, causal Sage, cut over the ranks
     along the flattened (batch, head) axis (1024 pairs -> 1024 / N per rank, strong scaling); every rank ends up
     with the whole bf16 output.  The inputs of pair p depend on p alone (a generator seeded per group of 8 pairs),
@@ -361,7 +361,13 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
     comm_stream = torch.cuda.Stream() if world > 1 else None
     p2p = False
     full = None
-    if world > 1 and use_p2p:
+    if world > 1 and multicast:
+        full = gather.multicast_open((world, n_local, S, D), torch.bfloat16)
+        multicast = full is not None
+        use_p2p = use_p2p or not multicast  # no multicast after all: the mapped buffers
+    else:
+        multicast = False
+    if world > 1 and use_p2p and not multicast:
         try:
             full = gather.p2p_open((world, n_local, S, D), torch.bfloat16)
             opened = 1
@@ -372,9 +378,9 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
         p2p = bool(flag.item())
         if not p2p and opened:
             gather.p2p_close()
-    if not p2p:
+    if not p2p and not multicast:
         full = torch.empty((world, n_local, S, D), dtype=torch.bfloat16, device=device)
-    fused = fused and p2p
+    fused = (fused and p2p) or multicast
     progressive = progressive and p2p
     npieces = 8 if (p2p and not fused and not progressive) else 1
     per = n_local // npieces
@@ -387,11 +393,16 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
                 full[rank, h0:h1].data_ptr(), _abi.DTYPE_BF16, reports[0], reports[1], reports[2], None, 1, h1 - h0,
                 h1 - h0, S, D, 1, None, stream.cuda_stream)
         elif replicate:
-            reps = gather.p2p_replicas(full[rank, h0:h1])
-            arr = (ctypes.c_void_p * len(reps))(*reps)
+            if multicast:
+                arr = (ctypes.c_void_p * 1)(gather.multicast_replica(full[rank, h0:h1])[1])
+                n_rep = _abi.REPLICAS_MULTICAST
+            else:
+                reps = gather.p2p_replicas(full[rank, h0:h1])
+                arr = (ctypes.c_void_p * len(reps))(*reps)
+                n_rep = len(reps)
             rc = L.ar_sage_attention_prequantized_replicated(
                 q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(), ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(),
-                full[rank, h0:h1].data_ptr(), arr, len(reps), None, 1, h1 - h0, h1 - h0, S, D, 1, None, stream.cuda_stream)
+                full[rank, h0:h1].data_ptr(), arr, n_rep, None, 1, h1 - h0, h1 - h0, S, D, 1, None, stream.cuda_stream)
         else:
             rc = L.ar_sage_attention_prequantized(q8[h0:h1].data_ptr(), k8[h0:h1].data_ptr(), qs[h0:h1].data_ptr(),
                                                   ks[h0:h1].data_ptr(), v[h0:h1].data_ptr(), full[rank, h0:h1].data_ptr(),
@@ -463,6 +474,8 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
            "gather_bytes_received_per_rank": (world - 1) * n_local * S * D * 2,
            "gather": (f"finished groups of {group} pairs, reported by the kernel while it runs, pushed by the copy engines "
                       "under the rest of the kernel" if progressive else
+                      "stored once by the attention kernel's epilogue through an NVLink multicast object, replicated to "
+                      "every rank's buffer by the NVSwitch" if multicast else
                       "stored into every rank's buffer by the attention kernel's epilogue" if fused else
                       "peer-to-peer copies on the copy engines, 8 pieces under the following pieces' kernels" if p2p
                       else "NCCL all-gather in place after the kernel") if world > 1 else None,
@@ -473,6 +486,10 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
     if p2p:
         del full
         gather.p2p_close()
+    if multicast:
+        del full
+        dist.barrier()
+        gather.multicast_close()
     return res
 
 
@@ -502,9 +519,18 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     gathered = None
     gather = None
     p2p = False
+    multicast = False
     if world > 1:
         from autorust_b200 import multi_gpu
         gather = multi_gpu.Gather(rank, world, local_rank)  # NCCL communicator of libar_gather.so
+        if args.gather == "multicast":
+            # every rank's buffer bound to one NVLink multicast object; where the box has none, the fused form
+            gathered = gather.multicast_open((world, B * H, S, D), torch.bfloat16)
+            multicast = gathered is not None
+            if not multicast:
+                if rank == 0:
+                    print("[bench] no NVLink multicast here: the kernel stores to every peer itself", file=sys.stderr)
+                args.gather = "fused"
         if args.gather in ("progressive", "fused", "p2p"):
             # copy-engine gather: this rank's outputs land in gathered[rank] and are pushed to the peers piece by piece.
             # Every rank has to have its peers mapped; if one could not, all of them take the NCCL form.
@@ -517,7 +543,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             flag = torch.tensor([opened], dtype=torch.int32, device=device)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             p2p = bool(flag.item())
-        if not p2p:
+        if not p2p and not multicast:
             gathered = torch.empty((B, world, H, S, D), dtype=torch.bfloat16, device=device)
     # N > 1, copy-engine gather: pieces of the flattened (batch, head) axis, each a whole number of waves of CTAs
     # as far as possible, with a short last piece so that little is left to push when the step's last kernel ends.
@@ -584,10 +610,15 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             e0 = torch.cuda.Event(enable_timing=True)
             e1 = torch.cuda.Event(enable_timing=True)
             e0.record(stream)
-        reps = gather.p2p_replicas(gathered[rank])
-        arr = (ctypes.c_void_p * len(reps))(*reps)
+        if multicast:
+            arr = (ctypes.c_void_p * 1)(gather.multicast_replica(gathered[rank])[1])
+            n_rep = _abi.REPLICAS_MULTICAST
+        else:
+            reps = gather.p2p_replicas(gathered[rank])
+            arr = (ctypes.c_void_p * len(reps))(*reps)
+            n_rep = len(reps)
         rc = L.ar_sage_attention_prequantized_replicated(q8.data_ptr(), k8.data_ptr(), qs.data_ptr(), ks.data_ptr(),
-                                                         v.data_ptr(), gathered[rank].data_ptr(), arr, len(reps), None,
+                                                         v.data_ptr(), gathered[rank].data_ptr(), arr, n_rep, None,
                                                          B, H, H, S, D, int(w["causal"]), None, stream.cuda_stream)
         _abi.check(rc, "ar_sage_attention_prequantized_replicated")
         if record:
@@ -624,7 +655,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             attend_reporting(record)
             gather.p2p_fence(stream)
             return
-        if fused:
+        if fused or multicast:
             quantise(0, B)
             attend_fused(record)
             gather.p2p_fence(stream)
@@ -701,7 +732,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     # the gathered buffers after the last step: every slab on every rank against its owner's copy
     gather_verified = None
     if world > 1:
-        slabs = [gathered[r] for r in range(world)] if p2p else [gathered[:, r] for r in range(world)]
+        slabs = [gathered[r] for r in range(world)] if (p2p or multicast) else [gathered[:, r] for r in range(world)]
         gather_verified, _ = verify_gather(torch, dist, slabs, rank, world)
         if not gather_verified:
             raise SystemExit("a gathered slab differs from its owner's copy")
@@ -764,10 +795,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1 and p2p:
         gathered = None
         gather.p2p_close()
+    if multicast:
+        gathered = None
+        dist.barrier()
+        gather.multicast_close()
     long_context = None
     if not args.no_long_context:
         long_context = long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=p2p, fused=fused,
-                                        progressive=progressive)
+                                        progressive=progressive, multicast=multicast)
 
     if rank == 0:
         line = {
@@ -776,7 +811,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "dtype": "int8 QK^T + bf16 PV, f32 softmax", "data": "synthetic",
             "config": {"workload": "sage_int8_fwd B=4 H=32 S=8192 D=128 non-causal per GPU (benchmark configuration 3)",
                        **w, "global_batch": B * world, "partition": ("one batch of B per rank (independent (batch, head) pairs, no reduction); bf16 "
-                       "outputs gathered on every rank " + (f"by the copy engines under the kernel: the kernel reports every "
+                       "outputs gathered on every rank " + ("by the attention kernel itself: its epilogue stores every row ONCE, "
+                       "to the address of an NVLink multicast object that every rank's buffer is bound to (torch symmetric "
+                       "memory), and the NVSwitch delivers the store to all ranks (multimem.st; nothing is read from a peer), "
+                       "closed by a 4-byte NCCL all-reduce" if multicast else f"by the copy engines under the kernel: the kernel reports every "
                        f"finished (batch, head) pair to the host while it runs, and a host thread queues each finished group "
                        f"of {group} pairs as peer-to-peer copies at once (CUDA IPC over NVLink), closed by a 4-byte NCCL "
                        "all-reduce" if progressive else "by the attention kernel itself: its epilogue stores every row "
@@ -807,7 +845,7 @@ def main() -> None:
     ap.add_argument("--no-vit", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the bf16_fwd and config2 legs")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=16 H=64 S=16384 causal leg")
-    ap.add_argument("--gather", default="fused", choices=["fused", "progressive", "p2p", "nccl"],
+    ap.add_argument("--gather", default="multicast", choices=["multicast", "fused", "progressive", "p2p", "nccl"],
                     help="N > 1: how the output slabs reach the other ranks (stored by the attention kernel's epilogue, "
                          "pushed by the copy engines, or NCCL's all-gather kernels)")
     args = ap.parse_args()

@@ -105,7 +105,13 @@ int ar_attn_forward(int mode, int dtype, const void* q, const void* k, const voi
  * so that head-parallel ranks assemble the whole output on every GPU while they compute (include/ar_attn_gather.h
  * maps the buffers and provides the fence that closes a round).  The reference has no multi-device code
  * (CURRENT_STATE.md:64,469; src/runtime/ops_cuda.rs:1162-1169): this call has no counterpart there.
- * AR_MODE_BF16, AR_MODE_SAGE_INT8 and AR_MODE_SAGE_FP8 with dtype AR_DTYPE_BF16; n_replicas = 0 is ar_attn_forward. */
+ * AR_MODE_BF16, AR_MODE_SAGE_INT8 and AR_MODE_SAGE_FP8 with dtype AR_DTYPE_BF16; n_replicas = 0 is ar_attn_forward.
+ * n_replicas = AR_REPLICAS_MULTICAST: replicas[0] is ONE address inside an NVLink multicast object (cuMulticast*,
+ * or torch's symmetric memory) that stands for the place of `o` on every GPU of the group, this one included.  The
+ * epilogue then issues one multimem.st per 16 bytes and the NVSwitch delivers it to all of them: the slab leaves
+ * this GPU once instead of once per peer, and `o` is not written separately (it must be this GPU's view of the same
+ * place).  Needs NVSwitch multicast support; the caller owns the object and unbinds it in an orderly way. */
+#define AR_REPLICAS_MULTICAST (-1)
 int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
                                void* const* replicas, int n_replicas, const float* mask, int64_t B, int64_t Hq,
                                int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace, size_t workspace_bytes,
@@ -126,11 +132,13 @@ int ar_attn_forward_replicated(int mode, int dtype, const void* q, const void* k
  * use (the call zeroes them on the stream; one launch at a time per set of words).  pair_flag: B * Hq words
  * the HOST can read while the kernel runs (mapped pinned memory, as the device sees it).  When every output row of
  * pair p is visible system-wide the kernel writes `epoch` (non-zero, different from the previous launch's) to
- * pair_flag[p].  Tensor-core modes only.  No counterpart in the reference, which is single-device. */
+ * pair_flag[p].  `replicas` as in ar_attn_forward_replicated (n_replicas = 0: none): some peers can be served by the
+ * kernel's own stores and the others by the host's copies.  Tensor-core modes only.  No counterpart in the
+ * reference, which is single-device. */
 int ar_attn_forward_reporting(int mode, int dtype, const void* q, const void* k, const void* v, void* o,
-                              uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch, const float* mask, int64_t B,
-                              int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
-                              size_t workspace_bytes, void* cu_stream);
+                              void* const* replicas, int n_replicas, uint32_t* pair_count, uint32_t* pair_flag,
+                              uint32_t epoch, const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                              int causal, void* workspace, size_t workspace_bytes, void* cu_stream);
 
 int ar_attn_forward_strided(int mode, int dtype, const void* q, const void* k, const void* v, void* o, const float* mask,
                             int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, const int64_t* q_strides,
@@ -203,9 +211,10 @@ int ar_sage_attention_prequantized(const int8_t* q8, const int8_t* k8, const flo
 /* ar_sage_attention_prequantized with completion reports per (batch, head) pair (see ar_attn_forward_reporting). */
 int ar_sage_attention_prequantized_reporting(const int8_t* q8, const int8_t* k8, const float* q_scale,
                                              const float* k_scale, const void* v_bf16, void* o, int out_dtype,
-                                             uint32_t* pair_count, uint32_t* pair_flag, uint32_t epoch,
-                                             const float* mask, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
-                                             int causal, void* status_word, void* cu_stream);
+                                             void* const* replicas, int n_replicas, uint32_t* pair_count,
+                                             uint32_t* pair_flag, uint32_t epoch, const float* mask, int64_t B, int64_t Hq,
+                                             int64_t Hkv, int64_t S, int64_t D, int causal, void* status_word,
+                                             void* cu_stream);
 
 /* ar_sage_attention_prequantized with a bf16 output that is also stored into `replicas` (see
  * ar_attn_forward_replicated). */

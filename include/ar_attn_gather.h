@@ -91,15 +91,22 @@ uint32_t ar_gather_p2p_next_epoch(void* comm);
 /* Call right after a reporting launch was queued on `cu_stream` with this comm's words and `epoch`: pair p of the
  * launch lies at [offset + p * bytes_per_pair, + bytes_per_pair) of the local buffer.  The calling thread watches the
  * flags and, group of `pairs_per_group` by group, queues the peer-to-peer copies of a group on the library's stream
- * as soon as its last pair is reported.  Returns when the copies of the last group are queued (the kernel is then
+ * as soon as its last pair is reported.  The copies go to the peers rank + first_peer, ..., rank + world - 1 of the
+ * ring (modulo world; first_peer = 1: every peer; larger when the kernel itself stores to the first peers of the ring
+ * as replicas).  Returns when the copies of the last group are queued (the kernel is then
  * all but finished); ar_gather_p2p_fence joins them into `cu_stream`.  The watch is bounded: it ends when an event
  * recorded behind the launch has completed (flags still missing then mean the launch failed: -7) or after 30 s
  * (-8).  0 on success. */
 int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_pair, int64_t n_pairs,
-                                   int64_t pairs_per_group, uint32_t epoch, void* cu_stream);
+                                   int64_t pairs_per_group, uint32_t epoch, int first_peer, void* cu_stream);
+
+/* How many streams of the library's own the progressive copies are spread over (1 to 8; peer i of the ring uses
+ * stream i modulo that number).  Call between ar_gather_p2p_open and the first push.  0 on success. */
+int ar_gather_p2p_copy_streams(void* comm, int n);
 
 /* Queues on `cu_stream` the point after which everything that any rank queued before ITS fence -- pushes, or
- * kernels that store into the peers -- has landed in this rank's buffer.  Collective. */
+ * kernels that store into the peers or through a multicast object (ar_attn_forward_replicated with
+ * AR_REPLICAS_MULTICAST; no ar_gather_p2p_open needed for those) -- has landed in this rank's buffer.  Collective. */
 int ar_gather_p2p_fence(void* comm, void* cu_stream);
 
 /* Unmaps the peers' buffers and frees the local one.  Collective in effect: no peer may still push. */

@@ -202,3 +202,73 @@ def test_two_gpu_gather_is_bit_identical_to_single_gpu(attn_lib):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert ok
+
+
+def _multicast_rank(rank, world, port, seed, result):
+    """The fused gather through an NVLink multicast object: every rank's buffer is bound to it, the kernel stores each
+    row once and the switch delivers it to both GPUs.  The ranks leave in an orderly way (nothing in flight, the
+    binding dropped before the process group goes)."""
+    import torch
+    import torch.distributed as dist
+    from autorust_b200 import ops
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=120), device_id=torch.device("cuda", rank))
+    B, H, S, D = 2, 8, 700, 128
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q, k, v = (torch.randn(B * H, S, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    sh = multi_gpu.equal_partition(B, H, H, world)[rank]
+    n = sh.q_end - sh.q_begin
+    gather = multi_gpu.Gather(rank, world, rank)
+    buf = gather.multicast_open((world, n, S, D), torch.bfloat16)
+    verdict = "no multicast"
+    if buf is not None:
+        ok = True
+        for mode in ("bf16", "sage"):
+            buf.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            ops.attn_forward(mode, q[sh.q_begin:sh.q_end].view(1, n, S, D), k[sh.kv_begin:sh.kv_end].view(1, n, S, D),
+                             v[sh.kv_begin:sh.kv_end].view(1, n, S, D), None, True, out=buf[rank].view(1, n, S, D),
+                             replicas=gather.multicast_replica(buf[rank]))
+            gather.p2p_fence()
+            torch.cuda.synchronize()
+            ref = ops.attn_forward(mode, q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(buf.reshape(B * H, S, D).view(torch.int16), ref.reshape(B * H, S, D).view(torch.int16))
+            ok = ok and ops.last_status(None) == 0
+            dist.barrier()
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(ok))
+        verdict = "ok" if all(flags) else "mismatch"
+        del buf
+        torch.cuda.synchronize()
+        dist.barrier()
+        gather.multicast_close()
+    if rank == 0:
+        result.put(verdict)
+    dist.barrier()
+    gather.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_multicast_gather_is_bit_identical_to_single_gpu(attn_lib):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_multicast_rank, args=(r, 2, port, 9, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    verdict = result.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    if verdict == "no multicast":
+        pytest.skip("this box has no NVLink multicast support")
+    assert verdict == "ok"
