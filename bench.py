@@ -458,9 +458,28 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
 
     ms_compute = timed(False)
     ms_total = timed(True) if world > 1 else ms_compute
+    def leave(message):
+        """A failure every rank knows about: the buffers go first, all ranks together (a rank must not leave while its
+        memory is still bound to the multicast object), then the exit."""
+        nonlocal full
+        full = None
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            if multicast:
+                gather.multicast_close()
+            elif p2p:
+                gather.p2p_close()
+        raise SystemExit(message)
+
     status = int(L.ar_attn_last_status(None, stream.cuda_stream))
+    if world > 1:  # one verdict for all ranks
+        worst = torch.tensor([1 if status != 0 else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        if int(worst.item()) and status == 0:
+            status = -7  # AR_ERR_DEVICE_WAIT on another rank
     if status != 0:
-        raise SystemExit(f"device status after the long-context steps: {_abi.strerror(status)}")
+        leave(f"device status after the long-context steps: {_abi.strerror(status)}")
     if world > 1:
         ok, checksum = verify_gather(torch, dist, [full[r] for r in range(world)], rank, world)
     else:
@@ -482,7 +501,7 @@ def long_context_leg(torch, dist, L, _abi, gather, rank, world, device, use_p2p=
            "gather_verified": bool(ok) if world > 1 else None, "output_checksum": checksum,
            "timing": "CUDA events on the launching stream, max over ranks; flops 4*B*H*S^2*D/2"}
     if world > 1 and not ok:
-        raise SystemExit("long_context: a gathered slab differs from its owner's copy")
+        leave("long_context: a gathered slab differs from its owner's copy")
     if p2p:
         del full
         gather.p2p_close()
@@ -715,9 +734,27 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     barrier()
     load_t1 = time.perf_counter()
     ms_total = t0.elapsed_time(t1)
+    def leave(message):
+        """A failure every rank knows about: the buffers go first, all ranks together (a rank must not leave while its
+        memory is still bound to the multicast object), then the exit."""
+        nonlocal gathered
+        gathered = None
+        torch.cuda.synchronize()
+        if rank == 0:
+            sampler.stop(load_t0, load_t1)
+        if world > 1:
+            dist.barrier()
+            gather.close()
+        raise SystemExit(message)
+
     status = int(L.ar_attn_last_status(None, stream.cuda_stream))
+    if world > 1:  # one verdict for all ranks
+        worst = torch.tensor([1 if status != 0 else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        if int(worst.item()) and status == 0:
+            status = -7  # AR_ERR_DEVICE_WAIT on another rank
     if status != 0:
-        raise SystemExit(f"device status after the timed region: {_abi.strerror(status)}")
+        leave(f"device status after the timed region: {_abi.strerror(status)}")
     clocks = sampler.stop(load_t0 + 0.1, load_t1) if rank == 0 else None
     if clocks is not None:
         clocks["window"] = "the timed steps and the same steps repeated right after them, %.2f s in all" % (load_t1 - load_t0)
@@ -735,7 +772,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         slabs = [gathered[r] for r in range(world)] if (p2p or multicast) else [gathered[:, r] for r in range(world)]
         gather_verified, _ = verify_gather(torch, dist, slabs, rank, world)
         if not gather_verified:
-            raise SystemExit("a gathered slab differs from its owner's copy")
+            leave("a gathered slab differs from its owner's copy")
 
     # roofline of the dominant kernel: its launches inside the timed region, bracketed by events
     # every event pair covers `nb` batch elements' worth of the kernel; scaled to a full-batch launch
