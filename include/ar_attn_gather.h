@@ -101,7 +101,8 @@ int ar_gather_p2p_push_progressive(void* comm, size_t offset, size_t bytes_per_p
                                    int64_t pairs_per_group, uint32_t epoch, int first_peer, void* cu_stream);
 
 /* How many streams of the library's own the progressive copies are spread over (1 to 8; peer i of the ring uses
- * stream i modulo that number).  Call between ar_gather_p2p_open and the first push.  0 on success. */
+ * stream i modulo that number; default 1).  Call between ar_gather_p2p_open and the first push.  0 on success.
+ * (Measured on eight B200s: seven streams move the same ~430 GB/s per GPU as one.) */
 int ar_gather_p2p_copy_streams(void* comm, int n);
 
 /* Queues on `cu_stream` the point after which everything that any rank queued before ITS fence -- pushes, or

@@ -153,15 +153,18 @@ def _gpu_rank(rank, world, port, seed, result):
     # the progressive form: the kernel reports finished pairs to the host while it runs, the host hands each finished
     # group to the copy engines at once
     progressive_ok = True
-    for mode, group in (("bf16", 1), ("sage", 3), ("bf16", 64)):
+    # (mode, pairs per group, copy streams, peers the kernel serves itself -- with two ranks: 0, or 1 = all of them)
+    for mode, group, streams, kernel_peers in (("bf16", 1, 1, 0), ("sage", 3, 3, 0), ("bf16", 64, 1, 0), ("sage", 2, 2, 1)):
         buf.zero_()
         torch.cuda.synchronize()
         dist.barrier()
         mine = buf[rank].view(1, hq_local, S, D)
+        gather.p2p_copy_streams(streams)
         reports = gather.p2p_reports(hq_local)
         ops.attn_forward(mode, q[sh.q_begin:sh.q_end].view(1, hq_local, S, D), k[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D),
-                         v[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D), None, True, out=mine, reports=reports)
-        gather.p2p_push_progressive(buf[rank], reports, pairs_per_group=group)
+                         v[sh.kv_begin:sh.kv_end].view(1, hq_local, S, D), None, True, out=mine, reports=reports,
+                         replicas=gather.p2p_replicas(buf[rank], kernel_peers) if kernel_peers else None)
+        gather.p2p_push_progressive(buf[rank], reports, pairs_per_group=group, kernel_peers=kernel_peers)
         gather.p2p_fence()
         torch.cuda.synchronize()
         ref_m = ops.attn_forward(mode, q.view(B, H, S, D), k.view(B, H, S, D), v.view(B, H, S, D), None, True)
