@@ -53,13 +53,16 @@ def test_prequantized_entry_reports_and_flags_arrive_while_the_kernel_runs(attn_
     done = torch.cuda.Event()
     ops.sage_attention_prequantized(q8, k8, qs, ks, v, out=out, reports=(count.data_ptr(), flag.data_ptr(), 3))
     done.record()
-    seen_early = 0
+    seen_early, polls = 0, 0
     t0 = time.monotonic()
     while not done.query() and time.monotonic() - t0 < 30.0:
         seen_early = max(seen_early, int((flag == 3).sum()))
+        polls += 1
     torch.cuda.synchronize()
     assert bool((flag == 3).all())
     assert torch.equal(out.view(torch.int16), want.view(torch.int16))
     # the first pairs were visible on the host well before the launch ended (a launch of ~0.8 ms against a poll of
-    # a few microseconds); zero would mean the reports only arrive with the end of the kernel
-    assert 0 < seen_early
+    # a few microseconds); zero would mean the reports only arrive with the end of the kernel.  A host that got
+    # fewer than a handful of polls in (descheduled for the length of the launch) has seen nothing either way.
+    if polls >= 8:
+        assert 0 < seen_early
