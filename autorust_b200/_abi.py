@@ -46,6 +46,7 @@ SYMBOLS = (
     "ar_sage_attention_prequantized_reporting",
     "ar_sage_attention_prequantized_fp8",
     "ar_sage_forward_static",
+    "ar_add_layernorm",
     "ar_attn_last_status",
     "ar_attn_selections",
     "ar_attn_launch_count",
@@ -89,6 +90,8 @@ def load() -> ctypes.CDLL:
     L.ar_attn_forward_reporting.argtypes = [ci, ci, p, p, p, p, p, ci, p, p, ctypes.c_uint32, p, i64, i64, i64, i64, i64, ci,
                                             p, ctypes.c_size_t, p]
     L.ar_attn_forward_reporting.restype = ci
+    L.ar_add_layernorm.argtypes = [p, p, p, p, p, p, i64, i64, ctypes.c_float, ci, p]
+    L.ar_add_layernorm.restype = ci
     L.ar_attn_forward_strided.argtypes = [ci, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, p, p, p, p, ctypes.c_size_t, p]
     L.ar_attn_forward_strided.restype = ci
     L.ar_attn_train_forward.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p]

@@ -36,7 +36,7 @@ NVCC_FLAGS = [
 ]
 
 KERNEL_SOURCES = ["attn_fwd_tc.cu", "attn_fwd_exact.cu", "attn_train.cu", "attn_train_tc.cu", "sage_prologue.cu", "api.cu",
-                  "sage_static.cu"]
+                  "sage_static.cu", "encoder_norm.cu"]
 
 
 def _nvcc() -> str:

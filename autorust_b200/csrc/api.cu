@@ -616,6 +616,22 @@ int ar_sage_attention_prequantized_fp8(const uint8_t* q8, const uint8_t* k8, con
                                cu_stream);
 }
 
+int ar_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* sum_out, void* y,
+                     int64_t rows, int64_t cols, float eps, int dtype, void* cu_stream) {
+  if (!x || !gamma || !beta || !y) return AR_ERR_NULL;
+  if (dtype != AR_DTYPE_BF16) return AR_ERR_UNSUPPORTED;
+  if (rows <= 0 || cols <= 0) return AR_ERR_SHAPE;
+  if (cols % 8 != 0 || cols > 4096) return AR_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(residual) || !aligned16(gamma) || !aligned16(beta) || !aligned16(sum_out) || !aligned16(y))
+    return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  if (ar::launch_add_layernorm(x, residual, gamma, beta, sum_out, y, (long long)rows, (int)cols, eps,
+                               (cudaStream_t)cu_stream) != cudaSuccess)
+    return AR_ERR_CUDA;
+  g_launches++;
+  return AR_OK;
+}
+
 int ar_attn_last_status(void* workspace, void* cu_stream) {
   // a workspace (or a named status word): the status of the last launch that used it.  NULL: the library's
   // accumulator of every launch since it was last read, which this call clears.

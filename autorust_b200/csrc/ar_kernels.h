@@ -53,6 +53,10 @@ struct TcArgs {
   uint32_t* sticky;     // the library's accumulator of the same bits (nullable)
 };
 cudaError_t launch_attn_tc(const TcArgs& a, cudaStream_t stream);
+// y = LayerNorm(x + r) * gamma + beta over rows of `cols` bf16 elements (cols a multiple of 8, at most 4096); r and
+// sum_out may be null (sum_out receives bf16(x + r) and may be x itself).
+cudaError_t launch_add_layernorm(const void* x, const void* r, const void* gamma, const void* beta, void* sum_out,
+                                 void* y, long long rows, int cols, float eps, cudaStream_t stream);
 // Rank-4 tile map (128-byte swizzle) of a tensor indexed (batch, head, row, inner) whose element lies at
 // batch * sb + head * sh + row * sr + inner (strides in elements, inner contiguous): box of box_inner x box_rows.
 // The two middle dimensions are entered in the order of their strides; *token_major_bit is 1 when the head comes

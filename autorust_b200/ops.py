@@ -277,6 +277,29 @@ def sage_attention_prequantized(q8, k8, q_scale, k_scale, v, out=None, mask=None
     return out
 
 
+def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, gamma: torch.Tensor, beta: torch.Tensor,
+                  eps: float = 1e-5, write_sum: bool = True, stream=None):
+    """(s, y) with s = x + residual (x itself when residual is None; not written when write_sum is False) and
+    y = LayerNorm(s) * gamma + beta over the last axis (ar_add_layernorm; bf16, contiguous)."""
+    L = _abi.load()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    for name, t in (("x", x), ("residual", residual)):
+        if t is not None:
+            _check_dense(name, t, x.shape, torch.bfloat16, x.device)
+    _check_dense("gamma", gamma, (cols,), torch.bfloat16, x.device)
+    _check_dense("beta", beta, (cols,), torch.bfloat16, x.device)
+    y = torch.empty_like(x)
+    s_out = torch.empty_like(x) if (residual is not None and write_sum) else None
+    with torch.cuda.device(x.device):
+        st = stream if stream is not None else torch.cuda.current_stream()
+        rc = L.ar_add_layernorm(x.data_ptr(), residual.data_ptr() if residual is not None else None, gamma.data_ptr(),
+                                beta.data_ptr(), s_out.data_ptr() if s_out is not None else None, y.data_ptr(), rows, cols,
+                                float(eps), _abi.DTYPE_BF16, st.cuda_stream)
+    _abi.check(rc, "ar_add_layernorm")
+    return (s_out if s_out is not None else x), y
+
+
 def last_status(workspace: torch.Tensor | None = None) -> int:
     """Synchronises the current stream and reads a status word: a workspace's (its last launch), or with None the
     library's accumulator over every launch since it was last read (reading clears it)."""

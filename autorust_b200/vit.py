@@ -11,7 +11,8 @@ The reference projects q, k and v separately and materialises the transposed [B,
 kernel (src/models/transformer.rs:260-262, 277-285).  With bf16 weights the default path here runs the three
 projections as one GEMM over the concatenated weights (the same numbers: the rows of the product do not mix)
 and hands the kernel VIEWS of that [B, S, 3E] buffer; the kernel's output lands in [B, S, H, D] memory, which is
-the [B, S, E] the output projection reads.  The four copies per block are gone (`copies=True` keeps them).
+the [B, S, E] the output projection reads.  The four copies per block are gone (`copies=True` keeps them), and the
+MLP's bias + GELU run in the first GEMM's epilogue.
 
 As in the reference, the projections stay library GEMMs (torch / cuBLAS, bf16) and only the attention
 goes to the hand-written kernel; torch supplies memory, GEMMs, LayerNorm and GELU -- it is the harness
@@ -86,7 +87,9 @@ class ViT:
             a = ops.attn_forward_views(q, k, v).transpose(1, 2).reshape(B, S, E)  # [B, S, H, D] memory: no copy
             x = x + F.linear(a, *blk["o"])
             n2 = F.layer_norm(x, (E,), blk["ln2"][0], blk["ln2"][1], 1e-5)
-            h = F.gelu(F.linear(n2, *blk["ff1"]), approximate="tanh")
+            # bias and the tanh GELU in the GEMM's epilogue (cuBLASLt): the [B, S, 4E] pre-activation is never
+            # written and read back
+            h = torch._addmm_activation(blk["ff1"][1], n2.view(B * S, E), blk["ff1"][0].t(), use_gelu=True).view(B, S, 4 * E)
             return x + F.linear(h, *blk["ff2"])
         # projections first (plain GEMMs), then the transposed views are materialised for the kernel
         # (src/models/transformer.rs:277-285, 260-262)
@@ -99,9 +102,39 @@ class ViT:
         h = F.gelu(F.linear(n2, *blk["ff1"]), approximate="tanh")
         return x + F.linear(h, *blk["ff2"])
 
+    def _forward_fused(self, images: torch.Tensor) -> torch.Tensor:
+        """The bf16 encoder with nothing between the GEMMs and the attention kernel that a pass of its own is not
+        needed for: patch embedding as one GEMM (a 16x16 convolution with stride 16 reads every pixel exactly once:
+        cast and patch order in one copy, then [B*196, 768] x [768, 768]); residual add + LayerNorm in one kernel
+        (ar_add_layernorm), which hands the next GEMM its input and keeps the residual stream; q, k, v as views of
+        one QKV GEMM; bias + GELU in the MLP GEMM's epilogue."""
+        B, E, P = images.shape[0], self.embed_dim, self.patch
+        g = images.shape[-1] // P
+        patches = torch.empty((B, g, g, images.shape[1], P, P), dtype=self.dtype, device=images.device)
+        patches.copy_(images.view(B, images.shape[1], g, P, g, P).permute(0, 2, 4, 1, 3, 5))
+        x = F.linear(patches.view(B, g * g, -1), self.embed_w.view(E, -1), self.embed_b)
+        x = torch.cat([self.cls.expand(B, -1, -1), x], dim=1) + self.pos
+        S, H, D = x.shape[1], self.num_heads, E // self.num_heads
+        _, n = ops.add_layernorm(x, None, *self.blocks[0]["ln1"])
+        for i, blk in enumerate(self.blocks):
+            qkv = F.linear(n, *blk["qkv"])  # [B, S, 3E]; q, k, v are views of it, read in place by the kernel
+            q, k, v = (qkv[..., j * E:(j + 1) * E].view(B, S, H, D).transpose(1, 2) for j in range(3))
+            a = ops.attn_forward_views(q, k, v).transpose(1, 2).reshape(B, S, E)  # [B, S, H, D] memory: no copy
+            x, n = ops.add_layernorm(x, F.linear(a, *blk["o"]), *blk["ln2"])
+            h = torch._addmm_activation(blk["ff1"][1], n.view(B * S, E), blk["ff1"][0].t(), use_gelu=True).view(B, S, 4 * E)
+            f = F.linear(h, *blk["ff2"])
+            if i + 1 < len(self.blocks):
+                x, n = ops.add_layernorm(x, f, *self.blocks[i + 1]["ln1"])
+            else:
+                x = x + f
+        cls_tok = F.layer_norm(x[:, 0], (E,), self.norm[0], self.norm[1], 1e-5)
+        return F.linear(cls_tok, *self.head)
+
     def forward(self, images: torch.Tensor, attention: str = "fused", copies: bool = False) -> torch.Tensor:
         """images [B, 3, 224, 224] -> logits [B, num_classes].  copies=True: the reference's form, with separate
         projections and materialised transposed views around the kernel."""
+        if attention == "fused" and not copies and self.dtype == torch.bfloat16:
+            return self._forward_fused(images)
         x = F.conv2d(images.to(self.dtype), self.embed_w, self.embed_b, stride=self.patch)
         x = x.flatten(2).transpose(1, 2)  # [B, 196, E]
         x = torch.cat([self.cls.expand(x.shape[0], -1, -1), x], dim=1) + self.pos
@@ -123,22 +156,43 @@ class ViT:
         return other
 
 
-def images_per_second(batch=64, iters=10, warmup=3, attention="fused", seed=3, copies=False) -> dict:
-    """benchmark configuration 4: ViT-B/16, batch 64, 224x224x3 inputs ~ U(0,1) (seed 3), bf16 GEMMs."""
+def images_per_second(batch=64, iters=10, warmup=3, attention="fused", seed=3, copies=False, graph=False) -> dict:
+    """benchmark configuration 4: ViT-B/16, batch 64, 224x224x3 inputs ~ U(0,1) (seed 3), bf16 GEMMs.
+    graph=True: the forward is captured once in a CUDA graph and replayed (the same launches, issued by one call)."""
     model = ViT(seed=seed)
     g = torch.Generator(device="cuda").manual_seed(seed)
     x = torch.rand(batch, 3, 224, 224, device="cuda", generator=g)
+    run = lambda: model.forward(x, attention, copies)
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # warm-up off the default stream, as capture wants it
+            for _ in range(3):
+                eager = model.forward(x, attention, copies)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            logits = model.forward(x, attention, copies)
+        captured.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(logits, eager):
+            raise RuntimeError("the replayed graph and the eager forward disagree")
+        run = captured.replay
     for _ in range(warmup):
-        model.forward(x, attention, copies)
+        run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
-        model.forward(x, attention, copies)
+        run()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
     return {"img_per_s": batch / (ms * 1e-3), "ms_per_batch": ms, "batch": batch, "attention": attention,
-            "layout": "separate projections, transposed copies" if copies or attention != "fused"
-            else "one QKV GEMM, kernel reads and writes [B, S, H, D] views",
+            "launch": "one CUDA graph replay per batch" if graph else "eager launches",
+            "layout": "separate projections, transposed copies, unfused LayerNorm / GELU / conv patch embedding"
+            if copies or attention != "fused"
+            else "patch embedding as a GEMM, one QKV GEMM, kernel reads and writes [B, S, H, D] views, residual add + "
+                 "LayerNorm in one kernel, bias + GELU in the GEMM epilogue",
             "model": "ViT-B/16 random-init, bf16 GEMMs (cuBLAS via torch), attention S=197 D=64"}

@@ -820,7 +820,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     vit_line = None
     if rank == 0 and world == 1 and not args.no_vit:
         from autorust_b200 import vit
-        vit_line = vit.images_per_second(batch=64, iters=10, warmup=3, attention="fused")
+        vit_line = vit.images_per_second(batch=64, iters=20, warmup=5, attention="fused", graph=True)
+        vit_line["img_per_s_eager_launches"] = vit.images_per_second(batch=64, iters=10, warmup=3,
+                                                                      attention="fused")["img_per_s"]
         vit_line["img_per_s_copy_form"] = vit.images_per_second(batch=64, iters=10, warmup=3, attention="fused",
                                                                   copies=True)["img_per_s"]
         vit_line["img_per_s_torch_sdpa"] = vit.images_per_second(batch=64, iters=10, warmup=3,

@@ -267,6 +267,16 @@ int ar_attn_last_status(void* workspace, void* cu_stream);
  * src/runtime/cuda_flash_sage.rs:421-436). */
 uint64_t ar_attn_selections(int mode);
 
+/* The transformer block's residual add and LayerNorm around the attention operator, in one pass over the rows:
+ *     s = x + residual (bf16; written to sum_out when given -- it may be x itself),  y = LayerNorm(s) * gamma + beta.
+ * autorust composes LayerNorm from graph ops (src/tensor/mod.rs:2450-2470: mean, mean of the centred squares,
+ * (x - mean) / sqrt(var + eps); weight and bias src/tensor/nn.rs:773-945) and the block adds its residual as an op of
+ * its own (src/models/transformer.rs:208-255); the statistics here are f32 over the bf16-rounded sum, as theirs over
+ * the stored tensor.  x, residual (nullable), sum_out (nullable), y: [rows, cols] contiguous; gamma, beta: [cols];
+ * dtype AR_DTYPE_BF16; cols a multiple of 8, at most 4096; 16-byte aligned.  Asynchronous on cu_stream. */
+int ar_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* sum_out, void* y,
+                     int64_t rows, int64_t cols, float eps, int dtype, void* cu_stream);
+
 /* Total kernel launches issued by this library since load (all kernels, prologue included). */
 uint64_t ar_attn_launch_count(void);
 

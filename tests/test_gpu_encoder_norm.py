@@ -1,0 +1,37 @@
+"""ar_add_layernorm: the block's residual add and LayerNorm around the attention operator in one pass
+(src/tensor/mod.rs:2450-2470, src/models/transformer.rs:208-255), against torch on the same bf16 inputs."""
+from __future__ import annotations
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 64), (197, 768), (64 * 197, 768), (33, 1024), (7, 3072), (3, 4096)])
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_add_layernorm_matches_torch(attn_lib, rows, cols, with_residual):
+    import torch
+    import torch.nn.functional as F
+    from autorust_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(rows * 131 + cols)
+    x = (torch.randn(rows, cols, device="cuda", generator=g) * 1.5 + 0.3).to(torch.bfloat16)
+    r = torch.randn(rows, cols, device="cuda", generator=g).to(torch.bfloat16) if with_residual else None
+    gamma = (1.0 + 0.2 * torch.randn(cols, device="cuda", generator=g)).to(torch.bfloat16)
+    beta = (0.1 * torch.randn(cols, device="cuda", generator=g)).to(torch.bfloat16)
+    s, y = ops.add_layernorm(x, r, gamma, beta, 1e-5)
+    torch.cuda.synchronize()
+    want_s = x + r if with_residual else x          # bf16 add: the residual stream
+    assert torch.equal(s.view(torch.int16), want_s.view(torch.int16))
+    want = F.layer_norm(want_s.float(), (cols,), gamma.float(), beta.float(), 1e-5)
+    err = (y.float() - want).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.abs().max().item()), err   # one bf16 rounding of an O(1) value
+    assert not torch.isnan(y).any()
+
+
+def test_add_layernorm_refuses_what_it_does_not_cover(attn_lib):
+    import torch
+    from autorust_b200 import _abi, ops
+    x = torch.zeros(4, 12, device="cuda", dtype=torch.bfloat16)   # 12 is not a multiple of 8
+    w = torch.ones(12, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(_abi.AttnLibraryError):
+        ops.add_layernorm(x, None, w, w)
