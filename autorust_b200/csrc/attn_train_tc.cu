@@ -43,27 +43,40 @@ struct TcBwd {
   static constexpr int STAGES = 2;
   static constexpr int SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + 2 * STAGES * T * 4 + 32 * 8 + 1024;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-  static constexpr uint32_t IDESC_SS = make_idesc(1, 1, 1, 0, 0, T, T);  // bf16 x bf16 -> f32, both K-major, N = 128
-  static constexpr uint32_t IDESC_TS = make_idesc(1, 1, 1, 0, 1, T, D);  // A from TMEM, B MN-major, N = D
+  // D = 64: a tile of 128 keys (dQ kernel) or 128 queries (dK/dV kernel) is walked in two halves of 64, so that the
+  // scores, dP and the accumulators of a CTA fit 256 TMEM columns and two CTAs share an SM -- one CTA's MMAs and
+  // waits run under the other's element-wise pass.  D = 128: one step per tile, one CTA per SM (shared memory).
+  static constexpr int HALVES = D == 64 ? 2 : 1;
+  static constexpr int NH = T / HALVES;              // score columns per step
+  static constexpr int TMEM_COLS = HALVES == 2 ? 256 : 512;
+  static constexpr int MIN_CTAS = HALVES;
+  static_assert(HALVES == 1 || 2 * SMEM_BYTES <= 226 * 1024, "two CTAs must fit an SM");
+  static constexpr int KSTEPS_NH = NH / 16;          // k-steps of a product over one step's queries or keys
+  static constexpr uint32_t IDESC_SS = make_idesc(1, 1, 1, 0, 0, T, NH);  // bf16 x bf16 -> f32, both K-major, N = NH
+  static constexpr uint32_t IDESC_TS = make_idesc(1, 1, 1, 0, 1, T, D);   // A from TMEM, B MN-major, N = D
 };
 
-// D[tmem, 128 x 128] = A[128 x D] B[128 x D]^T, both tiles K-major (rows of 128-byte boxes, 128-byte swizzle)
+// D[tmem, 128 x NH] = A[128 x D] B_half[NH x D]^T, both tiles K-major (rows of 128-byte boxes, 128-byte swizzle);
+// `half` selects rows half * NH ... of the B tile
 template <int D>
-__device__ __forceinline__ void mma_abt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi) {
+__device__ __forceinline__ void mma_abt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, int half) {
   if (!elect_one()) return;
+  const uint32_t b_half = b_lo + (uint32_t)((half * TcBwd<D>::NH * 128) >> 4);
 #pragma unroll
   for (int s = 0; s < TcBwd<D>::KSTEPS_D; s++) {
     const uint32_t off = ((s >> 2) * (T * 128) + (s & 3) * 32) >> 4;
-    mma_ss_lohi<KIND_F16>(d_tmem, a_lo + off, hi, b_lo + off, hi, TcBwd<D>::IDESC_SS, s > 0);
+    mma_ss_lohi<KIND_F16>(d_tmem, a_lo + off, hi, b_half + off, hi, TcBwd<D>::IDESC_SS, s > 0);
   }
 }
-// D[tmem, 128 x D] (+)= A[tmem, 128 x 128 bf16] B[128 x D], B consumed MN-major from a row-major tile
+// D[tmem, 128 x D] (+)= A[tmem, 128 x NH bf16] B_half[NH x D], B consumed MN-major from a row-major tile (rows
+// half * NH ... of it)
 template <int D>
-__device__ __forceinline__ void mma_tb(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, bool acc) {
+__device__ __forceinline__ void mma_tb(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, bool acc, int half) {
   if (!elect_one()) return;
+  const uint32_t b_half = b_lo + (uint32_t)(half * TcBwd<D>::KSTEPS_NH) * (2048 >> 4);
 #pragma unroll
-  for (int s = 0; s < TcBwd<D>::KSTEPS_T; s++)
-    mma_ts_lohi<KIND_F16>(d_tmem, a_tmem + s * 8, b_lo + s * (2048 >> 4), b_hi, TcBwd<D>::IDESC_TS, (acc || s > 0) ? 1u : 0u);
+  for (int s = 0; s < TcBwd<D>::KSTEPS_NH; s++)
+    mma_ts_lohi<KIND_F16>(d_tmem, a_tmem + s * 8, b_half + s * (2048 >> 4), b_hi, TcBwd<D>::IDESC_TS, (acc || s > 0) ? 1u : 0u);
 }
 
 // One [128 x D] bf16 tile of a [B, H, S, D] tensor into shared memory (boxes of 64 columns).
@@ -74,7 +87,7 @@ __device__ __forceinline__ void load_rows(uint8_t* dst, const CUtensorMap* m, ui
 
 // ------------------------------------------------------------------------------------------------ dQ
 template <int D>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, TcBwd<D>::MIN_CTAS)
 train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                    const float* __restrict__ LSE, const float* __restrict__ delta, const float* __restrict__ mask,
@@ -119,14 +132,15 @@ train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     fence_mbar_init();
   }
   if (warp == 5) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tb = *tmem_slot;
-  const uint32_t col_S = 0, col_dP = 128, col_dQ = 256;
+  constexpr int HV = C::HALVES, NH = C::NH;
+  const uint32_t col_S = 0, col_dP = NH, col_dQ = 2 * NH;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -159,13 +173,16 @@ train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       const uint32_t kt = smem_u32(sK + s * C::TILE_BYTES) >> 4, vt = smem_u32(sV + s * C::TILE_BYTES) >> 4;
-      mma_abt<D>(tb + col_S, q_lo, (uint32_t)k_proto | kt, k_hi);    // S = Q K^T
-      mma_abt<D>(tb + col_dP, do_lo, (uint32_t)k_proto | vt, k_hi);  // dP = dO V^T
-      commit_one(s_full);
-      ok = __all_sync(0xffffffffu, mbar_wait(ds_full, j & 1, wctx, 0x53));
+      for (int hf = 0; hf < HV && ok; hf++) {  // the tile's keys in steps of NH
+        mma_abt<D>(tb + col_S, q_lo, (uint32_t)k_proto | kt, k_hi, hf);    // S = Q K^T
+        mma_abt<D>(tb + col_dP, do_lo, (uint32_t)k_proto | vt, k_hi, hf);  // dP = dO V^T
+        commit_one(s_full);
+        ok = __all_sync(0xffffffffu, mbar_wait(ds_full, (j * HV + hf) & 1, wctx, 0x53));
+        if (!ok) break;
+        tc_fence_after();
+        mma_tb<D>(tb + col_dQ, tb + col_S, (uint32_t)mn_proto | kt, mn_hi, j > 0 || hf > 0, hf);  // dQ += dS K
+      }
       if (!ok) break;
-      tc_fence_after();
-      mma_tb<D>(tb + col_dQ, tb + col_S, (uint32_t)mn_proto | kt, mn_hi, j > 0);  // dQ += dS K
       commit_one(&kv_empty[s]);
     }
     if (ok) commit_one(acc_full);
@@ -180,12 +197,13 @@ train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float dl = row < N ? delta[(size_t)bh * N + row] : 0.f;
     const float* mrow = (mask != nullptr && row < N) ? mask + (size_t)row * N : nullptr;
     bool ok = true;
-    for (int j = 0; j < nkt; j++) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, wctx, 0x54));
+    for (int g = 0; g < nkt * HV; g++) {  // steps of NH keys
+      const int j = g / HV, hf = g - j * HV;
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, g & 1, wctx, 0x54));
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < NH / 32; c++) {
         uint32_t sv[32], pv[32], pk[16];
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tdP + c * 32, pv);
@@ -195,7 +213,7 @@ train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           float ds[2];
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const int col = j * T + c * 32 + i + e;
+            const int col = j * T + hf * NH + c * 32 + i + e;
             float x = __uint_as_float(sv[i + e]) * scale_log2;
             if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
             const bool out = col >= N || row >= N || (causal && col > row);
@@ -237,12 +255,12 @@ train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tb, 512);
+  if (warp == 5) tmem_dealloc(tb, C::TMEM_COLS);
 }
 
 // --------------------------------------------------------------------------------------------- dK, dV
 template <int D>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, TcBwd<D>::MIN_CTAS)
 train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const float* __restrict__ LSE, const float* __restrict__ delta, const float* __restrict__ mask,
@@ -293,14 +311,15 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     fence_mbar_init();
   }
   if (warp == 5) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tb = *tmem_slot;
-  const uint32_t col_S = 0, col_dP = 128, col_dV = 256, col_dK = 256 + D;
+  constexpr int HV = C::HALVES, NH = C::NH;
+  const uint32_t col_S = 0, col_dP = NH, col_dV = 2 * NH, col_dK = 2 * NH + D;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -334,14 +353,17 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!ok) break;
       tc_fence_after();
       const uint32_t qt = smem_u32(sQ + s * C::TILE_BYTES) >> 4, dot = smem_u32(sdO + s * C::TILE_BYTES) >> 4;
-      mma_abt<D>(tb + col_S, k_lo, (uint32_t)k_proto | qt, k_hi);    // S^T = K Q^T
-      mma_abt<D>(tb + col_dP, v_lo, (uint32_t)k_proto | dot, k_hi);  // dP^T = V dO^T
-      commit_one(s_full);
-      ok = __all_sync(0xffffffffu, mbar_wait(p_full, it & 1, wctx, 0x5b));
+      for (int hf = 0; hf < HV && ok; hf++) {  // the tile's queries in steps of NH
+        mma_abt<D>(tb + col_S, k_lo, (uint32_t)k_proto | qt, k_hi, hf);    // S^T = K Q^T
+        mma_abt<D>(tb + col_dP, v_lo, (uint32_t)k_proto | dot, k_hi, hf);  // dP^T = V dO^T
+        commit_one(s_full);
+        ok = __all_sync(0xffffffffu, mbar_wait(p_full, (it * HV + hf) & 1, wctx, 0x5b));
+        if (!ok) break;
+        tc_fence_after();
+        mma_tb<D>(tb + col_dV, tb + col_S, (uint32_t)mn_proto | dot, mn_hi, it > 0 || hf > 0, hf);  // dV += P^T dO
+        mma_tb<D>(tb + col_dK, tb + col_dP, (uint32_t)mn_proto | qt, mn_hi, it > 0 || hf > 0, hf);  // dK += dS^T Q
+      }
       if (!ok) break;
-      tc_fence_after();
-      mma_tb<D>(tb + col_dV, tb + col_S, (uint32_t)mn_proto | dot, mn_hi, it > 0);  // dV += P^T dO
-      mma_tb<D>(tb + col_dK, tb + col_dP, (uint32_t)mn_proto | qt, mn_hi, it > 0);  // dK += dS^T Q
       commit_one(&qd_empty[s]);
     }
     if (ok) commit_one(acc_full);
@@ -365,11 +387,12 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const float* lse2 = s_lse + (it & 1) * T;
       const float* dl = s_dl + (it & 1) * T;
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, it & 1, wctx, 0x5c));
+      for (int hf = 0; hf < HV && ok; hf++) {
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, (it * HV + hf) & 1, wctx, 0x5c));
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < NH / 32; c++) {
         uint32_t sv[32], pv[32], pk[16], dk[16];
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tdP + c * 32, pv);
@@ -379,7 +402,7 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           float p[2], ds[2];
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const int cc = c * 32 + e2 + e;
+            const int cc = hf * NH + c * 32 + e2 + e;
             const int qrow = i * T + cc;
             float x = __uint_as_float(sv[e2 + e]) * scale_log2;
             if (mask != nullptr && qrow < N && key < N) x = fmaf(mask[(size_t)qrow * N + key], LOG2E, x);
@@ -396,6 +419,8 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
+      }
+      if (!ok) break;
     }
     if (ok && items > 0) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, wctx, 0x5d));
     if (ok) {
@@ -429,7 +454,7 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tb, 512);
+  if (warp == 5) tmem_dealloc(tb, C::TMEM_COLS);
 }
 
 template <int D>
