@@ -202,25 +202,43 @@ train_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       ok = __all_sync(0xffffffffu, mbar_wait(s_full, g & 1, wctx, 0x54));
       if (!ok) break;
       tc_fence_after();
+      // a step whose 128 x NH block lies inside the sequence, below the causal diagonal and under no additive mask
+      // needs none of the per-element tests: two lanes per instruction
+      const int colh = j * T + hf * NH;
+      const bool interior = mask == nullptr && colh + NH <= N && q0 + T <= N && (!causal || colh + NH - 1 <= q0);
 #pragma unroll 1
       for (int c = 0; c < NH / 32; c++) {
         uint32_t sv[32], pv[32], pk[16];
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tdP + c * 32, pv);
         tmem_wait_ld();
+        if (interior) {
+          const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nl2 = pack_f32x2(-lse2, -lse2),
+                         ndl2 = pack_f32x2(-dl, -dl);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const int col = j * T + hf * NH + c * 32 + i + e;
-            float x = __uint_as_float(sv[i + e]) * scale_log2;
-            if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
-            const bool out = col >= N || row >= N || (causal && col > row);
-            const float p = out ? 0.f : ex2f(x - lse2);
-            ds[e] = p * (__uint_as_float(pv[i + e]) - dl);
+          for (int i = 0; i < 32; i += 2) {
+            float a, b2;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl2), a, b2);
+            const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(pv[i]), __uint_as_float(pv[i + 1])), ndl2);
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(ex2f(a), ex2f(b2)), d2), d0, d1);
+            pk[i >> 1] = pack_bf16x2(d0, d1);
           }
-          pk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int col = colh + c * 32 + i + e;
+              float x = __uint_as_float(sv[i + e]) * scale_log2;
+              if (mrow != nullptr && col < N) x = fmaf(mrow[col], LOG2E, x);
+              const bool out = col >= N || row >= N || (causal && col > row);
+              const float p = out ? 0.f : ex2f(x - lse2);
+              ds[e] = p * (__uint_as_float(pv[i + e]) - dl);
+            }
+            pk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+          }
         }
         tmem_st16(tS + c * 16, pk);  // dS over the columns of S that have been read
       }
@@ -381,22 +399,45 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // the item's per-query values: every thread brings one, all 128 read them
       {
         const int qrow = i * T + r;
-        s_lse[(it & 1) * T + r] = qrow < N ? LSE[(size_t)bhq * N + qrow] * LOG2E : 0.f;
-        s_dl[(it & 1) * T + r] = qrow < N ? delta[(size_t)bhq * N + qrow] : 0.f;
+        s_lse[(it & 1) * T + r] = qrow < N ? -LSE[(size_t)bhq * N + qrow] * LOG2E : 0.f;  // (negated: added below)
+        s_dl[(it & 1) * T + r] = qrow < N ? -delta[(size_t)bhq * N + qrow] : 0.f;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      const float* lse2 = s_lse + (it & 1) * T;
-      const float* dl = s_dl + (it & 1) * T;
+      const float* nlse2 = s_lse + (it & 1) * T;
+      const float* ndl = s_dl + (it & 1) * T;
       for (int hf = 0; hf < HV && ok; hf++) {
       ok = __all_sync(0xffffffffu, mbar_wait(s_full, (it * HV + hf) & 1, wctx, 0x5c));
       if (!ok) break;
       tc_fence_after();
+      // a step whose 128 keys x NH queries lie inside the sequence, on the visible side of the causal diagonal and
+      // under no additive mask needs none of the per-element tests: two lanes per instruction
+      const int qh = i * T + hf * NH;
+      const bool interior = mask == nullptr && k0 + T <= N && qh + NH <= N && (!causal || k0 + T - 1 <= qh);
 #pragma unroll 1
       for (int c = 0; c < NH / 32; c++) {
         uint32_t sv[32], pv[32], pk[16], dk[16];
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tdP + c * 32, pv);
         tmem_wait_ld();
+        if (interior) {
+          const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2);
+          const float2* nl = reinterpret_cast<const float2*>(nlse2 + hf * NH + c * 32);
+          const float2* nd = reinterpret_cast<const float2*>(ndl + hf * NH + c * 32);
+#pragma unroll
+          for (int e2 = 0; e2 < 32; e2 += 2) {
+            const float2 l = nl[e2 >> 1], dd = nd[e2 >> 1];
+            float a, b2;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[e2]), __uint_as_float(sv[e2 + 1])), sc2,
+                                   pack_f32x2(l.x, l.y)), a, b2);
+            const float p0 = ex2f(a), p1 = ex2f(b2);
+            const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(pv[e2]), __uint_as_float(pv[e2 + 1])),
+                                          pack_f32x2(dd.x, dd.y));
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), d2), d0, d1);
+            pk[e2 >> 1] = pack_bf16x2(p0, p1);
+            dk[e2 >> 1] = pack_bf16x2(d0, d1);
+          }
+        } else {
 #pragma unroll
         for (int e2 = 0; e2 < 32; e2 += 2) {
           float p[2], ds[2];
@@ -407,11 +448,12 @@ train_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             float x = __uint_as_float(sv[e2 + e]) * scale_log2;
             if (mask != nullptr && qrow < N && key < N) x = fmaf(mask[(size_t)qrow * N + key], LOG2E, x);
             const bool out = key >= N || qrow >= N || (causal && key > qrow);
-            p[e] = out ? 0.f : ex2f(x - lse2[cc]);
-            ds[e] = p[e] * (__uint_as_float(pv[e2 + e]) - dl[cc]);
+            p[e] = out ? 0.f : ex2f(x + nlse2[cc]);
+            ds[e] = p[e] * (__uint_as_float(pv[e2 + e]) + ndl[cc]);
           }
           pk[e2 >> 1] = pack_bf16x2(p[0], p[1]);
           dk[e2 >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
         }
         tmem_st16(tS + c * 16, pk);   // P^T over the columns of S^T that have been read
         tmem_st16(tdP + c * 16, dk);  // dS^T likewise over dP^T
