@@ -38,6 +38,7 @@ SYMBOLS = (
     "ar_attn_train_workspace_bytes",
     "ar_attn_train_backward",
     "ar_attn_train_tc_workspace_bytes",
+    "ar_attn_train_forward_tc",
     "ar_attn_train_backward_tc",
     "ar_sage_quantize",
     "ar_sage_quantize_fp8",
@@ -102,6 +103,8 @@ def load() -> ctypes.CDLL:
     L.ar_attn_train_backward.restype = ci
     L.ar_attn_train_tc_workspace_bytes.argtypes = [i64, i64, i64, i64, i64]
     L.ar_attn_train_tc_workspace_bytes.restype = ctypes.c_size_t
+    L.ar_attn_train_forward_tc.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, i64, ci, p, ctypes.c_size_t, p]
+    L.ar_attn_train_forward_tc.restype = ci
     L.ar_attn_train_backward_tc.argtypes = L.ar_attn_train_backward.argtypes
     L.ar_attn_train_backward_tc.restype = ci
     L.ar_sage_quantize.argtypes = [p, p, ci, p, p, p, p, p, i64, i64, i64, i64, i64, ci, ci, p]

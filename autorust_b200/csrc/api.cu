@@ -473,6 +473,50 @@ size_t ar_attn_train_tc_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int6
   return train_tc_layout(B, Hq, Hkv, S, D).total;
 }
 
+int ar_attn_train_forward_tc(const float* q, const float* k, const float* v, float* o, float* lse, const float* mask,
+                             int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                             size_t workspace_bytes, void* cu_stream) {
+  if (!q || !k || !v || !o || !lse || !workspace) return AR_ERR_NULL;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != AR_OK) return rc;
+  if ((D != 64 && D != 128) || B * Hq > 65535 || S > (1 << 24)) return AR_ERR_UNSUPPORTED;
+  const TrainTcLayout L = train_tc_layout(B, Hq, Hkv, S, D);
+  if (workspace_bytes < L.total) return AR_ERR_WORKSPACE;
+  for (const void* p : {(const void*)q, (const void*)k, (const void*)v, (const void*)o, (const void*)workspace})
+    if (!aligned16(p)) return AR_ERR_ALIGNMENT;
+  if (!aligned4(lse) || !aligned4(mask)) return AR_ERR_ALIGNMENT;
+  if (!device_ok()) return AR_ERR_NO_DEVICE;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  uint8_t* ws = (uint8_t*)workspace;
+  if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream) != cudaSuccess) return AR_ERR_CUDA;
+  if (ar::launch_f32_to_bf16(q, ws + L.q16, B * Hq * S * D, stream) != cudaSuccess ||
+      ar::launch_f32_to_bf16(k, ws + L.k16, B * Hkv * S * D, stream) != cudaSuccess ||
+      ar::launch_f32_to_bf16(v, ws + L.v16, B * Hkv * S * D, stream) != cudaSuccess)
+    return AR_ERR_CUDA;
+  ar::TcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.mode = ar::TC_BF16;
+  a.D = (int)D;
+  a.out = o;
+  a.out_f32 = 1;
+  a.o_sb = (long long)Hq * S * D;
+  a.o_sh = (long long)S * D;
+  a.o_ss = D;
+  a.mask = mask;
+  a.B = (int)B; a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.S = (int)S;
+  a.causal = causal ? 1 : 0;
+  a.lse_out = lse;
+  a.status = (uint32_t*)ws;
+  a.sticky = sticky_ptr();
+  if (!make_map(&a.tm_q, ws + L.q16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hq, S, D) ||
+      !make_map(&a.tm_k, ws + L.k16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D) ||
+      !make_map(&a.tm_v, ws + L.v16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, Hkv, S, D))
+    return AR_ERR_CUDA;
+  if (ar::launch_attn_tc(a, stream) != cudaSuccess) return AR_ERR_CUDA;
+  g_launches += 4;
+  return AR_OK;
+}
+
 int ar_attn_train_backward_tc(const float* q, const float* k, const float* v, const float* o, const float* d_o,
                               const float* lse, const float* mask, float* dq, float* dk, float* dv, int64_t B,
                               int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,

@@ -49,6 +49,7 @@ struct TcArgs {
   int causal;
   OutReplicas replicas; // bf16 output only
   OutProgress progress;
+  float* lse_out;       // [B*Hq, S] natural-log sum of exponentials per row (the training forward), or null
   uint32_t* status;     // the launch's device status word: zero at launch, set when a bounded wait ran out
   uint32_t* sticky;     // the library's accumulator of the same bits (nullable)
 };

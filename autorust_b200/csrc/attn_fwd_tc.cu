@@ -316,7 +316,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_v, void* __restrict__ out, const float* __restrict__ mask,
                    const float* __restrict__ q_scale, const float* __restrict__ k_scale, int N, int Hq, int Hkv,
                    int causal, int out_f32, int token_major, long long o_sb, long long o_sh, long long o_ss,
-                   const OutReplicas reps, const OutProgress progress, uint32_t* status, uint32_t* sticky) {
+                   const OutReplicas reps, const OutProgress progress, float* __restrict__ lse_out, uint32_t* status,
+                   uint32_t* sticky) {
   using C = Cfg<MODE, D, TILES>;
   constexpr int ST = C::STAGES;
   constexpr int W_PROD = 4 * TILES;     // warp that loads
@@ -611,6 +612,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (ok) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.0f / l : 0.f;
+        // the training forward's second output: ln sum_j exp(logit_j) = (m + log2 l) / log2 e, whatever reference the
+        // lazily updated m is
+        if (lse_out != nullptr && row < N) lse_out[(size_t)bh * N + row] = (m + log2f(l)) * (1.0f / LOG2E);
         if (out_f32) {
           const size_t obase = (size_t)((long long)b * o_sb + (long long)h * o_sh + (long long)row * o_ss);
 #pragma unroll
@@ -729,7 +733,7 @@ cudaError_t launch_one(const TcArgs& a, cudaStream_t stream) {
   kern<<<grid, Shape<TILES>::NUM_THREADS, C::SMEM_BYTES, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.out, a.mask, a.q_scale,
                                                                    a.k_scale, a.S, a.Hq, a.Hkv, a.causal, a.out_f32,
                                                                    a.token_major, a.o_sb, a.o_sh, a.o_ss, a.replicas,
-                                                                   a.progress, a.status, a.sticky);
+                                                                   a.progress, a.lse_out, a.status, a.sticky);
   return cudaGetLastError();
 }
 

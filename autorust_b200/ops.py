@@ -158,8 +158,9 @@ def attn_forward_views(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: 
 
 
 def train_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None = None,
-                  causal: bool = False, stream=None):
-    """Exact f32 forward that also returns the rows' log-sum-exp: (o [B,Hq,S,D], lse [B,Hq,S])."""
+                  causal: bool = False, stream=None, tensor_cores: bool = False):
+    """Forward that also returns the rows' log-sum-exp: (o [B,Hq,S,D], lse [B,Hq,S]), float32 tensors.  Exact f32
+    kernel, or with tensor_cores the bf16 tcgen05 kernel on bf16 copies of the operands (ar_attn_train_forward_tc)."""
     L = _abi.load()
     _check_qkv(q, k, v)
     if q.dtype != torch.float32:
@@ -168,6 +169,17 @@ def train_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch
     _check_mask(mask, S, q.device)
     o = torch.empty_like(q)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    if tensor_cores:
+        need = int(L.ar_attn_train_tc_workspace_bytes(B, Hq, k.shape[1], S, D))
+        ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        with torch.cuda.device(q.device):
+            s = stream if stream is not None else torch.cuda.current_stream()
+            rc = L.ar_attn_train_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                            mask.data_ptr() if mask is not None else None, B, Hq, k.shape[1], S, D,
+                                            int(causal), ws.data_ptr(), need, s.cuda_stream)
+        _abi.check(rc, "ar_attn_train_forward_tc")
+        ws.record_stream(s)
+        return o, lse
     with torch.cuda.device(q.device):
         s = stream if stream is not None else torch.cuda.current_stream()
         rc = L.ar_attn_train_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),

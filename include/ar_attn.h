@@ -173,6 +173,17 @@ int ar_attn_train_backward(const float* q, const float* k, const float* v, const
  * absolute 2e-3 (tests/flash_train_cuda.rs:80,102-104) for the plain and masked cases, above it for the causal and GQA
  * cases, whose gradients are larger; ar_attn_train_backward remains the exact f32 path.  The reference's backward is scalar f32 only (src/runtime/cuda_flash_train.rs:118-309). */
 size_t ar_attn_train_tc_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D);
+
+/* The training forward in the same fast mode: o and the rows' log-sum-exp from the bf16 tensor-core kernel, on bf16
+ * copies of q, k, v made inside the call (workspace of ar_attn_train_tc_workspace_bytes, whose status block
+ * ar_attn_last_status reads).  Arguments as ar_attn_train_forward; D in {64, 128}.  o carries the bf16 kernel's
+ * accuracy (2e-2 max-abs on N(0,1) inputs, P rounded to bf16), lse about 1e-3; gradients taken from them with
+ * ar_attn_train_backward_tc stay within that call's stated accuracy of the exact ones.  ar_attn_train_forward (f32)
+ * remains the exact path.  The reference's training forward is scalar f32 only
+ * (src/runtime/cuda_flash_train.rs:49-117). */
+int ar_attn_train_forward_tc(const float* q, const float* k, const float* v, float* o, float* lse, const float* mask,
+                             int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,
+                             size_t workspace_bytes, void* cu_stream);
 int ar_attn_train_backward_tc(const float* q, const float* k, const float* v, const float* o, const float* d_o,
                               const float* lse, const float* mask, float* dq, float* dk, float* dv, int64_t B,
                               int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int causal, void* workspace,

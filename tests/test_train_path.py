@@ -114,6 +114,33 @@ def test_gpu_tensor_core_backward_matches_oracle(ops, oracle_lib, tag, b, h, hk,
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tag,b,h,hk,n,d,causal,with_mask", CASES + [("d64-causal/300", 1, 4, 2, 300, 64, True, False)])
+def test_gpu_tensor_core_forward_and_the_whole_fast_step(ops, oracle_lib, tag, b, h, hk, n, d, causal, with_mask):
+    """ar_attn_train_forward_tc (o and log-sum-exp from the bf16 tcgen05 kernel) against the exact forward, and the
+    gradients ar_attn_train_backward_tc takes from ITS outputs against the float64-checked oracle: the whole fast
+    training step.  o: 2e-2 max-abs (the bf16 forward's bound); lse: 5e-3; gradients: 1e-2 of the largest entry and
+    a cosine of 0.9995 (the backward's own 5e-3 plus what the bf16 o adds to D_i)."""
+    import torch
+    q, k, v, d_o, mask = _case(b, h, hk, n, d, with_mask)
+    want_o, want_lse, want_dq, want_dk, want_dv = oracle_lib.attn_train(q, k, v, d_o, mask, causal)
+    tq, tk, tv, tdo = (torch.from_numpy(x).cuda() for x in (q, k, v, d_o))
+    tm = torch.from_numpy(mask).cuda() if mask is not None else None
+    o, lse = ops.train_forward(tq, tk, tv, tm, causal, tensor_cores=True)
+    o2, lse2 = ops.train_forward(tq, tk, tv, tm, causal, tensor_cores=True)
+    dq, dk, dv = ops.train_backward(tq, tk, tv, o, tdo, lse, tm, causal, tensor_cores=True)
+    torch.cuda.synchronize()
+    assert ops.last_status(None) == 0
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    assert max_abs(o.cpu().numpy(), want_o) <= 2e-2 * max(1.0, float(np.abs(want_o).max())), tag
+    assert max_abs(lse.cpu().numpy(), want_lse) <= 5e-3, (tag, max_abs(lse.cpu().numpy(), want_lse))
+    for name, got, want in (("dq", dq, want_dq), ("dk", dk, want_dk), ("dv", dv, want_dv)):
+        err = max_abs(got.cpu().numpy(), want)
+        g64, w64 = got.cpu().numpy().astype(np.float64).ravel(), want.astype(np.float64).ravel()
+        cos = float(g64 @ w64 / (np.linalg.norm(g64) * np.linalg.norm(w64)))
+        assert err < 1e-2 * max(1.0, float(np.abs(want).max())) and cos >= 0.9995, (tag, name, err, cos)
+
+
+@pytest.mark.gpu
 def test_gpu_tensor_core_backward_long_sequence_against_the_f32_kernels(ops):
     """Multi-tile, GQA, causal: the tensor-core gradients against the exact f32 kernels' on N(0,1) inputs."""
     import torch
