@@ -111,3 +111,50 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_abi, "LIB_DIR", tmp_path)
     with pytest.raises(_abi.AttnLibraryError, match="no fallback"):
         _abi.load()
+
+
+def test_gather_library_exports_every_symbol_its_header_declares():
+    declared = _declared_functions(ROOT / "include" / "ar_attn_gather.h")
+    assert "ar_gather_p2p_push_progressive" in declared and "ar_gather_init" in declared
+    lib = _abi.LIB_DIR / "libar_gather.so"
+    if not lib.exists():
+        from autorust_b200 import build
+        build.build_gather()
+    out = subprocess.run(["nm", "-D", "--defined-only", str(lib)], capture_output=True, text=True, check=True).stdout
+    exported = set(re.findall(r" T (ar_[a-z0-9_]+)", out))
+    missing = set(declared) - exported
+    assert not missing, f"declared but not exported: {missing}"
+    from autorust_b200 import multi_gpu
+    loaded = multi_gpu.load()  # binds NCCL; the calls below touch no device
+    assert loaded.ar_gather_p2p_open(None, 16) != 0
+    assert loaded.ar_gather_p2p_push_progressive(None, 0, 16, 1, 1, 1, 1, None) != 0
+    assert not loaded.ar_gather_p2p_peer(None, 0)
+
+
+def test_the_newer_entry_points_reject_bad_calls_without_touching_a_device(attn_lib):
+    L = attn_lib
+    # completion reports: both word arrays and a non-zero epoch are required
+    rc = L.ar_attn_forward_reporting(_abi.MODE_BF16, _abi.DTYPE_BF16, 0x1000, 0x2000, 0x3000, 0x4000, None, 0, None, 0x6000, 1,
+                                     None, 1, 2, 2, 128, 128, 0, None, 0, None)
+    assert rc == _abi.AR_ERR_NULL
+    rc = L.ar_attn_forward_reporting(_abi.MODE_BF16, _abi.DTYPE_BF16, 0x1000, 0x2000, 0x3000, 0x4000, None, 0, 0x5000, 0x6000, 0,
+                                     None, 1, 2, 2, 128, 128, 0, None, 0, None)
+    assert rc == _abi.AR_ERR_NULL
+    # a multicast "replica" must be a 16-byte aligned address
+    arr = (ctypes.c_void_p * 1)(0x7008)
+    rc = L.ar_attn_forward_replicated(_abi.MODE_BF16, _abi.DTYPE_BF16, 0x1000, 0x2000, 0x3000, 0x4000, arr,
+                                      _abi.REPLICAS_MULTICAST, None, 1, 2, 2, 128, 128, 0, None, 0, None)
+    assert rc == _abi.AR_ERR_ALIGNMENT
+    # the encoder kernel: bf16 rows whose length is a multiple of 8, at most 4096
+    ln = L.ar_add_layernorm
+    assert ln(None, None, 0x2000, 0x3000, None, 0x4000, 4, 64, 1e-5, _abi.DTYPE_BF16, None) == _abi.AR_ERR_NULL
+    assert ln(0x1000, None, 0x2000, 0x3000, None, 0x4000, 4, 12, 1e-5, _abi.DTYPE_BF16, None) == _abi.AR_ERR_UNSUPPORTED
+    assert ln(0x1000, None, 0x2000, 0x3000, None, 0x4000, 4, 8192, 1e-5, _abi.DTYPE_BF16, None) == _abi.AR_ERR_UNSUPPORTED
+    assert ln(0x1000, None, 0x2000, 0x3000, None, 0x4000, 4, 64, 1e-5, _abi.DTYPE_F32, None) == _abi.AR_ERR_UNSUPPORTED
+    assert ln(0x1000, None, 0x2000, 0x3000, None, 0x4000, 0, 64, 1e-5, _abi.DTYPE_BF16, None) == _abi.AR_ERR_SHAPE
+    assert ln(0x1004, None, 0x2000, 0x3000, None, 0x4000, 4, 64, 1e-5, _abi.DTYPE_BF16, None) == _abi.AR_ERR_ALIGNMENT
+    # the training forward on the tensor cores needs its workspace
+    tf = L.ar_attn_train_forward_tc
+    assert tf(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, None, 1, 2, 2, 128, 64, 0, None, 0, None) == _abi.AR_ERR_NULL
+    assert tf(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, None, 1, 2, 2, 128, 64, 0, 0x10000, 16, None) == _abi.AR_ERR_WORKSPACE
+    assert tf(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, None, 1, 2, 2, 128, 96, 0, 0x10000, 1 << 30, None) == _abi.AR_ERR_UNSUPPORTED
