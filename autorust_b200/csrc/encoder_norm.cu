@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(128) add_layernorm_kernel(const uint4* __restr
         const uint4 s = pack8(v[c]);  // the residual stream is bf16: the statistics see the rounded values
         if (sum_out) sum_out[row * chunks + idx] = s;
         unpack8(s, v[c]);
+      } else if (sum_out && sum_out != x) {
+        sum_out[row * chunks + idx] = xr[idx];  // no residual: the sum is x
       }
 #pragma unroll
       for (int i = 0; i < 8; i++) total += v[c][i];

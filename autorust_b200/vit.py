@@ -108,6 +108,7 @@ class ViT:
         cast and patch order in one copy, then [B*196, 768] x [768, 768]); residual add + LayerNorm in one kernel
         (ar_add_layernorm), which hands the next GEMM its input and keeps the residual stream; q, k, v as views of
         one QKV GEMM; bias + GELU in the MLP GEMM's epilogue."""
+        images = images.contiguous()
         B, E, P = images.shape[0], self.embed_dim, self.patch
         g = images.shape[-1] // P
         patches = torch.empty((B, g, g, images.shape[1], P, P), dtype=self.dtype, device=images.device)

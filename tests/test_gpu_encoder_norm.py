@@ -28,6 +28,21 @@ def test_add_layernorm_matches_torch(attn_lib, rows, cols, with_residual):
     assert not torch.isnan(y).any()
 
 
+def test_add_layernorm_without_residual_can_still_write_the_sum(attn_lib):
+    """Through the C ABI directly: sum_out with no residual receives x itself."""
+    import torch
+    from autorust_b200 import _abi
+    L = _abi.load()
+    x = torch.randn(9, 256, device="cuda").to(torch.bfloat16)
+    w = torch.ones(256, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(256, device="cuda", dtype=torch.bfloat16)
+    s, y = torch.zeros_like(x), torch.empty_like(x)
+    rc = L.ar_add_layernorm(x.data_ptr(), None, w.data_ptr(), b.data_ptr(), s.data_ptr(), y.data_ptr(), 9, 256, 1e-5,
+                            _abi.DTYPE_BF16, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(s, x) and not torch.isnan(y).any()
+
+
 def test_add_layernorm_refuses_what_it_does_not_cover(attn_lib):
     import torch
     from autorust_b200 import _abi, ops
