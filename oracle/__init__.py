@@ -239,3 +239,21 @@ def cpu_sdpa_f32(q, k, v, causal=False, bh_begin=0, bh_end=None):
     if n < 0:
         raise ValueError("ar_cpu_sdpa_f32 rejected the shapes")
     return out, n
+
+
+def add_layernorm(x_bf16, r_bf16, gamma_bf16, beta_bf16, eps=1e-5):
+    """The transformer block's `x = x + r` followed by LayerNorm over the last axis, as autorust composes it:
+    mean, mean of the centred squares, (x - mean) / sqrt(var + eps) (src/tensor/mod.rs:2450-2470), then weight and
+    bias (src/tensor/nn.rs:773-945); the sum is stored as bf16 and the statistics are taken over the stored values
+    (src/models/transformer.rs:208-255 adds the residual as an op of its own).  numpy, float32 statistics.
+    Arguments and results are bf16 bit patterns (uint16); r_bf16 may be None.  Returns (sum, y)."""
+    x = bf16_to_f32(np.ascontiguousarray(x_bf16, np.uint16))
+    s16 = np.ascontiguousarray(x_bf16, np.uint16)
+    if r_bf16 is not None:
+        s16 = f32_to_bf16(x + bf16_to_f32(np.ascontiguousarray(r_bf16, np.uint16)))
+    s = bf16_to_f32(s16).astype(np.float32)
+    mean = s.mean(axis=-1, keepdims=True, dtype=np.float32)
+    diff = s - mean
+    var = (diff * diff).mean(axis=-1, keepdims=True, dtype=np.float32)
+    y = diff / np.sqrt(var + np.float32(eps)) * bf16_to_f32(gamma_bf16) + bf16_to_f32(beta_bf16)
+    return s16, f32_to_bf16(y.astype(np.float32))

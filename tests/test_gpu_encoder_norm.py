@@ -28,6 +28,28 @@ def test_add_layernorm_matches_torch(attn_lib, rows, cols, with_residual):
     assert not torch.isnan(y).any()
 
 
+@pytest.mark.parametrize("rows,cols,with_residual", [(197, 768, True), (64, 768, False), (9, 4096, True)])
+def test_add_layernorm_matches_the_oracle(attn_lib, oracle_lib, rows, cols, with_residual):
+    """Against the CPU restatement of the reference's composition (oracle.add_layernorm): the sum bit for bit, the
+    output within one bf16 step of an O(1) value."""
+    import numpy as np
+    import torch
+    from autorust_b200 import ops
+    rng = np.random.default_rng(rows + cols)
+    mk = lambda *shape, scale=1.0, shift=0.0: oracle_lib.f32_to_bf16(rng.standard_normal(shape, dtype=np.float32) * scale + shift)
+    x, r = mk(rows, cols, scale=1.5, shift=0.3), (mk(rows, cols) if with_residual else None)
+    g, b = mk(cols, scale=0.2, shift=1.0), mk(cols, scale=0.1)
+    dev = lambda a: torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16)
+    s, y = ops.add_layernorm(dev(x), dev(r) if r is not None else None, dev(g), dev(b), 1e-5)
+    torch.cuda.synchronize()
+    want_s, want_y = oracle_lib.add_layernorm(x, r, g, b, 1e-5)
+    got_s = s.cpu().view(torch.int16).numpy().view(np.uint16)
+    got_y = oracle_lib.bf16_to_f32(y.cpu().view(torch.int16).numpy().view(np.uint16))
+    assert np.array_equal(got_s, want_s)
+    want = oracle_lib.bf16_to_f32(want_y)
+    assert np.abs(got_y - want).max() <= 2e-2 * max(1.0, np.abs(want).max())
+
+
 def test_add_layernorm_without_residual_can_still_write_the_sum(attn_lib):
     """Through the C ABI directly: sum_out with no residual receives x itself."""
     import torch

@@ -317,3 +317,30 @@ def test_cpu_baseline_thread_count_is_explicit(oracle_lib):
     assert oracle_lib.cpu_sdpa_f32(q, k, v)[1] == 2
     n = oracle_lib.set_cpu_threads()
     assert n >= 1 and oracle_lib.cpu_sdpa_f32(q, k, v)[1] == n
+
+
+def test_add_layernorm_oracle_against_float64(oracle_lib):
+    """The numpy restatement of residual add + LayerNorm against the same formulas in float64."""
+    rng = np.random.default_rng(11)
+    for rows, cols in ((3, 8), (5, 768), (2, 4096)):
+        x = oracle_lib.f32_to_bf16(rng.standard_normal((rows, cols), dtype=np.float32) * 1.5 + 0.3)
+        r = oracle_lib.f32_to_bf16(rng.standard_normal((rows, cols), dtype=np.float32))
+        g = oracle_lib.f32_to_bf16(1.0 + 0.2 * rng.standard_normal(cols, dtype=np.float32))
+        b = oracle_lib.f32_to_bf16(0.1 * rng.standard_normal(cols, dtype=np.float32))
+        for res in (None, r):
+            s16, y16 = oracle_lib.add_layernorm(x, res, g, b, 1e-5)
+            xs = oracle_lib.bf16_to_f32(x).astype(np.float64)
+            if res is not None:
+                want_s = oracle_lib.f32_to_bf16((xs + oracle_lib.bf16_to_f32(res)).astype(np.float32))
+                assert np.array_equal(s16, want_s)
+            else:
+                assert np.array_equal(s16, x)
+            s = oracle_lib.bf16_to_f32(s16).astype(np.float64)
+            mean = s.mean(-1, keepdims=True)
+            var = ((s - mean) ** 2).mean(-1, keepdims=True)
+            want = (s - mean) / np.sqrt(var + 1e-5) * oracle_lib.bf16_to_f32(g) + oracle_lib.bf16_to_f32(b)
+            got = oracle_lib.bf16_to_f32(y16).astype(np.float64)
+            assert np.abs(got - want).max() <= 2e-2 * max(1.0, np.abs(want).max())
+            # rows are normalised: mean 0 and variance 1 before the affine part, whatever went in
+            z = (s - mean) / np.sqrt(var + 1e-5)
+            assert np.abs(z.mean(-1)).max() < 1e-6 and np.abs(z.var(-1) - 1).max() < 1e-3
